@@ -1,0 +1,228 @@
+/*
+ * ref_kernels_host.cpp -- TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+ *
+ * Runs the reference's OWN CUDA kernels for the hot path on host threads, so
+ * that golden vectors come from the reference source itself on a machine
+ * without a GPU.  The kernel sources are compiled with g++ from the reference
+ * tree where they lie (include path given by the Makefile; nothing is copied):
+ *   cu_sIm2Col_r8_within   srcs/convolution/CUDA/im2col/im2col.cuh:86-178
+ *   cu_conv_eq_mm          srcs/convolution/CUDA/im2col/eq_GEMM.cuh:109-209
+ *   cu_GEMM_fp32_spec      srcs/GEMM/CUDA/large_squares/GEMM.cuh:31-100
+ *   cu_GEMM_fp32_ABC_spec  srcs/GEMM/CUDA/large_squares/GEMM.cuh:206-280
+ *
+ * How: one host thread per CUDA thread of a block; `threadIdx`/`blockIdx` are
+ * thread-local variables, `__shared__` becomes function-static storage (one
+ * block runs at a time), `__syncthreads()` is a pthread barrier.  The vector
+ * types and make_float4 etc. come from the CUDA toolkit's host headers.  The
+ * reference's umbrella headers (core/basic.h, core/include.h,
+ * classes/core_types.h) pull in windows.h and thrust and are skipped by
+ * pre-defining their include guards; the kernels use nothing from them.
+ *
+ * The launch geometry and the staging buffers of the reference's host
+ * drivers are reproduced here as plain arithmetic, each line citing the
+ * driver line it follows.  Staging buffers are zero-initialised (the
+ * reference takes them uninitialised from its pool; parity is defined with
+ * zeroed buffers).
+ */
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <pthread.h>
+#include <sys/types.h>
+#include <cmath>
+#include <cstdint>
+#include <cstdlib>
+#include <cstring>
+#include <functional>
+#include <thread>
+#include <vector>
+
+#undef __shared__
+#define __shared__ static
+static thread_local uint3 threadIdx, blockIdx;
+static thread_local dim3 blockDim, gridDim;
+static pthread_barrier_t g_block_barrier;
+static inline void __syncthreads() { pthread_barrier_wait(&g_block_barrier); }
+
+#define _BASIC_H_
+#define _INCLUDE_H_
+#define _CORE_TYPES_H_
+#include "convolution/CUDA/im2col/im2col.cuh"
+#include "convolution/CUDA/im2col/eq_GEMM.cuh"
+#include "GEMM/CUDA/large_squares/GEMM.cuh"
+
+/* Emulated <<<grid, block>>>: persistent worker threads walk the blocks in
+ * order with a barrier between blocks. */
+static void launch(dim3 grid, dim3 block, const std::function<void()>& kernel)
+{
+    const unsigned nt = block.x * block.y * block.z;
+    pthread_barrier_init(&g_block_barrier, nullptr, nt);
+    std::vector<std::thread> workers;
+    for (unsigned t = 0; t < nt; ++t) {
+        workers.emplace_back([=, &kernel] {
+            threadIdx = make_uint3(t % block.x, (t / block.x) % block.y, t / (block.x * block.y));
+            blockDim = block; gridDim = grid;
+            for (unsigned bz = 0; bz < grid.z; ++bz)
+                for (unsigned by = 0; by < grid.y; ++by)
+                    for (unsigned bx = 0; bx < grid.x; ++bx) {
+                        blockIdx = make_uint3(bx, by, bz);
+                        kernel();
+                        pthread_barrier_wait(&g_block_barrier);
+                    }
+        });
+    }
+    for (auto& w : workers) w.join();
+    pthread_barrier_destroy(&g_block_barrier);
+}
+
+static inline size_t ceil_to(size_t v, size_t m) { return (v + m - 1) / m * m; }
+
+static float4* zalloc4(size_t floats)
+{
+    void* p = nullptr;
+    const size_t bytes = ceil_to(floats * sizeof(float), 64) + 64;
+    if (posix_memalign(&p, 64, bytes)) return nullptr;
+    memset(p, 0, bytes);
+    return (float4*)p;
+}
+
+struct ConvDims {
+    int2 kernel_shift; unsigned out_w, out_h; unsigned dp, wp, kwp;
+    unsigned ker_buf_w, ker_buf_h, actual_dst_buf_W;
+    int2 eq_src; size_t src_buf_w, src_buf_h, i2c_w, i2c_h; unsigned dst_buf_w; size_t dst_buf_h;
+    unsigned src_row0, src_col0;
+};
+
+/* conv2_mk_im2col.h:60-93 (valid mode) and :170-199 (zero-border mode). */
+static int conv_dims(unsigned W, unsigned H, unsigned depth, unsigned kW, unsigned kH, unsigned N, int flag, ConvDims* d)
+{
+    if (flag != 0 && flag != 1) return 1;
+    d->dp = (unsigned)ceil_to(depth, 4); d->wp = (unsigned)ceil_to(W, 4); d->kwp = (unsigned)ceil_to(kW, 4);
+    d->kernel_shift = make_int2(8 - (int)kH / 2, 8 - (int)kW / 2);                     /* :60, :170 */
+    if (d->kernel_shift.x < 0 || d->kernel_shift.y < 0) return 2;
+    d->out_w = flag ? W : W - (kW / 2) * 2;                                            /* :63-64, :173-174 */
+    d->out_h = flag ? H : H - (kH / 2) * 2;
+    if ((int)d->out_w <= 0 || (int)d->out_h <= 0) return 3;
+    d->ker_buf_w = (unsigned)ceil_to((size_t)kW * kH * d->dp, 128);                    /* :72-73, :182-183 */
+    d->ker_buf_h = (unsigned)ceil_to(N, 32);
+    d->actual_dst_buf_W = (unsigned)ceil_to(N, 4);                                     /* :75, :185 */
+    d->eq_src = make_int2((int)ceil_to(d->out_w, 4), (int)d->out_h);                   /* :78-79, :188-189 */
+    if (flag) {                                                                        /* :192-193 */
+        d->src_buf_w = (ceil_to(W, 64) + 16) * (size_t)d->dp;
+        d->src_buf_h = ceil_to(H, 16) + 16;
+        d->src_row0 = 8; d->src_col0 = 8;                                              /* :235 */
+    } else {                                                                           /* :82-83 */
+        d->src_buf_w = (ceil_to(W, 64) + d->kernel_shift.y * 2) * (size_t)d->dp;
+        d->src_buf_h = ceil_to(H, 16) + d->kernel_shift.x * 2;
+        d->src_row0 = d->kernel_shift.x; d->src_col0 = d->kernel_shift.y;              /* :125 */
+    }
+    d->i2c_w = (size_t)kW * kH * d->dp;                                                /* :85-86, :195-196 */
+    d->i2c_h = (size_t)d->eq_src.x * d->eq_src.y;
+    d->dst_buf_w = (unsigned)ceil_to(N, 32);                                           /* :88-89, :198-199 */
+    d->dst_buf_h = ceil_to(d->i2c_h, 128);
+    return 0;
+}
+
+/* Staging of the source tensor (conv2_mk_im2col.h:124-128, :234-238) and the
+ * pack launch (:130-142, :240-251).  The valid-mode buffer is allocated with
+ * the zero-border mode's larger size: the pack kernel always loads a 32x80
+ * pixel tile (im2col.cuh:107-138) and would read past the smaller one. */
+static float4* run_pack(const float* src, unsigned W, unsigned H, const ConvDims& d, unsigned kW, unsigned kH)
+{
+    const size_t rows_alloc = ceil_to(H, 16) + 16 + 32;
+    const size_t row_floats = d.src_buf_w;
+    float4* src_buf = zalloc4(row_floats * rows_alloc + (size_t)96 * d.dp);
+    float4* i2c = zalloc4(d.i2c_w * d.i2c_h);
+    if (!src_buf || !i2c) { free(src_buf); free(i2c); return nullptr; }
+    for (unsigned r = 0; r < H; ++r)
+        memcpy((float*)src_buf + (size_t)(d.src_row0 + r) * row_floats + (size_t)d.src_col0 * d.dp,
+               src + (size_t)r * d.wp * d.dp, (size_t)d.wp * d.dp * sizeof(float));
+    int2 thread_bounds = make_int2(d.eq_src.x / 4, d.eq_src.y);
+    dim3 block(16, 16);
+    dim3 grid((thread_bounds.y + 15) / 16, (thread_bounds.x + 15) / 16);
+    launch(grid, block, [&] {
+        cu_sIm2Col_r8_within(src_buf, i2c, d.kernel_shift, thread_bounds, row_floats / 4, d.i2c_w / 4,
+                             make_int2((int)kW, (int)kH), (int)d.dp / 4);
+    });
+    free(src_buf);
+    return i2c;
+}
+
+extern "C" {
+
+/* Output of the reference's pack kernel for one tensor: [eq_w*out_h][kW*kH*dpitch]. */
+__attribute__((visibility("default")))
+int decx_ref_im2col_pack(const float* src, unsigned W, unsigned H, unsigned depth,
+                         unsigned kW, unsigned kH, int flag, float* i2c_out)
+{
+    ConvDims d;
+    int rc = conv_dims(W, H, depth, kW, kH, 1, flag, &d);
+    if (rc) return rc;
+    float4* i2c = run_pack(src, W, H, d, kW, kH);
+    if (!i2c) return 9;
+    memcpy(i2c_out, i2c, d.i2c_w * d.i2c_h * sizeof(float));
+    free(i2c);
+    return 0;
+}
+
+/* The whole reference driver: staging, pack, equivalent GEMM, flat copy-out
+ * (conv2_mk_im2col.h:57-162, :167-274).  dst receives out_h*eq_w*ceil4(N) floats. */
+__attribute__((visibility("default")))
+int decx_ref_conv2_im2col(const float* src, unsigned W, unsigned H, unsigned depth,
+                          const float* filters, unsigned kW, unsigned kH, unsigned N,
+                          int flag, float* dst)
+{
+    ConvDims d;
+    int rc = conv_dims(W, H, depth, kW, kH, N, flag, &d);
+    if (rc) return rc;
+    float4* i2c = run_pack(src, W, H, d, kW, kH);
+    float4* ker_buf = zalloc4((size_t)d.ker_buf_w * d.ker_buf_h);
+    float4* dst_buf = zalloc4((size_t)d.actual_dst_buf_W * d.dst_buf_h);
+    if (!i2c || !ker_buf || !dst_buf) { free(i2c); free(ker_buf); free(dst_buf); return 9; }
+    /* :116-121, :226-231 -- one 2-D copy per filter */
+    const size_t gap = (size_t)d.dp * d.kwp * kH;
+    for (unsigned i = 0; i < N; ++i)
+        for (unsigned ky = 0; ky < kH; ++ky)
+            memcpy((float*)ker_buf + (size_t)i * d.ker_buf_w + (size_t)ky * d.dp * kW,
+                   filters + i * gap + (size_t)ky * d.dp * d.kwp, (size_t)d.dp * kW * sizeof(float));
+    /* :144-154, :253-264 */
+    ulong2 bounds; bounds.x = d.i2c_w / 4; bounds.y = d.i2c_h / 4;
+    dim3 block(32, 8);
+    dim3 grid((unsigned)(d.dst_buf_h / 128), d.dst_buf_w / 32);
+    launch(grid, block, [&] {
+        cu_conv_eq_mm(i2c, ker_buf, dst_buf, bounds, d.actual_dst_buf_W / 4, d.ker_buf_w / 4, d.ker_buf_w / 128);
+    });
+    /* :156, :266 -- flat copy of the destination tensor's total_bytes */
+    memcpy(dst, dst_buf, (size_t)d.out_h * d.eq_src.x * d.actual_dst_buf_W * sizeof(float));
+    free(i2c); free(ker_buf); free(dst_buf);
+    return 0;
+}
+
+/* K1 / K2 through the launcher of GEMM3_macros.h:65-78 with the padding of
+ * the host-resident driver GEMM.h:80-82 (K to 16, N to 128, M to 128; the
+ * padded device buffers are zero here).  A: M x K (row stride lda), B: K x N,
+ * C: optional M x N addend, D: M x N. */
+__attribute__((visibility("default")))
+int decx_ref_gemm_spec(unsigned M, unsigned N, unsigned K,
+                       const float* A, unsigned lda, const float* B, unsigned ldb,
+                       const float* C, unsigned ldc, float* D, unsigned ldd)
+{
+    const unsigned pitch_A = (unsigned)ceil_to(K, 16), pitch_B = (unsigned)ceil_to(N, 128), hA = (unsigned)ceil_to(M, 128);
+    float4* DA = zalloc4((size_t)pitch_A * hA);
+    float4* DB = zalloc4((size_t)pitch_B * pitch_A);
+    float4* DC = C ? zalloc4((size_t)pitch_B * hA) : nullptr;
+    float4* DD = zalloc4((size_t)pitch_B * hA);
+    if (!DA || !DB || !DD || (C && !DC)) return 9;
+    for (unsigned r = 0; r < M; ++r) memcpy((float*)DA + (size_t)r * pitch_A, A + (size_t)r * lda, K * sizeof(float));
+    for (unsigned r = 0; r < K; ++r) memcpy((float*)DB + (size_t)r * pitch_B, B + (size_t)r * ldb, N * sizeof(float));
+    if (C) for (unsigned r = 0; r < M; ++r) memcpy((float*)DC + (size_t)r * pitch_B, C + (size_t)r * ldc, N * sizeof(float));
+    dim3 grid(hA / (GEMM_BlockDim * 8), pitch_B / (GEMM_BlockDim * 8));
+    dim3 block(GEMM_BlockDim * GEMM_BlockDim);
+    const uint iter = pitch_A / GEMM_BlockDim;
+    if (C) launch(grid, block, [&] { cu_GEMM_fp32_ABC_spec(DA, DB, DC, DD, pitch_A / 4, pitch_B / 4, iter); });
+    else   launch(grid, block, [&] { cu_GEMM_fp32_spec(DA, DB, DD, pitch_A / 4, pitch_B / 4, iter); });
+    for (unsigned r = 0; r < M; ++r) memcpy(D + (size_t)r * ldd, (float*)DD + (size_t)r * pitch_B, N * sizeof(float));
+    free(DA); free(DB); free(DC); free(DD);
+    return 0;
+}
+
+}  /* extern "C" */
