@@ -1,0 +1,286 @@
+/*
+ * C-ABI entry points for GEMM and the im2col convolution: argument checks, scratch from the
+ * arena, operand preparation, kernel launches, host staging.  See include/decxb.h.
+ */
+#include "common.h"
+
+#include <vector>
+
+namespace {
+
+/* Scratch blocks of one call; returned to the arena when the stream has passed the point
+ * where release() was called (host callback), so a block is never handed out while the GPU
+ * may still touch it. */
+struct Scratch {
+    decxb_ctx* ctx;
+    std::vector<void*> ptrs;
+    explicit Scratch(decxb_ctx* c) : ctx(c) {}
+    int get(size_t bytes, void** p)
+    {
+        int rc = decxb_malloc(ctx, bytes, p);
+        if (rc == DECXB_OK) ptrs.push_back(*p);
+        return rc;
+    }
+    struct Pending { decxb_ctx* ctx; std::vector<void*> ptrs; };
+    static void CUDART_CB on_done(void* u)
+    {
+        Pending* pd = static_cast<Pending*>(u);
+        for (void* q : pd->ptrs) decxb_free(pd->ctx, q);
+        delete pd;
+    }
+    void release(cudaStream_t s)
+    {
+        if (ptrs.empty()) return;
+        Pending* pd = new Pending{ctx, std::move(ptrs)};
+        ptrs.clear();
+        if (cudaLaunchHostFunc(s, on_done, pd) != cudaSuccess) {
+            cudaGetLastError();
+            cudaStreamSynchronize(s);
+            on_done(pd);
+        }
+    }
+    void release_now()
+    {
+        for (void* q : ptrs) decxb_free(ctx, q);
+        ptrs.clear();
+    }
+    ~Scratch() { release_now(); }
+};
+
+bool tma_ok(const float* p, int64_t ld) { return ((uintptr_t)p % 16 == 0) && (ld % 4 == 0); }
+
+/* D = A * op(B) (+C).  b_is_nt: B given as Bt[N][K]. */
+int gemm_device(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_t K,
+                const float* A, int64_t lda, const float* B, int64_t ldb, bool b_is_nt,
+                const float* C, int64_t ldc, float* D, int64_t ldd, cudaStream_t s)
+{
+    if (mode != DECXB_GEMM_3XTF32 && mode != DECXB_GEMM_1XTF32) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "gemm mode");
+    if (M <= 0 || N <= 0 || K <= 0) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "gemm dims must be positive");
+    if (!A || !B || !D) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null operand");
+    if (lda < K || ldb < (b_is_nt ? K : N) || ldd < N || (C && ldc < N))
+        return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
+
+    Scratch scratch(ctx);
+    const int64_t Kp = decxb_ceil_to(K, 4);
+    decxb_gemm_args g = {};
+    g.M = M; g.N = N; g.K = K; g.C = C; g.ldc = ldc; g.D = D; g.ldd = ldd; g.tile = tile; g.b_rows = N;
+    int rc;
+    const bool x3 = mode == DECXB_GEMM_3XTF32;
+
+    /* A operand */
+    if (x3 || !tma_ok(A, lda)) {
+        float *hi = nullptr, *lo = nullptr;
+        if ((rc = scratch.get((size_t)M * Kp * sizeof(float), (void**)&hi))) return rc;
+        if (x3 && (rc = scratch.get((size_t)M * Kp * sizeof(float), (void**)&lo))) return rc;
+        if (x3) { if ((rc = decxb_launch_split_rows(ctx, A, M, K, lda, hi, lo, Kp, M, s))) return rc; }
+        else    { DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(hi, Kp * 4, A, lda * 4, K * 4, M, cudaMemcpyDeviceToDevice, s)); }
+        g.a_hi = hi; g.a_lo = lo; g.lda = Kp;
+    } else { g.a_hi = A; g.a_lo = nullptr; g.lda = lda; }
+
+    /* B operand */
+    if (b_is_nt) {
+        if (x3 || !tma_ok(B, ldb)) {
+            float *hi = nullptr, *lo = nullptr;
+            if ((rc = scratch.get((size_t)N * Kp * sizeof(float), (void**)&hi))) return rc;
+            if (x3 && (rc = scratch.get((size_t)N * Kp * sizeof(float), (void**)&lo))) return rc;
+            if (x3) { if ((rc = decxb_launch_split_rows(ctx, B, N, K, ldb, hi, lo, Kp, N, s))) return rc; }
+            else    { DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(hi, Kp * 4, B, ldb * 4, K * 4, N, cudaMemcpyDeviceToDevice, s)); }
+            g.b_hi = hi; g.b_lo = lo; g.ldb = Kp;
+        } else { g.b_hi = B; g.b_lo = nullptr; g.ldb = ldb; }
+    } else {
+        float *hi = nullptr, *lo = nullptr;
+        if ((rc = scratch.get((size_t)N * Kp * sizeof(float), (void**)&hi))) return rc;
+        if (x3 && (rc = scratch.get((size_t)N * Kp * sizeof(float), (void**)&lo))) return rc;
+        if ((rc = decxb_launch_split_transpose(ctx, B, K, N, ldb, hi, lo, Kp, x3 ? 0 : 1, s))) return rc;
+        g.b_hi = hi; g.b_lo = lo; g.ldb = Kp;
+    }
+    rc = decxb_launch_gemm_tn(ctx, g, s);
+    scratch.release(s);
+    return rc;
+}
+
+cudaStream_t pick_stream(decxb_ctx* ctx, void* stream) { return stream ? (cudaStream_t)stream : ctx->stream; }
+
+}  // namespace
+
+extern "C" int decxb_gemm_f32(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_t K,
+                              const float* A, int64_t lda, const float* B, int64_t ldb,
+                              const float* C, int64_t ldc, float* D, int64_t ldd, void* stream)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    return gemm_device(ctx, mode, tile, M, N, K, A, lda, B, ldb, false, C, ldc, D, ldd, pick_stream(ctx, stream));
+}
+
+extern "C" int decxb_gemm_f32_nt(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_t K,
+                                 const float* A, int64_t lda, const float* Bt, int64_t ldbt,
+                                 const float* C, int64_t ldc, float* D, int64_t ldd, void* stream)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    return gemm_device(ctx, mode, tile, M, N, K, A, lda, Bt, ldbt, true, C, ldc, D, ldd, pick_stream(ctx, stream));
+}
+
+extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_t K,
+                                   const float* hA, int64_t lda, const float* hB, int64_t ldb,
+                                   const float* hC, int64_t ldc, float* hD, int64_t ldd)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    if (M <= 0 || N <= 0 || K <= 0) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "gemm dims must be positive");
+    if (!hA || !hB || !hD) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null operand");
+    if (lda < K || ldb < N || ldd < N || (hC && ldc < N))
+        return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
+    Scratch scratch(ctx);
+    cudaStream_t s = ctx->stream;
+    const int64_t Kp = decxb_ceil_to(K, 4), Np = decxb_ceil_to(N, 4);
+    float *dA, *dB, *dC = nullptr, *dD;
+    if ((rc = scratch.get((size_t)M * Kp * 4, (void**)&dA))) return rc;
+    if ((rc = scratch.get((size_t)K * Np * 4, (void**)&dB))) return rc;
+    if ((rc = scratch.get((size_t)M * Np * 4, (void**)&dD))) return rc;
+    if (hC && (rc = scratch.get((size_t)M * Np * 4, (void**)&dC))) return rc;
+    DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dA, Kp * 4, hA, lda * 4, K * 4, M, cudaMemcpyHostToDevice, s));
+    DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dB, Np * 4, hB, ldb * 4, N * 4, K, cudaMemcpyHostToDevice, s));
+    if (hC) DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dC, Np * 4, hC, ldc * 4, N * 4, M, cudaMemcpyHostToDevice, s));
+    rc = gemm_device(ctx, mode, tile, M, N, K, dA, Kp, dB, Np, false, dC, Np, dD, Np, s);
+    if (rc) { cudaStreamSynchronize(s); return rc; }
+    DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(hD, ldd * 4, dD, Np * 4, N * 4, M, cudaMemcpyDeviceToHost, s));
+    DECXB_CUDA_TRY(ctx, cudaStreamSynchronize(s));
+    return decxb_check_dev_status(ctx);
+}
+
+/* ---- convolution ------------------------------------------------------------------------ */
+extern "C" int decxb_conv_geometry(int64_t W, int64_t H, int64_t depth, int64_t kW, int64_t kH, int64_t N,
+                                   int flag, decxb_conv_geom* g)
+{
+    if (!g) return DECXB_ERR_BAD_PARAM;
+    if (W <= 0 || H <= 0 || depth <= 0 || kW <= 0 || kH <= 0 || N <= 0) return DECXB_ERR_BAD_PARAM;
+    if (kW / 2 > 8 || kH / 2 > 8) return DECXB_ERR_BAD_KERNEL;   /* the reference's fixed apron of 8 */
+    if (flag == DECXB_CONV_ZERO_COMPENSATE) { g->out_w = W; g->out_h = H; }
+    else if (flag == DECXB_CONV_NO_COMPENSATE) {
+        g->out_w = W - (kW / 2) * 2; g->out_h = H - (kH / 2) * 2;
+        if (g->out_w <= 0 || g->out_h <= 0) return DECXB_ERR_BAD_KERNEL;
+    } else return DECXB_ERR_BAD_FLAG;
+    g->eq_w = decxb_ceil_to(g->out_w, 4);
+    g->M = g->eq_w * g->out_h;
+    g->Kp = kW * kH * decxb_ceil_to(depth, 4);
+    g->Np = decxb_ceil_to(N, 4);
+    return DECXB_OK;
+}
+
+extern "C" int decxb_im2col_pack_f32(decxb_ctx* ctx, const float* src, int64_t W, int64_t H, int64_t depth,
+                                     int64_t kW, int64_t kH, int flag, float* i2c, int64_t batch,
+                                     int64_t src_stride, int64_t i2c_stride, void* stream)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    if (!src || !i2c) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null tensor");
+    return decxb_launch_pack(ctx, src, W, H, depth, kW, kH, flag, i2c, batch, src_stride, i2c_stride, pick_stream(ctx, stream));
+}
+
+namespace {
+
+int conv_device(decxb_ctx* ctx, int mode, int algo, int flag,
+                const float* src, int64_t W, int64_t H, int64_t depth,
+                const float* filters, int64_t kW, int64_t kH, int64_t N,
+                float* dst, int64_t batch, int64_t src_stride, int64_t dst_stride, cudaStream_t s)
+{
+    if (mode != DECXB_GEMM_3XTF32 && mode != DECXB_GEMM_1XTF32) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "gemm mode");
+    if (algo != DECXB_CONV_EXPLICIT && algo != DECXB_CONV_IMPLICIT) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "conv algo");
+    if (!src || !filters || !dst) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null tensor");
+    decxb_conv_geom g;
+    int rc = decxb_conv_geometry(W, H, depth, kW, kH, N, flag, &g);
+    if (rc) return decxb_fail(ctx, rc, "convolution geometry");
+    if (batch <= 0) return DECXB_OK;
+    const int64_t dp = decxb_ceil_to(depth, 4), wp = decxb_ceil_to(W, 4);
+    if (src_stride == 0) src_stride = H * wp * dp;
+    if (dst_stride == 0) dst_stride = g.M * g.Np;
+    const bool x3 = mode == DECXB_GEMM_3XTF32;
+    if (algo == DECXB_CONV_IMPLICIT) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "implicit convolution is not built yet");
+
+    Scratch scratch(ctx);
+    /* filter matrix [Np][Kp] (hi/lo), rows >= N zero so padding channels come out 0 */
+    float *k_hi = nullptr, *k_lo = nullptr;
+    if ((rc = scratch.get((size_t)g.Np * g.Kp * 4, (void**)&k_hi))) return rc;
+    if (x3 && (rc = scratch.get((size_t)g.Np * g.Kp * 4, (void**)&k_lo))) return rc;
+    if ((rc = decxb_launch_filter_matrix(ctx, filters, kW, kH, depth, N, k_hi, k_lo, g.Np, g.Kp, x3 ? 0 : 1, s))) return rc;
+
+    /* images are processed in groups so that the column matrix of a group stays a few hundred MB */
+    const int64_t i2c_bytes_img = g.M * g.Kp * 4;
+    int64_t group = (512LL << 20) / i2c_bytes_img;
+    if (group < 1) group = 1;
+    if (group > batch) group = batch;
+    /* a group of images forms ONE tall GEMM when the destination images are densely packed */
+    const bool dense_dst = dst_stride == g.M * g.Np;
+    float *i2c = nullptr, *a_hi = nullptr, *a_lo = nullptr;
+    if ((rc = scratch.get((size_t)group * i2c_bytes_img, (void**)&i2c))) return rc;
+    if (x3) {
+        if ((rc = scratch.get((size_t)group * i2c_bytes_img, (void**)&a_hi))) return rc;
+        if ((rc = scratch.get((size_t)group * i2c_bytes_img, (void**)&a_lo))) return rc;
+    }
+    for (int64_t b0 = 0; b0 < batch; b0 += group) {
+        const int64_t nb = batch - b0 < group ? batch - b0 : group;
+        if ((rc = decxb_launch_pack(ctx, src + b0 * src_stride, W, H, depth, kW, kH, flag, i2c, nb, src_stride, g.M * g.Kp, s))) return rc;
+        if (x3 && (rc = decxb_launch_split_rows(ctx, i2c, nb * g.M, g.Kp, g.Kp, a_hi, a_lo, g.Kp, nb * g.M, s))) return rc;
+        const int64_t n_gemm = dense_dst ? 1 : nb;
+        const int64_t rows_per = dense_dst ? nb * g.M : g.M;
+        for (int64_t j = 0; j < n_gemm; ++j) {
+            decxb_gemm_args a = {};
+            a.M = rows_per; a.N = g.Np; a.K = g.Kp;
+            a.a_hi = (x3 ? a_hi : i2c) + j * g.M * g.Kp; a.a_lo = x3 ? a_lo + j * g.M * g.Kp : nullptr; a.lda = g.Kp;
+            a.b_hi = k_hi; a.b_lo = k_lo; a.ldb = g.Kp; a.b_rows = g.Np;
+            a.C = nullptr; a.ldc = 0;
+            a.D = dst + (b0 + j) * dst_stride; a.ldd = g.Np;
+            a.tile = DECXB_TILE_AUTO;
+            if ((rc = decxb_launch_gemm_tn(ctx, a, s))) return rc;
+        }
+    }
+    scratch.release(s);
+    return DECXB_OK;
+}
+
+}  // namespace
+
+extern "C" int decxb_conv2_im2col_f32(decxb_ctx* ctx, int mode, int algo, int flag,
+                                      const float* src, int64_t W, int64_t H, int64_t depth,
+                                      const float* filters, int64_t kW, int64_t kH, int64_t N,
+                                      float* dst, int64_t batch, int64_t src_stride, int64_t dst_stride, void* stream)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    return conv_device(ctx, mode, algo, flag, src, W, H, depth, filters, kW, kH, N, dst, batch, src_stride, dst_stride,
+                       pick_stream(ctx, stream));
+}
+
+extern "C" int decxb_conv2_im2col_f32_host(decxb_ctx* ctx, int mode, int algo, int flag,
+                                           const float* h_src, int64_t W, int64_t H, int64_t depth,
+                                           const float* h_filters, int64_t kW, int64_t kH, int64_t N,
+                                           float* h_dst, int64_t batch, int64_t src_stride, int64_t dst_stride)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    if (!h_src || !h_filters || !h_dst) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null tensor");
+    decxb_conv_geom g;
+    rc = decxb_conv_geometry(W, H, depth, kW, kH, N, flag, &g);
+    if (rc) return decxb_fail(ctx, rc, "convolution geometry");
+    if (batch <= 0) return DECXB_OK;
+    const int64_t dp = decxb_ceil_to(depth, 4), wp = decxb_ceil_to(W, 4), kwp = decxb_ceil_to(kW, 4);
+    const int64_t src_img = H * wp * dp, dst_img = g.M * g.Np;
+    if (src_stride == 0) src_stride = src_img;
+    if (dst_stride == 0) dst_stride = dst_img;
+    Scratch scratch(ctx);
+    cudaStream_t s = ctx->stream;
+    float *d_src, *d_flt, *d_dst;
+    if ((rc = scratch.get((size_t)batch * src_img * 4, (void**)&d_src))) return rc;
+    if ((rc = scratch.get((size_t)N * kH * kwp * dp * 4, (void**)&d_flt))) return rc;
+    if ((rc = scratch.get((size_t)batch * dst_img * 4, (void**)&d_dst))) return rc;
+    /* one copy for the whole filter bank (the reference issues one 2-D copy per filter,
+     * conv2_mk_im2col.h:226-231), one strided copy for all images */
+    DECXB_CUDA_TRY(ctx, cudaMemcpyAsync(d_flt, h_filters, (size_t)N * kH * kwp * dp * 4, cudaMemcpyHostToDevice, s));
+    DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(d_src, src_img * 4, h_src, src_stride * 4, src_img * 4, batch, cudaMemcpyHostToDevice, s));
+    rc = conv_device(ctx, mode, algo, flag, d_src, W, H, depth, d_flt, kW, kH, N, d_dst, batch, src_img, dst_img, s);
+    if (rc) { cudaStreamSynchronize(s); return rc; }
+    DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(h_dst, dst_stride * 4, d_dst, dst_img * 4, dst_img * 4, batch, cudaMemcpyDeviceToHost, s));
+    DECXB_CUDA_TRY(ctx, cudaStreamSynchronize(s));
+    return decxb_check_dev_status(ctx);
+}

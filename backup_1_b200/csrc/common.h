@@ -1,0 +1,103 @@
+/* Shared declarations of the decxb CUDA library (internal; the public ABI is include/decxb.h). */
+#ifndef DECXB_COMMON_H_
+#define DECXB_COMMON_H_
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <atomic>
+#include <map>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+
+#include "decxb.h"
+
+/* Status word the kernels report to (device memory, one per context; copied to the pinned
+ * host twin when the host checks it). */
+struct decxb_dev_status {
+    int code;        /* 0 = fine; else a DECXB_DEVERR_* code              */
+    int where;       /* role/barrier id that gave up                       */
+    int block;       /* blockIdx.x of the reporter                         */
+    int detail;      /* stage / tile index                                 */
+};
+
+enum {
+    DECXB_DEVERR_NONE = 0,
+    DECXB_DEVERR_WAIT_EXPIRED = 1,
+};
+
+struct decxb_arena {
+    std::mutex mtx;
+    std::unordered_map<void*, size_t> live;           /* ptr -> block bytes */
+    std::multimap<size_t, void*> cached;              /* block bytes -> ptr */
+    size_t bytes_in_use = 0, bytes_cached = 0, peak = 0;
+    uint64_t n_driver_allocs = 0, n_reuses = 0;
+};
+
+struct decxb_ctx {
+    int device = -1;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;      /* the context's own compute stream        */
+    cudaStream_t copy_stream[2] = {nullptr, nullptr};
+    decxb_arena arena;
+    decxb_dev_status* h_status = nullptr;   /* pinned host twin                     */
+    decxb_dev_status* d_status = nullptr;   /* device word the kernels write        */
+    long long wait_limit_ns = 2000000000LL;
+    std::atomic<uint64_t> launches{0};
+    std::string last_error;
+};
+
+#define DECXB_CUDA_TRY(ctx, expr)                                                              \
+    do {                                                                                       \
+        cudaError_t _e = (expr);                                                               \
+        if (_e != cudaSuccess) {                                                               \
+            decxb_set_error((ctx), std::string(#expr) + ": " + cudaGetErrorString(_e));       \
+            return DECXB_ERR_CUDA;                                                             \
+        }                                                                                      \
+    } while (0)
+
+int decxb_fail(decxb_ctx* ctx, int status, const std::string& msg);
+void decxb_set_error(decxb_ctx* ctx, const std::string& msg);
+/* Binds the context's device to the calling thread. */
+int decxb_bind(decxb_ctx* ctx);
+/* Reads (and clears) the device status word after a synchronisation. */
+int decxb_check_dev_status(decxb_ctx* ctx);
+
+static inline int64_t decxb_ceil_to(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
+static inline int64_t decxb_ceil_div(int64_t v, int64_t m) { return (v + m - 1) / m; }
+
+/* ---- internal kernels' launchers (each returns a decxb_status) ------------------------ */
+
+/* hi = tf32(a), lo = tf32(a - hi); out pitch `ld_out` (pad columns zeroed).  lo may be NULL. */
+int decxb_launch_split_rows(decxb_ctx* ctx, const float* in, int64_t rows, int64_t cols, int64_t ld_in,
+                            float* hi, float* lo, int64_t ld_out, int64_t rows_out, cudaStream_t s);
+/* Transposing variant: in[K][ld_in] (K rows, N cols) -> hi/lo[N][ld_out]; `raw` keeps hi = a unrounded. */
+int decxb_launch_split_transpose(decxb_ctx* ctx, const float* in, int64_t K, int64_t N, int64_t ld_in,
+                                 float* hi, float* lo, int64_t ld_out, int raw, cudaStream_t s);
+
+/* The tensor-core GEMM on K-contiguous operands.  a_hi/a_lo: [M][lda], b_hi/b_lo: [N][ldb]
+ * (lo pointers NULL for plain TF32).  C optional addend, D output. */
+struct decxb_gemm_args {
+    int64_t M, N, K;
+    const float *a_hi, *a_lo; int64_t lda;
+    const float *b_hi, *b_lo; int64_t ldb;
+    int64_t b_rows;            /* rows of the B operand arrays that exist (>= N is not required: rows beyond are read as 0) */
+    const float* C; int64_t ldc;
+    float* D; int64_t ldd;
+    int tile;
+};
+int decxb_launch_gemm_tn(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s);
+
+int decxb_launch_pack(decxb_ctx* ctx, const float* src, int64_t W, int64_t H, int64_t depth,
+                      int64_t kW, int64_t kH, int flag, float* i2c, int64_t batch,
+                      int64_t src_stride, int64_t i2c_stride, cudaStream_t s);
+
+/* Filter bank (TensorArray layout) -> hi/lo [rows_out][ld_out] matrices, filter n in row n. */
+int decxb_launch_filter_matrix(decxb_ctx* ctx, const float* filters, int64_t kW, int64_t kH, int64_t depth,
+                               int64_t N, float* hi, float* lo, int64_t rows_out, int64_t ld_out, int raw,
+                               cudaStream_t s);
+
+#endif

@@ -1,0 +1,252 @@
+/* Context, error text, device arena, copies: the host-side runtime of the decxb library. */
+#include "common.h"
+
+#include <string.h>
+
+static const char* kVersion = "decxb 0.1 (sm_100a)";
+
+extern "C" const char* decxb_version(void) { return kVersion; }
+
+extern "C" const char* decxb_status_string(int status)
+{
+    switch (status) {
+    case DECXB_OK: return "success";
+    case DECXB_ERR_NOT_INIT: return "CUDA should be initialized first";
+    case DECXB_ERR_DIM_MISMATCH: return "matrix dims don't match each other";
+    case DECXB_ERR_BAD_KERNEL: return "convolution kernel is not supported";
+    case DECXB_ERR_BAD_FLAG: return "invalid flag";
+    case DECXB_ERR_BAD_PARAM: return "invalid parameter";
+    case DECXB_ERR_ALLOC: return "fail to allocate memory on device";
+    case DECXB_ERR_CUDA: return "CUDA call failed";
+    case DECXB_ERR_NO_DEVICE: return "no CUDA device";
+    case DECXB_ERR_ARCH: return "device is not compute capability 10.x (sm_100a code only)";
+    case DECXB_ERR_TIMEOUT: return "a bounded device-side wait expired";
+    case DECXB_ERR_TOO_LARGE: return "request exceeds a fixed limit";
+    default: return "unknown status";
+    }
+}
+
+void decxb_set_error(decxb_ctx* ctx, const std::string& msg)
+{
+    if (ctx) ctx->last_error = msg;
+}
+
+int decxb_fail(decxb_ctx* ctx, int status, const std::string& msg)
+{
+    decxb_set_error(ctx, std::string(decxb_status_string(status)) + ": " + msg);
+    return status;
+}
+
+extern "C" const char* decxb_last_error(decxb_ctx* ctx)
+{
+    return ctx ? ctx->last_error.c_str() : "null context";
+}
+
+int decxb_bind(decxb_ctx* ctx)
+{
+    if (!ctx || ctx->device < 0) return DECXB_ERR_NOT_INIT;
+    DECXB_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return DECXB_OK;
+}
+
+extern "C" int decxb_init(int device, decxb_ctx** out)
+{
+    if (!out) return DECXB_ERR_BAD_PARAM;
+    *out = nullptr;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) { cudaGetLastError(); return DECXB_ERR_NO_DEVICE; }
+    if (device < 0 || device >= n) return DECXB_ERR_BAD_PARAM;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return DECXB_ERR_CUDA;
+    if (prop.major != 10) return DECXB_ERR_ARCH;
+    decxb_ctx* ctx = new decxb_ctx();
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    bool ok = cudaSetDevice(device) == cudaSuccess
+           && cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) == cudaSuccess
+           && cudaStreamCreateWithFlags(&ctx->copy_stream[0], cudaStreamNonBlocking) == cudaSuccess
+           && cudaStreamCreateWithFlags(&ctx->copy_stream[1], cudaStreamNonBlocking) == cudaSuccess
+           && cudaMalloc((void**)&ctx->d_status, sizeof(decxb_dev_status)) == cudaSuccess
+           && cudaMemset(ctx->d_status, 0, sizeof(decxb_dev_status)) == cudaSuccess
+           && cudaHostAlloc((void**)&ctx->h_status, sizeof(decxb_dev_status), cudaHostAllocDefault) == cudaSuccess;
+    if (!ok) { cudaGetLastError(); delete ctx; return DECXB_ERR_CUDA; }
+    memset(ctx->h_status, 0, sizeof(decxb_dev_status));
+    *out = ctx;
+    return DECXB_OK;
+}
+
+extern "C" int decxb_destroy(decxb_ctx* ctx)
+{
+    if (!ctx) return DECXB_OK;
+    if (decxb_bind(ctx) == DECXB_OK) {
+        cudaDeviceSynchronize();
+        decxb_release_cached(ctx);
+        for (auto& kv : ctx->arena.live) cudaFree(kv.first);
+        cudaFree(ctx->d_status);
+        cudaFreeHost(ctx->h_status);
+        cudaStreamDestroy(ctx->stream);
+        cudaStreamDestroy(ctx->copy_stream[0]);
+        cudaStreamDestroy(ctx->copy_stream[1]);
+    }
+    delete ctx;
+    return DECXB_OK;
+}
+
+extern "C" int decxb_device(decxb_ctx* ctx) { return ctx ? ctx->device : -1; }
+extern "C" void* decxb_stream(decxb_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+extern "C" uint64_t decxb_kernel_launch_count(decxb_ctx* ctx) { return ctx ? ctx->launches.load() : 0; }
+
+extern "C" int decxb_set_wait_limit_ms(decxb_ctx* ctx, int ms)
+{
+    if (!ctx || ms <= 0) return DECXB_ERR_BAD_PARAM;
+    ctx->wait_limit_ns = (long long)ms * 1000000LL;
+    return DECXB_OK;
+}
+
+int decxb_check_dev_status(decxb_ctx* ctx)
+{
+    DECXB_CUDA_TRY(ctx, cudaMemcpy(ctx->h_status, ctx->d_status, sizeof(decxb_dev_status), cudaMemcpyDeviceToHost));
+    if (ctx->h_status->code != DECXB_DEVERR_NONE) {
+        char buf[160];
+        snprintf(buf, sizeof buf, "device wait gave up: code %d at role/barrier %d, block %d, detail %d",
+                 ctx->h_status->code, ctx->h_status->where, ctx->h_status->block, ctx->h_status->detail);
+        cudaMemset(ctx->d_status, 0, sizeof(decxb_dev_status));
+        return decxb_fail(ctx, DECXB_ERR_TIMEOUT, buf);
+    }
+    return DECXB_OK;
+}
+
+extern "C" int decxb_synchronize(decxb_ctx* ctx)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    DECXB_CUDA_TRY(ctx, cudaDeviceSynchronize());
+    return decxb_check_dev_status(ctx);
+}
+
+/* ---- arena ----------------------------------------------------------------------------
+ * Blocks are rounded to 256 B (below 1 MiB) or 2 MiB (above) and cached on free.  A cached
+ * block serves a request when it is large enough and not more than twice the request, so a
+ * 4 GiB scratch block is never pinned under a 1 KiB request. */
+static size_t arena_round(size_t bytes)
+{
+    if (bytes == 0) bytes = 1;
+    const size_t g = bytes < (1u << 20) ? 256 : (size_t)2 << 20;
+    return (bytes + g - 1) / g * g;
+}
+
+extern "C" int decxb_malloc(decxb_ctx* ctx, size_t bytes, void** dptr)
+{
+    if (!ctx || !dptr) return DECXB_ERR_BAD_PARAM;
+    *dptr = nullptr;
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    const size_t need = arena_round(bytes);
+    decxb_arena& a = ctx->arena;
+    std::lock_guard<std::mutex> lock(a.mtx);
+    auto it = a.cached.lower_bound(need);
+    void* p = nullptr; size_t got = 0;
+    if (it != a.cached.end() && it->first <= need * 2) {
+        p = it->second; got = it->first;
+        a.cached.erase(it);
+        a.bytes_cached -= got;
+        a.n_reuses++;
+    } else {
+        cudaError_t e = cudaMalloc(&p, need);
+        if (e != cudaSuccess) {
+            /* give cached blocks back and retry once */
+            cudaGetLastError();
+            for (auto& kv : a.cached) cudaFree(kv.second);
+            a.cached.clear(); a.bytes_cached = 0;
+            e = cudaMalloc(&p, need);
+        }
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return decxb_fail(ctx, DECXB_ERR_ALLOC, std::to_string(need) + " bytes");
+        }
+        got = need;
+        a.n_driver_allocs++;
+    }
+    a.live[p] = got;
+    a.bytes_in_use += got;
+    if (a.bytes_in_use > a.peak) a.peak = a.bytes_in_use;
+    *dptr = p;
+    return DECXB_OK;
+}
+
+extern "C" int decxb_free(decxb_ctx* ctx, void* dptr)
+{
+    if (!ctx) return DECXB_ERR_BAD_PARAM;
+    if (!dptr) return DECXB_OK;
+    decxb_arena& a = ctx->arena;
+    std::lock_guard<std::mutex> lock(a.mtx);
+    auto it = a.live.find(dptr);
+    if (it == a.live.end()) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "pointer not owned by this arena");
+    const size_t sz = it->second;
+    a.live.erase(it);
+    a.bytes_in_use -= sz;
+    a.cached.emplace(sz, dptr);
+    a.bytes_cached += sz;
+    return DECXB_OK;
+}
+
+extern "C" int decxb_release_cached(decxb_ctx* ctx)
+{
+    if (!ctx) return DECXB_ERR_BAD_PARAM;
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    decxb_arena& a = ctx->arena;
+    std::lock_guard<std::mutex> lock(a.mtx);
+    cudaDeviceSynchronize();
+    for (auto& kv : a.cached) cudaFree(kv.second);
+    a.cached.clear();
+    a.bytes_cached = 0;
+    return DECXB_OK;
+}
+
+extern "C" int decxb_arena_get_stats(decxb_ctx* ctx, decxb_arena_stats* out)
+{
+    if (!ctx || !out) return DECXB_ERR_BAD_PARAM;
+    decxb_arena& a = ctx->arena;
+    std::lock_guard<std::mutex> lock(a.mtx);
+    out->bytes_in_use = a.bytes_in_use; out->bytes_cached = a.bytes_cached; out->peak_bytes_in_use = a.peak;
+    out->n_driver_allocs = a.n_driver_allocs; out->n_reuses = a.n_reuses;
+    return DECXB_OK;
+}
+
+extern "C" int decxb_host_alloc(size_t bytes, void** hptr)
+{
+    if (!hptr) return DECXB_ERR_BAD_PARAM;
+    if (cudaHostAlloc(hptr, bytes ? bytes : 1, cudaHostAllocDefault) != cudaSuccess) {
+        cudaGetLastError(); *hptr = nullptr; return DECXB_ERR_ALLOC;
+    }
+    return DECXB_OK;
+}
+
+extern "C" int decxb_host_free(void* hptr)
+{
+    if (hptr && cudaFreeHost(hptr) != cudaSuccess) { cudaGetLastError(); return DECXB_ERR_CUDA; }
+    return DECXB_OK;
+}
+
+extern "C" int decxb_memcpy2d(decxb_ctx* ctx, void* dst, size_t dpitch, const void* src, size_t spitch,
+                              size_t width, size_t rows, int kind)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    cudaMemcpyKind k = kind == 1 ? cudaMemcpyHostToDevice : kind == 2 ? cudaMemcpyDeviceToHost
+                     : kind == 3 ? cudaMemcpyDeviceToDevice : cudaMemcpyDefault;
+    if (width == 0 || rows == 0) return DECXB_OK;
+    DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dst, dpitch, src, spitch, width, rows, k, ctx->stream));
+    DECXB_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    return DECXB_OK;
+}
+
+extern "C" int decxb_memset(decxb_ctx* ctx, void* dptr, int value, size_t bytes)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    DECXB_CUDA_TRY(ctx, cudaMemsetAsync(dptr, value, bytes, ctx->stream));
+    DECXB_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    return DECXB_OK;
+}

@@ -1,0 +1,558 @@
+/*
+ * fp32 GEMM on Blackwell tensor cores (sm_100a): D[M][N] = A[M][K] * Bt[N][K]^T (+ C).
+ *
+ * Replaces the reference's CUDA-core FFMA kernels cu_GEMM_fp32_spec / _ABC_spec and their
+ * ragged variants (srcs/GEMM/CUDA/large_squares/GEMM.cuh:31-100, :206-280;
+ * GEMM_nonuniform.cuh:32-693) and the convolution's cu_conv_eq_mm
+ * (srcs/convolution/CUDA/im2col/eq_GEMM.cuh:109-209).
+ *
+ * Shape of the kernel
+ *  - Both operands arrive K-contiguous ("TN"), already split into TF32 hi/lo parts for the
+ *    3xTF32 mode (prep_kernels.cu).  Every k-block of 32 floats is one 128-byte row, loaded
+ *    by TMA (cp.async.bulk.tensor, 128-byte swizzle) into a ring of shared-memory stages.
+ *  - tcgen05.mma kind::tf32, accumulators in tensor memory (TMEM), fp32.  3xTF32 issues
+ *    a_lo*b_hi, a_hi*b_lo, a_hi*b_hi into the same accumulator for every k-step of 8.
+ *  - Warp-specialised, persistent: warp 0 = TMA producer, warp 1 = MMA issuer (and TMEM
+ *    owner), warps 2..5 = epilogue (tcgen05.ld -> registers -> 128-bit global stores).  The
+ *    accumulator is double-buffered in TMEM so the epilogue of tile i overlaps the main loop
+ *    of tile i+1.
+ *  - CTAS = 2 pairs two CTAs (one thread-block cluster) on a 256 x (2*BN) tile with
+ *    cta_group::2: each CTA loads its own 128 rows of A and its own half of B, the leader
+ *    CTA issues the MMAs for both, completion is signalled to both CTAs with one commit.
+ *    Loads are plain (non-multicast) TMA into the issuing CTA's own shared memory.
+ *  - Every wait on an mbarrier is bounded (wall-clock limit from the context); on expiry the
+ *    waiter records where it gave up in the context's status word, all roles drain, tensor
+ *    memory is released and the kernel returns.
+ */
+#include "common.h"
+
+#include <cudaTypedefs.h>
+
+namespace {
+
+constexpr int BM_CTA = 128;        /* rows of A (and of the accumulator) per CTA          */
+constexpr int BK = 32;             /* floats per k-block = one 128-byte swizzle row        */
+constexpr int UMMA_K = 8;          /* k per tcgen05.mma kind::tf32                          */
+constexpr int NUM_THREADS = 192;   /* 6 warps                                                */
+constexpr int SMEM_LIMIT = 232448; /* 227 KiB opt-in maximum per CTA                        */
+
+/* ---------------------------------------------------------------- PTX wrappers ------ */
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r;
+}
+
+__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank)
+{
+    uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank)); return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void fence_barrier_init()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+}
+
+/* Arrive on a barrier given by a shared::cluster address (own CTA or the peer). */
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(bar_cluster_addr) : "memory");
+}
+
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+
+__device__ __forceinline__ unsigned long long globaltimer_ns()
+{
+    unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t;
+}
+
+/* Plain 2-D tiled TMA load into this CTA's shared memory, completion on this CTA's barrier. */
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        :: "r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+/* Same load inside a CTA pair: data lands in the issuing CTA's shared memory, the
+ * transaction bytes are counted on the barrier at `bar_cluster_addr` (the leader CTA's). */
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        :: "r"(dst), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+template <int CTAS>
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols)
+{
+    if (CTAS == 1) asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_dst), "r"(ncols) : "memory");
+    else           asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_dst), "r"(ncols) : "memory");
+}
+
+template <int CTAS>
+__device__ __forceinline__ void tmem_relinquish()
+{
+    if (CTAS == 1) asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    else           asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+template <int CTAS>
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols)
+{
+    if (CTAS == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(taddr), "r"(ncols) : "memory");
+    else           asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" :: "r"(taddr), "r"(ncols) : "memory");
+}
+
+/* D(tmem) (+)= A(smem desc) * B(smem desc), issued by one thread. */
+template <int CTAS>
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
+{
+    if (CTAS == 1) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+            :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+            :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+    }
+}
+
+/* Make the barrier observe completion of every tcgen05.mma this thread issued so far.
+ * In a CTA pair the arrival is delivered to the same barrier offset in both CTAs. */
+template <int CTAS>
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    if (CTAS == 1) {
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
+    } else {
+        const uint16_t mask = 3;
+        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                     :: "r"(bar), "h"(mask) : "memory");
+    }
+}
+
+/* 32 lanes x 32 consecutive fp32 columns of TMEM -> 32 registers per thread. */
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float* v)
+{
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+/* Shared-memory matrix descriptor for a K-contiguous tile whose rows are 128 bytes,
+ * written by TMA with the 128-byte swizzle: 8-row groups lie 1024 bytes apart (stride
+ * byte offset), the leading byte offset is unused for swizzled K-major layouts (set to 1),
+ * descriptor version 1 (Blackwell), layout type 2 (128-byte swizzle). */
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+/* Instruction descriptor: D fp32 (bits 4-5 = 1), A and B TF32 (bits 7-9, 10-12 = 2), both
+ * K-major (bits 15, 16 = 0), N>>3 at bits 17-22, M>>4 at bits 24-28. */
+__host__ __device__ constexpr uint32_t make_idesc(int umma_m, int umma_n)
+{
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(umma_n >> 3) << 17) | ((uint32_t)(umma_m >> 4) << 24);
+}
+
+struct GemmParams {
+    int64_t M, N, K;
+    const float* C; int64_t ldc;
+    float* D; int64_t ldd;
+    int tiles_m, tiles_n, num_kb;
+    long long wait_limit_ns;
+    decxb_dev_status* status;
+};
+
+/* Bounded wait.  Returns false when it gave up (or another role already had). */
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, const GemmParams& p, int where, int detail)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 1023u) == 0) {
+            if (*reinterpret_cast<volatile int*>(&p.status->code) != 0) return false;
+            if ((long long)(globaltimer_ns() - t0) > p.wait_limit_ns) {
+                if (atomicCAS(&p.status->code, 0, DECXB_DEVERR_WAIT_EXPIRED) == 0) {
+                    p.status->where = where; p.status->block = (int)blockIdx.x; p.status->detail = detail;
+                    __threadfence_system();
+                }
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+/* Tile order: groups of 8 tile-rows, column by column inside a group, so that the CTAs
+ * running at the same time share A row-panels and B column-panels in L2. */
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn)
+{
+    constexpr int GROUP = 8;
+    const int per_group = GROUP * tiles_n;
+    const int g = t / per_group;
+    const int first_m = g * GROUP;
+    const int gsz = min(tiles_m - first_m, GROUP);
+    const int r = t - g * per_group;
+    tm = first_m + r % gsz;
+    tn = r / gsz;
+}
+
+/* --------------------------------------------------------------------------------------
+ * CTAS   : 1 or 2 CTAs per tile (cta_group)
+ * BN     : rows of the B operand (columns of D) loaded per CTA; UMMA N = BN * CTAS
+ * NSPLIT : 3 = 3xTF32 (hi and lo parts of both operands), 1 = plain TF32
+ * ------------------------------------------------------------------------------------ */
+template <int CTAS, int BN, int NSPLIT>
+struct Cfg {
+    static constexpr int PARTS = NSPLIT == 3 ? 2 : 1;
+    static constexpr int UMMA_M = BM_CTA * CTAS;
+    static constexpr int UMMA_N = BN * CTAS;
+    static constexpr int A_BYTES = BM_CTA * BK * 4;            /* 16 KiB */
+    static constexpr int B_BYTES = BN * BK * 4;
+    static constexpr int STAGE_BYTES = PARTS * (A_BYTES + B_BYTES);
+    static constexpr int STAGES_RAW = (SMEM_LIMIT - 2048) / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+    static constexpr int TMEM_COLS_RAW = 2 * UMMA_N;
+    static constexpr int TMEM_COLS = TMEM_COLS_RAW <= 32 ? 32 : TMEM_COLS_RAW <= 64 ? 64 : TMEM_COLS_RAW <= 128 ? 128
+                                   : TMEM_COLS_RAW <= 256 ? 256 : 512;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+    static_assert(STAGES >= 2, "need at least two stages");
+    static_assert(UMMA_N % 16 == 0 && UMMA_N >= 16 && UMMA_N <= 256, "UMMA N");
+    static_assert(TMEM_COLS_RAW <= 512, "two accumulators must fit in TMEM");
+};
+
+template <int CTAS, int BN, int NSPLIT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                       const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+                       const GemmParams p)
+{
+    using C = Cfg<CTAS, BN, NSPLIT>;
+    extern __shared__ uint8_t smem_raw[];
+    /* 1024-byte alignment: the 128-byte swizzle pattern is a function of address bits 4-9. */
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = smem_base + C::STAGES * C::STAGE_BYTES;
+    auto full_bar   = [&](int s) { return bars + 8u * s; };
+    auto empty_bar  = [&](int s) { return bars + 8u * (C::STAGES + s); };
+    auto tfull_bar  = [&](int b) { return bars + 8u * (2 * C::STAGES + b); };
+    auto tempty_bar = [&](int b) { return bars + 8u * (2 * C::STAGES + 2 + b); };
+    const uint32_t tmem_slot = bars + 8u * (2 * C::STAGES + 4);
+    auto stage_a = [&](int s, int part) { return smem_base + s * C::STAGE_BYTES + part * C::A_BYTES; };
+    auto stage_b = [&](int s, int part) { return smem_base + s * C::STAGE_BYTES + C::PARTS * C::A_BYTES + part * C::B_BYTES; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t cta_rank = CTAS == 2 ? cluster_ctarank() : 0u;
+    const bool is_leader = cta_rank == 0;
+    const int cluster_id = (int)blockIdx.x / CTAS;
+    const int num_clusters = (int)gridDim.x / CTAS;
+    const int num_tiles = p.tiles_m * p.tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4 * CTAS); }
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc<CTAS>(tmem_slot, C::TMEM_COLS);
+        tmem_relinquish<CTAS>();
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (CTAS == 2) cluster_sync_all();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+    if (warp == 0) {
+        /* ------------------------------------------------------------ TMA producer ---- */
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            bool alive = true;
+            for (int t = cluster_id; t < num_tiles && alive; t += num_clusters) {
+                int tm, tn; tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+                const int row_a = tm * C::UMMA_M + (int)cta_rank * BM_CTA;
+                const int row_b = tn * C::UMMA_N + (int)cta_rank * BN;
+                for (int kb = 0; kb < p.num_kb; ++kb) {
+                    if (!wait_bounded(empty_bar(stage), phase ^ 1u, p, 100 + stage, t)) { alive = false; break; }
+                    const int kx = kb * BK;
+                    if (CTAS == 1) {
+                        const uint32_t fb = full_bar(stage);
+                        mbar_arrive_expect_tx(fb, C::STAGE_BYTES);
+                        tma_load_2d(stage_a(stage, 0), &map_a_hi, fb, kx, row_a);
+                        tma_load_2d(stage_b(stage, 0), &map_b_hi, fb, kx, row_b);
+                        if (NSPLIT == 3) {
+                            tma_load_2d(stage_a(stage, 1), &map_a_lo, fb, kx, row_a);
+                            tma_load_2d(stage_b(stage, 1), &map_b_lo, fb, kx, row_b);
+                        }
+                    } else {
+                        /* Both CTAs' bytes are counted on the leader's barrier. */
+                        if (is_leader) mbar_arrive_expect_tx(full_bar(stage), 2 * C::STAGE_BYTES);
+                        const uint32_t fb = mapa(full_bar(stage), 0);
+                        tma_load_2d_pair(stage_a(stage, 0), &map_a_hi, fb, kx, row_a);
+                        tma_load_2d_pair(stage_b(stage, 0), &map_b_hi, fb, kx, row_b);
+                        if (NSPLIT == 3) {
+                            tma_load_2d_pair(stage_a(stage, 1), &map_a_lo, fb, kx, row_a);
+                            tma_load_2d_pair(stage_b(stage, 1), &map_b_lo, fb, kx, row_b);
+                        }
+                    }
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        /* ------------------------------------------------------------ MMA issuer ------ */
+        if (is_leader && lane == 0) {
+            constexpr uint32_t idesc = make_idesc(C::UMMA_M, C::UMMA_N);
+            int stage = 0; uint32_t phase = 0;
+            int it = 0;
+            bool alive = true;
+            for (int t = cluster_id; t < num_tiles && alive; t += num_clusters, ++it) {
+                const int acc = it & 1;
+                const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+                if (!wait_bounded(tempty_bar(acc), acc_phase ^ 1u, p, 200 + acc, t)) { alive = false; break; }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * C::UMMA_N);
+                for (int kb = 0; kb < p.num_kb; ++kb) {
+                    if (!wait_bounded(full_bar(stage), phase, p, 300 + stage, t)) { alive = false; break; }
+                    tc_fence_after();
+                    const uint64_t da_hi = make_smem_desc(stage_a(stage, 0));
+                    const uint64_t db_hi = make_smem_desc(stage_b(stage, 0));
+                    const uint64_t da_lo = make_smem_desc(stage_a(stage, C::PARTS - 1));
+                    const uint64_t db_lo = make_smem_desc(stage_b(stage, C::PARTS - 1));
+#pragma unroll
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        /* advance 8 floats = 32 bytes inside the 128-byte swizzled row */
+                        const uint64_t koff = (uint64_t)((kk * UMMA_K * 4) >> 4);
+                        const uint32_t first = (kb | kk) != 0 ? 1u : 0u;
+                        if (NSPLIT == 3) {
+                            umma_tf32<CTAS>(tmem_d, da_lo + koff, db_hi + koff, idesc, first);
+                            umma_tf32<CTAS>(tmem_d, da_hi + koff, db_lo + koff, idesc, 1u);
+                            umma_tf32<CTAS>(tmem_d, da_hi + koff, db_hi + koff, idesc, 1u);
+                        } else {
+                            umma_tf32<CTAS>(tmem_d, da_hi + koff, db_hi + koff, idesc, first);
+                        }
+                    }
+                    umma_commit<CTAS>(empty_bar(stage));     /* stage reusable once these MMAs have read it */
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (alive) umma_commit<CTAS>(tfull_bar(acc)); /* accumulator complete */
+            }
+        }
+    } else {
+        /* ------------------------------------------------------------ epilogue -------- */
+        const int q = warp & 3;                   /* TMEM lane quarter this warp may read */
+        const bool d_vec = ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) && (p.ldd % 4 == 0);
+        const bool c_vec = p.C && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && (p.ldc % 4 == 0);
+        int it = 0;
+        bool alive = true;
+        for (int t = cluster_id; t < num_tiles && alive; t += num_clusters, ++it) {
+            int tm, tn; tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+            const int acc = it & 1;
+            const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+            if (!wait_bounded(tfull_bar(acc), acc_phase, p, 400 + acc, t)) { alive = false; break; }
+            tc_fence_after();
+            const int64_t row = (int64_t)tm * C::UMMA_M + (int64_t)cta_rank * BM_CTA + q * 32 + lane;
+            const int64_t col0 = (int64_t)tn * C::UMMA_N;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * C::UMMA_N);
+            float* __restrict__ drow = p.D + row * p.ldd;
+            const float* __restrict__ crow = p.C ? p.C + row * p.ldc : nullptr;
+#pragma unroll 1
+            for (int c = 0; c < C::UMMA_N; c += 32) {
+                if (col0 + c >= p.N) break;           /* warp-uniform */
+                float v[32];
+                tmem_ld_32x32(taddr + (uint32_t)c, v);
+                tmem_ld_wait();
+                if (row < p.M) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        const int64_t col = col0 + c + j;
+                        if (col + 3 < p.N && d_vec && (!crow || c_vec)) {
+                            float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                            if (crow) {
+                                const float4 ci = __ldg(reinterpret_cast<const float4*>(crow + col));
+                                o.x += ci.x; o.y += ci.y; o.z += ci.z; o.w += ci.w;
+                            }
+                            *reinterpret_cast<float4*>(drow + col) = o;
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e)
+                                if (col + e < p.N) drow[col + e] = v[j + e] + (crow ? __ldg(crow + col + e) : 0.0f);
+                        }
+                    }
+                }
+            }
+            /* accumulator drained: hand it back to the MMA issuer (in the leader CTA) */
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (CTAS == 1) mbar_arrive_cluster(tempty_bar(acc));
+                else           mbar_arrive_cluster(mapa(tempty_bar(acc), 0));
+            }
+        }
+    }
+
+    /* ---------------------------------------------------------------- teardown -------- */
+    if (*reinterpret_cast<volatile int*>(&p.status->code) != 0) __nanosleep(20000);  /* let copies in flight land */
+    tc_fence_before();
+    __syncthreads();
+    if (CTAS == 2) cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc<CTAS>(tmem_base, C::TMEM_COLS);
+    }
+}
+
+/* ------------------------------------------------------------------ host side -------- */
+PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn()
+{
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(sym);
+    });
+    return fn;
+}
+
+/* rows x K fp32 array with K contiguous and a row pitch of `ld` floats; box = 32 floats x box_rows. */
+int make_map(decxb_ctx* ctx, CUtensorMap* map, const float* base, int64_t rows, int64_t K, int64_t ld, int box_rows)
+{
+    auto fn = get_encode_fn();
+    if (!fn) return decxb_fail(ctx, DECXB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
+    if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld % 4))
+        return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "TMA operand must be 16-byte aligned with a pitch that is a multiple of 4 floats");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return decxb_fail(ctx, DECXB_ERR_CUDA, "cuTensorMapEncodeTiled failed: " + std::to_string((int)r));
+    return DECXB_OK;
+}
+
+template <int CTAS, int BN, int NSPLIT>
+int launch_cfg(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s)
+{
+    using C = Cfg<CTAS, BN, NSPLIT>;
+    auto kernel = decxb_gemm_tf32_kernel<CTAS, BN, NSPLIT>;
+    static std::once_flag once[16];
+    static cudaError_t attr_err[16];
+    const int dev = ctx->device & 15;
+    std::call_once(once[dev], [&] {
+        attr_err[dev] = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    });
+    if (attr_err[dev] != cudaSuccess)
+        return decxb_fail(ctx, DECXB_ERR_CUDA, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(attr_err[dev]));
+
+    CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
+    int rc;
+    if ((rc = make_map(ctx, &ma_hi, a.a_hi, a.M, a.K, a.lda, BM_CTA))) return rc;
+    if ((rc = make_map(ctx, &mb_hi, a.b_hi, a.b_rows, a.K, a.ldb, BN))) return rc;
+    if (NSPLIT == 3) {
+        if ((rc = make_map(ctx, &ma_lo, a.a_lo, a.M, a.K, a.lda, BM_CTA))) return rc;
+        if ((rc = make_map(ctx, &mb_lo, a.b_lo, a.b_rows, a.K, a.ldb, BN))) return rc;
+    } else { ma_lo = ma_hi; mb_lo = mb_hi; }
+
+    GemmParams p;
+    p.M = a.M; p.N = a.N; p.K = a.K;
+    p.C = a.C; p.ldc = a.ldc; p.D = a.D; p.ldd = a.ldd;
+    p.tiles_m = (int)decxb_ceil_div(a.M, C::UMMA_M);
+    p.tiles_n = (int)decxb_ceil_div(a.N, C::UMMA_N);
+    p.num_kb = (int)decxb_ceil_div(a.K, BK);
+    p.wait_limit_ns = ctx->wait_limit_ns;
+    p.status = ctx->d_status;
+
+    const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
+    int64_t clusters = ctx->sm_count / CTAS;
+    if (clusters > tiles) clusters = tiles;
+    if (clusters < 1) clusters = 1;
+
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(clusters * CTAS), 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CTAS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    DECXB_CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kernel, ma_hi, ma_lo, mb_hi, mb_lo, p));
+    ctx->launches++;
+    return DECXB_OK;
+}
+
+}  // namespace
+
+int decxb_launch_gemm_tn(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s)
+{
+    if (a.M <= 0 || a.N <= 0 || a.K <= 0) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "gemm dims must be positive");
+    if (a.M > 0x7fffffffLL || a.N > 0x7fffffffLL || a.K > 0x7fffffffLL) return decxb_fail(ctx, DECXB_ERR_TOO_LARGE, "gemm dims");
+    const bool x3 = a.a_lo != nullptr;
+    int tile = a.tile;
+    if (tile == DECXB_TILE_AUTO) {
+        if (a.N <= 64) tile = DECXB_TILE_1CTA_128x64;
+        else if (a.N <= 128 || a.M <= 128) tile = DECXB_TILE_1CTA_128x128;
+        else tile = DECXB_TILE_2CTA_256x256;
+    }
+    switch (tile) {
+    case DECXB_TILE_1CTA_128x128: return x3 ? launch_cfg<1, 128, 3>(ctx, a, s) : launch_cfg<1, 128, 1>(ctx, a, s);
+    case DECXB_TILE_2CTA_256x256: return x3 ? launch_cfg<2, 128, 3>(ctx, a, s) : launch_cfg<2, 128, 1>(ctx, a, s);
+    case DECXB_TILE_1CTA_128x256: return x3 ? launch_cfg<1, 256, 3>(ctx, a, s) : launch_cfg<1, 256, 1>(ctx, a, s);
+    case DECXB_TILE_1CTA_128x64:  return x3 ? launch_cfg<1, 64, 3>(ctx, a, s)  : launch_cfg<1, 64, 1>(ctx, a, s);
+    default: return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "unknown gemm tile");
+    }
+}

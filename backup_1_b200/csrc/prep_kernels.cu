@@ -1,0 +1,208 @@
+/*
+ * Memory-bound helper kernels of the decxb library (sm_100a):
+ *   - seeded synthetic data,
+ *   - the TF32 hi/lo operand split (with and without transposition) that feeds the
+ *     3xTF32 tensor-core GEMM,
+ *   - the filter bank -> [N][Kp] matrix gather of the convolution
+ *     (what the reference does with one cudaMemcpy2DAsync per filter,
+ *      srcs/convolution/CUDA/im2col/conv2_mk_im2col.h:226-231).
+ * All of them stream their operands once with 128-bit accesses where alignment allows.
+ */
+#include "common.h"
+
+/* ------------------------------------------------------------------------------------ */
+__device__ __forceinline__ uint32_t fmix32(uint32_t h)
+{
+    h ^= h >> 16; h *= 0x85EBCA6Bu;
+    h ^= h >> 13; h *= 0xC2B2AE35u;
+    h ^= h >> 16;
+    return h;
+}
+
+__device__ __forceinline__ float uniform_pm1(uint32_t seed, uint64_t idx)
+{
+    uint32_t hi = fmix32((uint32_t)(idx >> 32) + seed * 0x85EBCA77u + 0x165667B1u);
+    uint32_t u = fmix32(((uint32_t)idx * 0x9E3779B1u) ^ hi);
+    return __fsub_rn(__fmul_rn((float)(u >> 8), 1.0f / 8388608.0f), 1.0f);
+}
+
+__global__ void __launch_bounds__(256)
+decxb_fill_uniform_kernel(float* __restrict__ dst, uint64_t rows, uint64_t cols, uint64_t pitch,
+                          uint32_t seed, uint64_t first_index)
+{
+    const uint64_t total = rows * pitch;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t r = i / pitch, c = i - r * pitch;
+        dst[i] = c < cols ? uniform_pm1(seed, first_index + r * cols + c) : 0.0f;
+    }
+}
+
+extern "C" int decxb_fill_uniform_f32(decxb_ctx* ctx, float* dptr, uint64_t rows, uint64_t cols, uint64_t pitch,
+                                      uint32_t seed, uint64_t first_index, void* stream)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    if (!dptr || pitch < cols) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "fill_uniform");
+    if (rows == 0 || pitch == 0) return DECXB_OK;
+    cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
+    const uint64_t total = rows * pitch;
+    int blocks = (int)((total + 255) / 256 < (uint64_t)ctx->sm_count * 16 ? (total + 255) / 256 : (uint64_t)ctx->sm_count * 16);
+    decxb_fill_uniform_kernel<<<blocks, 256, 0, s>>>(dptr, rows, cols, pitch, seed, first_index);
+    ctx->launches++;
+    DECXB_CUDA_TRY(ctx, cudaGetLastError());
+    return DECXB_OK;
+}
+
+/* ------------------------------------------------------------------------------------
+ * TF32 split.  hi = round-to-nearest TF32 of a (low 13 mantissa bits zero), lo = TF32 of
+ * the exact remainder a - hi.  Both are exactly representable in TF32, so whatever the
+ * tensor core does with the low bits of its inputs cannot matter.
+ * ---------------------------------------------------------------------------------- */
+__device__ __forceinline__ float tf32_rna(float x)
+{
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
+__device__ __forceinline__ void split1(float a, float& hi, float& lo)
+{
+    hi = tf32_rna(a);
+    lo = tf32_rna(__fsub_rn(a, hi));
+}
+
+/* in[rows][ld_in] -> hi/lo[rows_out][ld_out]; columns >= cols and rows >= rows are written
+ * as zero.  One thread per 4 output columns. */
+__global__ void __launch_bounds__(256)
+decxb_split_rows_kernel(const float* __restrict__ in, int64_t rows, int64_t cols, int64_t ld_in,
+                        float* __restrict__ hi, float* __restrict__ lo, int64_t ld_out, int64_t rows_out,
+                        int in_vec_ok)
+{
+    const int64_t q_per_row = ld_out >> 2;
+    const int64_t total = rows_out * q_per_row;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / q_per_row, c = (i - r * q_per_row) << 2;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (r < rows) {
+            const float* p = in + r * ld_in + c;
+            if (in_vec_ok && c + 3 < cols) {
+                const float4 t = __ldg(reinterpret_cast<const float4*>(p));
+                v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) if (c + j < cols) v[j] = __ldg(p + j);
+            }
+        }
+        float4 h, l;
+        split1(v[0], h.x, l.x); split1(v[1], h.y, l.y); split1(v[2], h.z, l.z); split1(v[3], h.w, l.w);
+        *reinterpret_cast<float4*>(hi + r * ld_out + c) = h;
+        if (lo) *reinterpret_cast<float4*>(lo + r * ld_out + c) = l;
+    }
+}
+
+int decxb_launch_split_rows(decxb_ctx* ctx, const float* in, int64_t rows, int64_t cols, int64_t ld_in,
+                            float* hi, float* lo, int64_t ld_out, int64_t rows_out, cudaStream_t s)
+{
+    if (ld_out % 4 || ld_out < cols || rows_out < rows) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "split_rows pitch");
+    const int64_t total = rows_out * (ld_out / 4);
+    if (total == 0) return DECXB_OK;
+    const int vec_ok = ((uintptr_t)in % 16 == 0) && (ld_in % 4 == 0);
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > (int64_t)ctx->sm_count * 32) blocks = (int64_t)ctx->sm_count * 32;
+    decxb_split_rows_kernel<<<(int)blocks, 256, 0, s>>>(in, rows, cols, ld_in, hi, lo, ld_out, rows_out, vec_ok);
+    ctx->launches++;
+    DECXB_CUDA_TRY(ctx, cudaGetLastError());
+    return DECXB_OK;
+}
+
+/* in[K][ld_in] (K rows, N columns) -> hi/lo[N][ld_out] with K contiguous.  64x64 tiles
+ * through shared memory; `raw` stores hi = a unrounded (plain-TF32 mode) and skips lo. */
+__global__ void __launch_bounds__(256)
+decxb_split_transpose_kernel(const float* __restrict__ in, int64_t K, int64_t N, int64_t ld_in,
+                             float* __restrict__ hi, float* __restrict__ lo, int64_t ld_out, int raw,
+                             int64_t tiles_n)
+{
+    __shared__ float tile[64][65];
+    const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;   /* 64 x 4 */
+    const int64_t tiles_k = (ld_out + 63) / 64;
+    const int64_t n_tiles = tiles_k * tiles_n;
+    for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+        const int64_t k0 = (t / tiles_n) * 64, n0 = (t % tiles_n) * 64;
+#pragma unroll 4
+        for (int j = ty; j < 64; j += 4) {
+            const int64_t k = k0 + j, n = n0 + tx;
+            tile[j][tx] = (k < K && n < N) ? __ldg(in + k * ld_in + n) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int j = ty; j < 64; j += 4) {
+            const int64_t n = n0 + j, k = k0 + tx;
+            if (n < N && k < ld_out) {
+                const float a = tile[tx][j];
+                if (raw) {
+                    hi[n * ld_out + k] = a;
+                } else {
+                    float h, l; split1(a, h, l);
+                    hi[n * ld_out + k] = h;
+                    lo[n * ld_out + k] = l;
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+int decxb_launch_split_transpose(decxb_ctx* ctx, const float* in, int64_t K, int64_t N, int64_t ld_in,
+                                 float* hi, float* lo, int64_t ld_out, int raw, cudaStream_t s)
+{
+    if (ld_out % 4 || ld_out < K) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "split_transpose pitch");
+    const int64_t tiles_n = (N + 63) / 64, tiles_k = (ld_out + 63) / 64;
+    int64_t blocks = tiles_n * tiles_k;
+    if (blocks == 0) return DECXB_OK;
+    if (blocks > (int64_t)ctx->sm_count * 16) blocks = (int64_t)ctx->sm_count * 16;
+    decxb_split_transpose_kernel<<<(int)blocks, 256, 0, s>>>(in, K, N, ld_in, hi, lo, ld_out, raw, tiles_n);
+    ctx->launches++;
+    DECXB_CUDA_TRY(ctx, cudaGetLastError());
+    return DECXB_OK;
+}
+
+/* Filter bank -> matrix.  Row n, column (ky*kW + kx)*dp + c  <-  filters[n][ky][kx][c]
+ * (TensorArray layout [N][kH][ceil4(kW)][dp]).  Rows n >= N and columns >= Kp are zero. */
+__global__ void __launch_bounds__(256)
+decxb_filter_matrix_kernel(const float* __restrict__ filters, int kW, int kH, int dp, int64_t N,
+                           float* __restrict__ hi, float* __restrict__ lo, int64_t rows_out, int64_t ld_out, int raw)
+{
+    const int64_t Kp = (int64_t)kW * kH * dp;
+    const int64_t kwp = (kW + 3) / 4 * 4;
+    const int64_t gap = (int64_t)dp * kwp * kH;
+    const int64_t total = rows_out * ld_out;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t n = i / ld_out, k = i - n * ld_out;
+        float a = 0.0f;
+        if (n < N && k < Kp) {
+            const int64_t tap = k / dp, c = k - tap * dp;
+            const int64_t ky = tap / kW, kx = tap - ky * kW;
+            a = __ldg(filters + n * gap + (ky * kwp + kx) * dp + c);
+        }
+        if (raw) { hi[i] = a; }
+        else { float h, l; split1(a, h, l); hi[i] = h; lo[i] = l; }
+    }
+}
+
+int decxb_launch_filter_matrix(decxb_ctx* ctx, const float* filters, int64_t kW, int64_t kH, int64_t depth,
+                               int64_t N, float* hi, float* lo, int64_t rows_out, int64_t ld_out, int raw,
+                               cudaStream_t s)
+{
+    const int64_t dp = decxb_ceil_to(depth, 4);
+    const int64_t total = rows_out * ld_out;
+    if (total == 0) return DECXB_OK;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > (int64_t)ctx->sm_count * 16) blocks = (int64_t)ctx->sm_count * 16;
+    decxb_filter_matrix_kernel<<<(int)blocks, 256, 0, s>>>(filters, (int)kW, (int)kH, (int)dp, N, hi, lo, rows_out, ld_out, raw);
+    ctx->launches++;
+    DECXB_CUDA_TRY(ctx, cudaGetLastError());
+    return DECXB_OK;
+}

@@ -1,0 +1,187 @@
+"""ctypes binding of ``libdecxb.so`` (see ``include/decxb.h`` for the contract)."""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+GEMM_3XTF32, GEMM_1XTF32 = 0, 1
+TILE_AUTO, TILE_1CTA_128x128, TILE_2CTA_256x256, TILE_1CTA_128x256, TILE_1CTA_128x64 = 0, 1, 2, 3, 4
+CONV_NO_COMPENSATE, CONV_ZERO_COMPENSATE = 0, 1
+CONV_EXPLICIT, CONV_IMPLICIT = 0, 1
+
+_PKG = Path(__file__).resolve().parent
+
+
+class DecxbError(RuntimeError):
+    def __init__(self, status: int, text: str):
+        super().__init__(f"decxb status {status}: {text}")
+        self.status = status
+
+
+def library_path() -> Path:
+    return _PKG / "libdecxb.so"
+
+
+class ConvGeom(C.Structure):
+    _fields_ = [(n, C.c_int64) for n in ("out_w", "out_h", "eq_w", "M", "Kp", "Np")]
+
+
+class ArenaStats(C.Structure):
+    _fields_ = [("bytes_in_use", C.c_size_t), ("bytes_cached", C.c_size_t), ("peak_bytes_in_use", C.c_size_t),
+                ("n_driver_allocs", C.c_uint64), ("n_reuses", C.c_uint64)]
+
+
+_lib = None
+
+# name -> (restype, argtypes); every symbol include/decxb.h declares
+_i, _i64, _u64, _u32, _vp, _sz = C.c_int, C.c_int64, C.c_uint64, C.c_uint32, C.c_void_p, C.c_size_t
+SIGNATURES = {
+    "decxb_init": (_i, [_i, C.POINTER(_vp)]),
+    "decxb_destroy": (_i, [_vp]),
+    "decxb_status_string": (C.c_char_p, [_i]),
+    "decxb_last_error": (C.c_char_p, [_vp]),
+    "decxb_device": (_i, [_vp]),
+    "decxb_stream": (_vp, [_vp]),
+    "decxb_synchronize": (_i, [_vp]),
+    "decxb_set_wait_limit_ms": (_i, [_vp, _i]),
+    "decxb_malloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
+    "decxb_free": (_i, [_vp, _vp]),
+    "decxb_release_cached": (_i, [_vp]),
+    "decxb_arena_get_stats": (_i, [_vp, C.POINTER(ArenaStats)]),
+    "decxb_host_alloc": (_i, [_sz, C.POINTER(_vp)]),
+    "decxb_host_free": (_i, [_vp]),
+    "decxb_memcpy2d": (_i, [_vp, _vp, _sz, _vp, _sz, _sz, _sz, _i]),
+    "decxb_memset": (_i, [_vp, _vp, _i, _sz]),
+    "decxb_fill_uniform_f32": (_i, [_vp, _vp, _u64, _u64, _u64, _u32, _u64, _vp]),
+    "decxb_gemm_f32": (_i, [_vp, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
+    "decxb_gemm_f32_nt": (_i, [_vp, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
+    "decxb_gemm_f32_host": (_i, [_vp, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64]),
+    "decxb_conv_geometry": (_i, [_i64, _i64, _i64, _i64, _i64, _i64, _i, C.POINTER(ConvGeom)]),
+    "decxb_im2col_pack_f32": (_i, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _i, _vp, _i64, _i64, _i64, _vp]),
+    "decxb_conv2_im2col_f32": (_i, [_vp, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp]),
+    "decxb_conv2_im2col_f32_host": (_i, [_vp, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64]),
+    "decxb_kernel_launch_count": (_u64, [_vp]),
+    "decxb_version": (C.c_char_p, []),
+}
+
+
+def load_library() -> C.CDLL:
+    """Loads libdecxb.so and sets the prototypes.  Raises if the library is not built."""
+    global _lib
+    if _lib is None:
+        p = library_path()
+        if not p.exists():
+            raise FileNotFoundError(f"{p} is not built: run `python -c 'import __graft_entry__ as g; g.build()'` "
+                                    "or `make -C backup_1_b200/csrc`")
+        L = C.CDLL(str(p))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = L
+    return _lib
+
+
+def conv_geometry(W, H, depth, kW, kH, N, flag) -> ConvGeom:
+    g = ConvGeom()
+    rc = load_library().decxb_conv_geometry(W, H, depth, kW, kH, N, flag, C.byref(g))
+    if rc:
+        raise DecxbError(rc, load_library().decxb_status_string(rc).decode())
+    return g
+
+
+def _ptr(x):
+    """Raw address of a torch tensor / numpy array / int / None."""
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    if hasattr(x, "data_ptr"):
+        return x.data_ptr()
+    if hasattr(x, "ctypes"):
+        return x.ctypes.data
+    raise TypeError(type(x))
+
+
+class Context:
+    """One decxb context (device, stream, arena).  Pointer arguments are torch tensors, numpy
+    arrays or raw integer addresses; leading dimensions are in elements."""
+
+    def __init__(self, device: int = 0):
+        self.L = load_library()
+        h = _vp()
+        rc = self.L.decxb_init(device, C.byref(h))
+        if rc:
+            raise DecxbError(rc, self.L.decxb_status_string(rc).decode())
+        self.h = h
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.L.decxb_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _chk(self, rc):
+        if rc:
+            raise DecxbError(rc, self.L.decxb_last_error(self.h).decode() or self.L.decxb_status_string(rc).decode())
+
+    # -- runtime ------------------------------------------------------------------------
+    def synchronize(self):
+        self._chk(self.L.decxb_synchronize(self.h))
+
+    def set_wait_limit_ms(self, ms: int):
+        self._chk(self.L.decxb_set_wait_limit_ms(self.h, ms))
+
+    def launches(self) -> int:
+        return int(self.L.decxb_kernel_launch_count(self.h))
+
+    def malloc(self, nbytes: int) -> int:
+        p = _vp()
+        self._chk(self.L.decxb_malloc(self.h, nbytes, C.byref(p)))
+        return p.value
+
+    def free(self, ptr: int):
+        self._chk(self.L.decxb_free(self.h, ptr))
+
+    def release_cached(self):
+        self._chk(self.L.decxb_release_cached(self.h))
+
+    def arena_stats(self) -> ArenaStats:
+        s = ArenaStats()
+        self._chk(self.L.decxb_arena_get_stats(self.h, C.byref(s)))
+        return s
+
+    def fill_uniform(self, dst, rows, cols, pitch, seed, first_index=0, stream=None):
+        self._chk(self.L.decxb_fill_uniform_f32(self.h, _ptr(dst), rows, cols, pitch, seed, first_index, stream))
+
+    # -- GEMM ---------------------------------------------------------------------------
+    def gemm(self, M, N, K, A, lda, B, ldb, D, ldd, Cin=None, ldc=0, mode=GEMM_3XTF32, tile=TILE_AUTO, stream=None):
+        self._chk(self.L.decxb_gemm_f32(self.h, mode, tile, M, N, K, _ptr(A), lda, _ptr(B), ldb,
+                                        _ptr(Cin), ldc, _ptr(D), ldd, stream))
+
+    def gemm_nt(self, M, N, K, A, lda, Bt, ldbt, D, ldd, Cin=None, ldc=0, mode=GEMM_3XTF32, tile=TILE_AUTO, stream=None):
+        self._chk(self.L.decxb_gemm_f32_nt(self.h, mode, tile, M, N, K, _ptr(A), lda, _ptr(Bt), ldbt,
+                                           _ptr(Cin), ldc, _ptr(D), ldd, stream))
+
+    def gemm_host(self, M, N, K, A, lda, B, ldb, D, ldd, Cin=None, ldc=0, mode=GEMM_3XTF32, tile=TILE_AUTO):
+        self._chk(self.L.decxb_gemm_f32_host(self.h, mode, tile, M, N, K, _ptr(A), lda, _ptr(B), ldb,
+                                             _ptr(Cin), ldc, _ptr(D), ldd))
+
+    # -- convolution ----------------------------------------------------------------------
+    def im2col_pack(self, src, W, H, depth, kW, kH, flag, i2c, batch=1, src_stride=0, i2c_stride=0, stream=None):
+        self._chk(self.L.decxb_im2col_pack_f32(self.h, _ptr(src), W, H, depth, kW, kH, flag, _ptr(i2c),
+                                               batch, src_stride, i2c_stride, stream))
+
+    def conv2_im2col(self, src, W, H, depth, filters, kW, kH, N, dst, flag=CONV_ZERO_COMPENSATE, batch=1,
+                     src_stride=0, dst_stride=0, mode=GEMM_3XTF32, algo=CONV_EXPLICIT, stream=None):
+        self._chk(self.L.decxb_conv2_im2col_f32(self.h, mode, algo, flag, _ptr(src), W, H, depth, _ptr(filters),
+                                                kW, kH, N, _ptr(dst), batch, src_stride, dst_stride, stream))
+
+    def conv2_im2col_host(self, src, W, H, depth, filters, kW, kH, N, dst, flag=CONV_ZERO_COMPENSATE, batch=1,
+                          src_stride=0, dst_stride=0, mode=GEMM_3XTF32, algo=CONV_EXPLICIT):
+        self._chk(self.L.decxb_conv2_im2col_f32_host(self.h, mode, algo, flag, _ptr(src), W, H, depth, _ptr(filters),
+                                                     kW, kH, N, _ptr(dst), batch, src_stride, dst_stride))

@@ -1,0 +1,215 @@
+/*
+ * decxb.h -- C ABI of the B200 (sm_100a) implementation of DECX's dense-contraction
+ * hot path: the fp32 GEMM and the im2col convolution.
+ *
+ * Plain pointers and sizes only; every function returns a decxb_status.  This is the
+ * boundary a DECX build binds instead of launching its own kernels and using its own
+ * device pool on this path.  Each entry names the reference interface it replaces
+ * (paths relative to the reference project root).
+ *
+ * Conventions
+ *  - Matrices are row-major fp32 with a leading dimension in ELEMENTS (DECX "pitch",
+ *    srcs/classes/Matrix.h:253-267).  DECX names sizes (width, height); here
+ *    M = height of A, K = width of A = height of B, N = width of B.
+ *  - Tensors are DECX's padded HWC layout (srcs/classes/Tensor.h:162-184, :389-394):
+ *    dpitch = ceil4(depth), wpitch = ceil4(width), element (row, col, ch) at
+ *    ptr[(row*wpitch + col)*dpitch + ch]; filter banks are TensorArrays
+ *    (srcs/classes/TensorArray.h:174-198): filters lie dpitch*wpitch*height floats apart.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the context's own stream).
+ *    Device-resident entry points are asynchronous on that stream; host-resident
+ *    entry points block until the result is in host memory, as the reference does
+ *    (srcs/GEMM/CUDA/large_squares/GEMM.h:122, conv2_mk_im2col.h:268).
+ *  - There is no CPU fallback: without a usable sm_100 device every compute entry
+ *    fails with DECXB_ERR_NO_DEVICE / DECXB_ERR_ARCH.
+ */
+#ifndef DECXB_H_
+#define DECXB_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DECXB_API __attribute__((visibility("default")))
+
+typedef enum decxb_status {
+    DECXB_OK               = 0,
+    DECXB_ERR_NOT_INIT     = 1,   /* maps to DECX_FAIL_not_init        (srcs/handles/decx_handles.h:10) */
+    DECXB_ERR_DIM_MISMATCH = 3,   /* maps to DECX_FAIL_DimsNotMatching (:14)                            */
+    DECXB_ERR_BAD_KERNEL   = 5,   /* maps to DECX_FAIL_ConvBadKernel   (:17)                            */
+    DECXB_ERR_BAD_FLAG     = 11,  /* maps to DECX_FAIL_ErrorFlag       (:27)                            */
+    DECXB_ERR_BAD_PARAM    = 13,  /* maps to DECX_FAIL_ErrorParams     (:31)                            */
+    DECXB_ERR_ALLOC        = 16,  /* maps to DECX_FAIL_ALLOCATION      (:37)                            */
+    DECXB_ERR_CUDA         = 100, /* a CUDA runtime/driver call failed; see decxb_last_error            */
+    DECXB_ERR_NO_DEVICE    = 101,
+    DECXB_ERR_ARCH         = 102, /* device is not compute capability 10.x                              */
+    DECXB_ERR_TIMEOUT      = 103, /* a bounded device-side wait expired; the context stays usable       */
+    DECXB_ERR_TOO_LARGE    = 104  /* request exceeds a documented fixed limit                           */
+} decxb_status;
+
+/* Precision of the tensor-core GEMM.  3xTF32 (default) splits every fp32 operand into a
+ * TF32 "hi" part and a TF32 "lo" remainder and accumulates lo*hi + hi*lo + hi*hi in fp32,
+ * which keeps max|C-Cref| / (K max|a| max|b|) below 1e-6 against the reference's fp32 FMA
+ * chain (srcs/GEMM/CUDA/large_squares/GEMM.cuh:53-94).  Plain TF32 is opt-in. */
+typedef enum decxb_gemm_mode {
+    DECXB_GEMM_3XTF32 = 0,
+    DECXB_GEMM_1XTF32 = 1
+} decxb_gemm_mode;
+
+/* Tile configuration of the GEMM kernel (0 = choose from the shape). */
+typedef enum decxb_gemm_tile {
+    DECXB_TILE_AUTO        = 0,
+    DECXB_TILE_1CTA_128x128 = 1,
+    DECXB_TILE_2CTA_256x256 = 2,  /* CTA pair, tcgen05 cta_group::2 */
+    DECXB_TILE_1CTA_128x256 = 3,
+    DECXB_TILE_1CTA_128x64  = 4
+} decxb_gemm_tile;
+
+/* Border handling of the convolution: values of decx::conv_property
+ * (srcs/convolution/CUDA/conv_flags.h:16-20). */
+typedef enum decxb_conv_flag {
+    DECXB_CONV_NO_COMPENSATE   = 0,   /* "valid": output (W-2*(kW/2)) x (H-2*(kH/2)) */
+    DECXB_CONV_ZERO_COMPENSATE = 1    /* zero border: output W x H                      */
+} decxb_conv_flag;
+
+/* Convolution algorithm. */
+typedef enum decxb_conv_algo {
+    DECXB_CONV_EXPLICIT = 0,  /* pack kernel writes the column matrix, then the GEMM (the reference's two steps) */
+    DECXB_CONV_IMPLICIT = 1   /* column tiles are built in shared memory; the column matrix is never written    */
+} decxb_conv_algo;
+
+typedef struct decxb_ctx decxb_ctx;
+
+/* ---- context ---------------------------------------------------------------------
+ * Replaces de::InitCuda / decx::cuP (srcs/core/configs/config.h:50-78).  One context per
+ * device; it owns a stream, the device arena and the status word device-side waits report to. */
+DECXB_API int decxb_init(int device, decxb_ctx** out);
+DECXB_API int decxb_destroy(decxb_ctx* ctx);
+DECXB_API const char* decxb_status_string(int status);
+/* Text of the last failure on this context (never NULL; valid until the next call). */
+DECXB_API const char* decxb_last_error(decxb_ctx* ctx);
+DECXB_API int decxb_device(decxb_ctx* ctx);
+DECXB_API void* decxb_stream(decxb_ctx* ctx);
+DECXB_API int decxb_synchronize(decxb_ctx* ctx);
+/* Device-side waits give up after this many milliseconds (default 2000). */
+DECXB_API int decxb_set_wait_limit_ms(decxb_ctx* ctx, int ms);
+
+/* ---- device arena -----------------------------------------------------------------
+ * Replaces decx::alloc::_alloc_D / _dealloc_D and MemPool_D
+ * (srcs/core/allocators/allocator.h:83-97, srcs/core/memory_management/MemoryPool_D.h:18-194).
+ * 256-byte aligned, size_t-clean (the reference's `1 << n` int shift breaks at 2 GiB,
+ * MemoryPool_D.h:129), thread-safe; freed blocks are cached for reuse. */
+DECXB_API int decxb_malloc(decxb_ctx* ctx, size_t bytes, void** dptr);
+DECXB_API int decxb_free(decxb_ctx* ctx, void* dptr);
+/* Return every cached block to the driver: de::release_all_tmp
+ * (srcs/core/memory_management/Memory_pool.h:28-38). */
+DECXB_API int decxb_release_cached(decxb_ctx* ctx);
+typedef struct decxb_arena_stats {
+    size_t bytes_in_use, bytes_cached, peak_bytes_in_use;
+    uint64_t n_driver_allocs, n_reuses;
+} decxb_arena_stats;
+DECXB_API int decxb_arena_get_stats(decxb_ctx* ctx, decxb_arena_stats* out);
+
+/* Pinned host memory for DATA_STORE_TYPE::Page_Locked containers
+ * (srcs/core/allocators/aligned_allocators.h:76, srcs/classes/store_types.h:24-28). */
+DECXB_API int decxb_host_alloc(size_t bytes, void** hptr);
+DECXB_API int decxb_host_free(void* hptr);
+
+/* Plain copies used by the GPU containers' Load_from_host / Load_to_host
+ * (srcs/classes/GPU_Matrix.h:334-354, GPU_Tensor.h:355-371). kind: 1 H2D, 2 D2H, 3 D2D. */
+DECXB_API int decxb_memcpy2d(decxb_ctx* ctx, void* dst, size_t dpitch_bytes, const void* src, size_t spitch_bytes,
+                             size_t width_bytes, size_t rows, int kind);
+DECXB_API int decxb_memset(decxb_ctx* ctx, void* dptr, int value, size_t bytes);
+
+/* ---- seeded synthetic data ---------------------------------------------------------
+ * Fills rows x cols (row pitch `pitch` elements, pitch tail zeroed) with uniform [-1,1)
+ * values; element (r, c) is a pure function of (seed, first_index + r*cols + c).  No
+ * counterpart in the reference (its tests fill from index formulas). */
+DECXB_API int decxb_fill_uniform_f32(decxb_ctx* ctx, float* dptr, uint64_t rows, uint64_t cols, uint64_t pitch,
+                                     uint32_t seed, uint64_t first_index, void* stream);
+
+/* ---- GEMM -------------------------------------------------------------------------
+ * D[M][N] = A[M][K] * B[K][N] (+ C[M][N] when C != NULL), all device-resident.
+ * Replaces the kernel selection and launches of de::cuda::GEMM on GPU_Matrix
+ * (srcs/GEMM/CUDA/large_squares/GEMM.h:398-454 and, with C, :522-582), i.e. kernels
+ * cu_GEMM_fp32_spec / _ABC_spec and the six ragged variants (GEMM.cuh:31-100,206-280;
+ * GEMM_nonuniform.cuh:32-693).  Any M, N, K >= 1; no alignment demands beyond fp32. */
+DECXB_API int decxb_gemm_f32(decxb_ctx* ctx, int mode, int tile,
+                             int64_t M, int64_t N, int64_t K,
+                             const float* A, int64_t lda,
+                             const float* B, int64_t ldb,
+                             const float* C, int64_t ldc,
+                             float* D, int64_t ldd, void* stream);
+
+/* Same product with B given K-contiguous: Bt[N][K] ("TN"), the orientation of the
+ * convolution's filter matrix (cu_conv_eq_mm, srcs/convolution/CUDA/im2col/eq_GEMM.cuh:109-209). */
+DECXB_API int decxb_gemm_f32_nt(decxb_ctx* ctx, int mode, int tile,
+                                int64_t M, int64_t N, int64_t K,
+                                const float* A, int64_t lda,
+                                const float* Bt, int64_t ldbt,
+                                const float* C, int64_t ldc,
+                                float* D, int64_t ldd, void* stream);
+
+/* Host-resident operands: stages A, B (and C) to the device, multiplies, copies D back and
+ * blocks until done.  Replaces de::cuda::GEMM on Matrix (GEMM.h:56-131, with C :136-221). */
+DECXB_API int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile,
+                                  int64_t M, int64_t N, int64_t K,
+                                  const float* hA, int64_t lda,
+                                  const float* hB, int64_t ldb,
+                                  const float* hC, int64_t ldc,
+                                  float* hD, int64_t ldd);
+
+/* ---- im2col convolution --------------------------------------------------------------
+ * Geometry shared by the entry points below (conv2_mk_im2col.h:60-93, :170-199). */
+typedef struct decxb_conv_geom {
+    int64_t out_w, out_h;  /* logical output size                                   */
+    int64_t eq_w;          /* ceil4(out_w) = wpitch of the destination tensor       */
+    int64_t M;             /* eq_w * out_h: rows of the column matrix                */
+    int64_t Kp;            /* kW*kH*dpitch: columns of the column matrix             */
+    int64_t Np;            /* ceil4(N): dpitch of the destination tensor             */
+} decxb_conv_geom;
+DECXB_API int decxb_conv_geometry(int64_t W, int64_t H, int64_t depth, int64_t kW, int64_t kH, int64_t N,
+                                  int flag, decxb_conv_geom* out);
+
+/* The pack step alone: column matrix I2C[M][Kp] of one tensor, bit-exact to
+ * cu_sIm2Col_r8_within (srcs/convolution/CUDA/im2col/im2col.cuh:86-178) fed by the staging of
+ * conv2_mk_im2col.h:234-238 with a zero apron:
+ *   I2C[(y*eq_w + x)*Kp + (ky*kW + kx)*dpitch + c] = S[y+ky-oy][x+kx-ox][c]
+ * (oy, ox) = (kH/2, kW/2) for the zero-border flag, (0, 0) for the valid flag; S is the
+ * tensor value for 0<=row<H, 0<=col<wpitch and 0 elsewhere.  `batch` tensors lie
+ * src_stride / i2c_stride elements apart. */
+DECXB_API int decxb_im2col_pack_f32(decxb_ctx* ctx, const float* src, int64_t W, int64_t H, int64_t depth,
+                                    int64_t kW, int64_t kH, int flag,
+                                    float* i2c, int64_t batch, int64_t src_stride, int64_t i2c_stride,
+                                    void* stream);
+
+/* Whole convolution on device-resident tensors.  Replaces the pack and GEMM launches of
+ * de::cuda::Conv2_MK_im2col (conv2_mk_im2col.h:278-306; drivers :57-162 and :167-274;
+ * kernels cu_sIm2Col_r8_within and cu_conv_eq_mm).  dst is the destination tensor in its
+ * padded layout [out_h][eq_w][Np] per image; padding pixels hold the convolution
+ * evaluated there and padding channels hold 0, as in the reference.  Cross-correlation,
+ * stride 1, kernel radius <= 8 (conv2_mk_im2col.h:170).  `batch` images lie
+ * src_stride / dst_stride elements apart (0 = densely packed). */
+DECXB_API int decxb_conv2_im2col_f32(decxb_ctx* ctx, int mode, int algo, int flag,
+                                     const float* src, int64_t W, int64_t H, int64_t depth,
+                                     const float* filters, int64_t kW, int64_t kH, int64_t N,
+                                     float* dst, int64_t batch, int64_t src_stride, int64_t dst_stride,
+                                     void* stream);
+
+/* Host-resident tensors; blocks until dst is in host memory. */
+DECXB_API int decxb_conv2_im2col_f32_host(decxb_ctx* ctx, int mode, int algo, int flag,
+                                          const float* h_src, int64_t W, int64_t H, int64_t depth,
+                                          const float* h_filters, int64_t kW, int64_t kH, int64_t N,
+                                          float* h_dst, int64_t batch, int64_t src_stride, int64_t dst_stride);
+
+/* ---- introspection for tests and benchmarks --------------------------------------- */
+/* Number of kernels this library has launched on the context since it was created. */
+DECXB_API uint64_t decxb_kernel_launch_count(decxb_ctx* ctx);
+DECXB_API const char* decxb_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DECXB_H_ */

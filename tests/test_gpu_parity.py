@@ -1,0 +1,298 @@
+"""Parity of the CUDA path against the oracle, through the C ABI, on a B200.
+
+Bars: pack and seeded fill bit-exact; 3xTF32 GEMM / convolution
+max|X - Xref| / (K * max|a| * max|b|) <= 1e-6 against the reference's fp32 fma chain
+(plain TF32 is opt-in and only held to 2e-3)."""
+import numpy as np
+import pytest
+import torch
+
+import backup_1_b200 as b
+from oracle import oracle as o
+
+pytestmark = pytest.mark.gpu
+
+TOL_3X = 1e-6
+TOL_1X = 2e-3
+DEV = "cuda:0"
+
+
+def dev(a: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def run_gemm(ctx, A, B, Cin=None, mode=b.GEMM_3XTF32, tile=b.TILE_AUTO, nt=False):
+    M, K = A.shape
+    N = B.shape[1]
+    dA = dev(A)
+    dB = dev(np.ascontiguousarray(B.T)) if nt else dev(B)
+    dC = dev(Cin) if Cin is not None else None
+    dD = torch.full((M, N), float("nan"), device=DEV, dtype=torch.float32)
+    fn = ctx.gemm_nt if nt else ctx.gemm
+    fn(M, N, K, dA, K, dB, K if nt else N, dD, N, Cin=dC, ldc=N if dC is not None else 0, mode=mode, tile=tile)
+    ctx.synchronize()
+    return dD.cpu().numpy()
+
+
+GEMM_SHAPES = [(128, 128, 32), (128, 128, 64), (256, 256, 256), (512, 384, 160), (100, 70, 50), (1, 1, 1),
+               (257, 129, 33), (1024, 1024, 1024), (300, 520, 777), (128, 64, 576)]
+TILES = [b.TILE_1CTA_128x128, b.TILE_2CTA_256x256, b.TILE_1CTA_128x256, b.TILE_1CTA_128x64]
+
+
+def test_seeded_fill_is_bit_identical_to_oracle(ctx):
+    for rows, cols, pitch, seed, first in [(7, 13, 16, 1, 0), (1, 1000, 1000, 2, 5), (33, 64, 64, 9, 2 ** 33)]:
+        t = torch.empty((rows, pitch), device=DEV, dtype=torch.float32)
+        ctx.fill_uniform(t, rows, cols, pitch, seed, first)
+        ctx.synchronize()
+        ref = o.fill_uniform_2d(rows, cols, pitch, seed, first)
+        assert np.array_equal(t.cpu().numpy().view(np.uint32), ref.view(np.uint32))
+
+
+@pytest.mark.parametrize("tile", TILES)
+@pytest.mark.parametrize("shape", GEMM_SHAPES)
+def test_gemm_3xtf32_matches_fma_chain(ctx, shape, tile):
+    M, N, K = shape
+    A = o.fill_uniform(M * K, 1).reshape(M, K)
+    B = o.fill_uniform(K * N, 2).reshape(K, N)
+    D = run_gemm(ctx, A, B, tile=tile)
+    R = o.gemm_fmaf(A, B)
+    err = o.norm_err(D, R, K, 1.0, 1.0)
+    assert err <= TOL_3X, f"{shape} tile {tile}: {err:.3e}"
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 256), (100, 70, 50), (1024, 512, 2048)])
+def test_gemm_plain_tf32_is_opt_in_and_looser(ctx, shape):
+    M, N, K = shape
+    A = o.fill_uniform(M * K, 1).reshape(M, K)
+    B = o.fill_uniform(K * N, 2).reshape(K, N)
+    R = o.gemm_fmaf(A, B)
+    e1 = o.norm_err(run_gemm(ctx, A, B, mode=b.GEMM_1XTF32), R, K, 1.0, 1.0)
+    e3 = o.norm_err(run_gemm(ctx, A, B, mode=b.GEMM_3XTF32), R, K, 1.0, 1.0)
+    assert e1 <= TOL_1X and e3 <= TOL_3X and e3 < e1
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 64), (257, 129, 33), (512, 512, 128)])
+def test_gemm_with_addend_and_nt(ctx, shape):
+    """dst = A*B + C (cu_GEMM_fp32_ABC_spec) and the K-contiguous B orientation."""
+    M, N, K = shape
+    A = o.fill_uniform(M * K, 1).reshape(M, K)
+    B = o.fill_uniform(K * N, 2).reshape(K, N)
+    Cin = o.fill_uniform(M * N, 3).reshape(M, N)
+    R = o.gemm_fmaf(A, B, Cin)
+    assert o.norm_err(run_gemm(ctx, A, B, Cin), R, K, 1.0, 1.0) <= TOL_3X
+    assert o.norm_err(run_gemm(ctx, A, B, Cin, nt=True), R, K, 1.0, 1.0) <= TOL_3X
+
+
+def test_gemm_golden_vectors_of_reference_kernels(ctx, golden):
+    z, cases = golden
+    for c in cases["gemm"]:
+        if c["name"] in cases["sha256"]:
+            continue
+        A = o.fill_uniform(c["M"] * c["K"], 1).reshape(c["M"], c["K"])
+        B = o.fill_uniform(c["K"] * c["N"], 2).reshape(c["K"], c["N"])
+        Cin = o.fill_uniform(c["M"] * c["N"], 3).reshape(c["M"], c["N"]) if c["with_c"] else None
+        D = run_gemm(ctx, A, B, Cin)
+        assert o.norm_err(D, z[c["name"]], c["K"], 1.0, 1.0) <= TOL_3X, c["name"]
+
+
+def test_gemm_known_answer_of_reference_test_program(ctx):
+    """test/test/CUDA_GEMM/CUDA_GEMM.cpp:24-42 at its own size 2048^3: every element equals
+    sum_k (0.1 k)^2."""
+    n = 2048
+    v = (0.1 * np.arange(n, dtype=np.float32)).astype(np.float32)
+    A = np.tile(v[None, :], (n, 1))
+    B = np.tile(v[:, None], (1, n))
+    D = run_gemm(ctx, A, B)
+    expect = float(np.sum(v.astype(np.float64) ** 2))
+    assert np.abs(D.astype(np.float64) - expect).max() / (n * v.max() ** 2) <= TOL_3X
+
+
+def test_gemm_pitched_operands(ctx):
+    """Leading dimensions larger than the row length (DECX pitch = ceil8(width))."""
+    M, N, K = 130, 100, 70
+    lda, ldb, ldd = 72, 104, 104
+    A = o.fill_uniform_2d(M, K, lda, 1)
+    B = o.fill_uniform_2d(K, N, ldb, 2)
+    dD = torch.full((M, ldd), 7.0, device=DEV)
+    ctx.gemm(M, N, K, dev(A), lda, dev(B), ldb, dD, ldd)
+    ctx.synchronize()
+    D = dD.cpu().numpy()
+    R = o.gemm_fmaf(A[:, :K], B[:, :N])
+    assert o.norm_err(D[:, :N], R, K, 1.0, 1.0) <= TOL_3X
+    assert np.all(D[:, N:] == 7.0), "columns beyond N must not be written"
+
+
+def test_gemm_host_resident(ctx):
+    M, N, K = 384, 200, 320
+    A = o.fill_uniform(M * K, 1).reshape(M, K)
+    B = o.fill_uniform(K * N, 2).reshape(K, N)
+    Cin = o.fill_uniform(M * N, 3).reshape(M, N)
+    D = np.empty((M, N), dtype=np.float32)
+    ctx.gemm_host(M, N, K, A, K, B, N, D, N)
+    assert o.norm_err(D, o.gemm_fmaf(A, B), K, 1.0, 1.0) <= TOL_3X
+    ctx.gemm_host(M, N, K, A, K, B, N, D, N, Cin=Cin, ldc=N)
+    assert o.norm_err(D, o.gemm_fmaf(A, B, Cin), K, 1.0, 1.0) <= TOL_3X
+
+
+def test_gemm_argument_errors(ctx):
+    t = torch.zeros(64, device=DEV)
+    with pytest.raises(b.DecxbError) as e:
+        ctx.gemm(8, 8, 8, t, 4, t, 8, t, 8)          # lda < K
+    assert e.value.status == 3
+    with pytest.raises(b.DecxbError) as e:
+        ctx.gemm(0, 8, 8, t, 8, t, 8, t, 8)
+    assert e.value.status == 13
+    with pytest.raises(b.DecxbError) as e:
+        ctx.gemm(8, 8, 8, t, 8, t, 8, t, 8, mode=9)
+    assert e.value.status == 11
+
+
+def test_gemm_config2_full_size_sampled_rows_and_linearity(ctx):
+    """BASELINE config 2 (8192 x 4096 x 2048) on device-generated data: sampled rows against
+    the oracle, plus linearity D(A, 2B) = 2 D(A, B) (exact in binary floating point)."""
+    M, N, K = 8192, 4096, 2048
+    dA = torch.empty((M, K), device=DEV); dB = torch.empty((K, N), device=DEV); dD = torch.empty((M, N), device=DEV)
+    ctx.fill_uniform(dA, M, K, K, 1); ctx.fill_uniform(dB, K, N, N, 2)
+    ctx.gemm(M, N, K, dA, K, dB, N, dD, N)
+    ctx.synchronize()
+    rows = np.array([0, 1, 127, 128, 255, 256, 4095, 4096, 8063, 8191])
+    A = dA[rows].cpu().numpy(); B = dB.cpu().numpy()
+    R = o.gemm_fmaf(A, B)
+    assert o.norm_err(dD[rows].cpu().numpy(), R, K, 1.0, 1.0) <= TOL_3X
+    dB2 = dB * 2.0
+    dD2 = torch.empty_like(dD)
+    ctx.gemm(M, N, K, dA, K, dB2, N, dD2, N)
+    ctx.synchronize()
+    assert torch.equal(dD2, dD * 2.0)
+
+
+# ---- im2col pack ------------------------------------------------------------------------
+PACK_CASES = [(12, 20, 6, 5, 3, 1), (22, 19, 6, 3, 5, 0), (9, 7, 3, 3, 3, 1), (70, 18, 4, 3, 3, 1), (17, 33, 8, 7, 5, 0),
+              (28, 28, 64, 3, 3, 1), (8, 8, 16, 17, 17, 1), (5, 4, 1, 1, 1, 1), (40, 3, 300, 3, 3, 1), (224, 224, 64, 3, 3, 1)]
+
+
+def run_pack(ctx, src, W, depth, kW, kH, flag):
+    H = src.shape[0]
+    _, _, _, M, Kp = o.conv_geometry(W, H, depth, kW, kH, flag)
+    out = torch.full((M, Kp), float("nan"), device=DEV)
+    ctx.im2col_pack(dev(src), W, H, depth, kW, kH, flag, out)
+    ctx.synchronize()
+    return out.cpu().numpy()
+
+
+@pytest.mark.parametrize("case", PACK_CASES)
+def test_pack_is_bit_exact(ctx, case):
+    W, H, C, kW, kH, flag = case
+    src = o.make_tensor(W, H, C, 4)
+    P = run_pack(ctx, src, W, C, kW, kH, flag)
+    R = o.im2col_pack(src, W, C, kW, kH, flag)
+    assert np.array_equal(P.view(np.uint32), R.view(np.uint32))
+
+
+def test_pack_golden_vectors_of_reference_kernel(ctx, golden):
+    import hashlib
+    z, cases = golden
+    for c in cases["conv"]:
+        src = o.make_tensor(c["W"], c["H"], c["depth"], 4)
+        P = run_pack(ctx, src, c["W"], c["depth"], c["kW"], c["kH"], c["flag"])
+        name = "pack_" + c["name"]
+        if name in cases["sha256"]:
+            assert hashlib.sha256(P.tobytes()).hexdigest() == cases["sha256"][name]
+        else:
+            assert np.array_equal(P.view(np.uint32), z[name].view(np.uint32))
+
+
+def test_pack_batched_equals_per_image(ctx):
+    W, H, C, kW, kH, flag, nb = 14, 9, 8, 3, 3, 1, 5
+    imgs = np.stack([o.make_tensor(W, H, C, 4, first_index=i * 10007) for i in range(nb)])
+    _, _, _, M, Kp = o.conv_geometry(W, H, C, kW, kH, flag)
+    out = torch.empty((nb, M, Kp), device=DEV)
+    ctx.im2col_pack(dev(imgs), W, H, C, kW, kH, flag, out, batch=nb)
+    ctx.synchronize()
+    got = out.cpu().numpy()
+    for i in range(nb):
+        assert np.array_equal(got[i].view(np.uint32), o.im2col_pack(imgs[i], W, C, kW, kH, flag).view(np.uint32))
+
+
+# ---- convolution --------------------------------------------------------------------------
+CONV_CASES = [(12, 20, 6, 5, 3, 5, 1), (22, 19, 6, 3, 5, 5, 0), (9, 7, 3, 3, 3, 2, 1), (70, 18, 4, 3, 3, 33, 1),
+              (17, 33, 8, 7, 5, 4, 0), (28, 28, 64, 3, 3, 64, 1), (56, 56, 64, 3, 3, 130, 1)]
+
+
+def run_conv(ctx, src, W, depth, flt, kW, flag, mode=b.GEMM_3XTF32, algo=b.CONV_EXPLICIT, host=False):
+    H = src.shape[-3]
+    N, kH = flt.shape[0], flt.shape[1]
+    nb = src.shape[0] if src.ndim == 4 else 1
+    _, oh, eq, _, _ = o.conv_geometry(W, H, depth, kW, kH, flag)
+    if host:
+        out = np.empty((nb, oh, eq, o.ceil4(N)), dtype=np.float32)
+        ctx.conv2_im2col_host(src, W, H, depth, flt, kW, kH, N, out, flag=flag, batch=nb, mode=mode, algo=algo)
+        return out if src.ndim == 4 else out[0]
+    out = torch.full((nb, oh, eq, o.ceil4(N)), float("nan"), device=DEV)
+    ctx.conv2_im2col(dev(src), W, H, depth, dev(flt), kW, kH, N, out, flag=flag, batch=nb, mode=mode, algo=algo)
+    ctx.synchronize()
+    r = out.cpu().numpy()
+    return r if src.ndim == 4 else r[0]
+
+
+@pytest.mark.parametrize("case", CONV_CASES)
+def test_conv_matches_oracle(ctx, case):
+    W, H, C, kW, kH, N, flag = case
+    src = o.make_tensor(W, H, C, 4)
+    flt = o.make_filters(kW, kH, C, N, 5)
+    R = o.conv2_im2col(src, W, C, flt, kW, flag)
+    K = kW * kH * o.ceil4(C)
+    D = run_conv(ctx, src, W, C, flt, kW, flag)
+    assert o.norm_err(D, R, K, 1.0, 1.0) <= TOL_3X
+    assert np.all(D[..., N:] == 0), "padding channels must be zero"
+    Dh = run_conv(ctx, src, W, C, flt, kW, flag, host=True)
+    assert np.array_equal(D, Dh), "host-resident path must give the device path's bits"
+
+
+def test_conv_golden_vectors_of_reference_driver(ctx, golden):
+    z, cases = golden
+    for c in cases["conv"]:
+        name = "conv_" + c["name"]
+        if name in cases["sha256"]:
+            continue
+        src = o.make_tensor(c["W"], c["H"], c["depth"], 4)
+        flt = o.make_filters(c["kW"], c["kH"], c["depth"], c["N"], 5)
+        D = run_conv(ctx, src, c["W"], c["depth"], flt, c["kW"], c["flag"])
+        K = c["kW"] * c["kH"] * o.ceil4(c["depth"])
+        assert o.norm_err(D, z[name], K, 1.0, 1.0) <= TOL_3X, name
+
+
+def test_conv_batched_equals_per_image(ctx):
+    W, H, C, kW, N, nb = 20, 12, 16, 3, 24, 6
+    imgs = np.stack([o.make_tensor(W, H, C, 4, first_index=i * 7919) for i in range(nb)])
+    flt = o.make_filters(kW, kW, C, N, 5)
+    D = run_conv(ctx, imgs, W, C, flt, kW, 1)
+    for i in range(nb):
+        assert np.array_equal(D[i], run_conv(ctx, imgs[i], W, C, flt, kW, 1))
+
+
+def test_conv_config3_full_size(ctx):
+    """BASELINE config 3: 224x224x64 -> 64 filters 3x3, zero border.  Sampled output rows
+    against the oracle GEMM over the oracle pack."""
+    W = H = 224; C = 64; N = 64; kW = 3
+    src = o.make_tensor(W, H, C, 4)
+    flt = o.make_filters(kW, kW, C, N, 5)
+    D = run_conv(ctx, src, W, C, flt, kW, 1).reshape(-1, N)
+    P = o.im2col_pack(src, W, C, kW, kW, 1)
+    Km = o.kernel_matrix(flt, kW, C)
+    rows = np.arange(0, P.shape[0], 97)
+    R = o.gemm_fmaf(P[rows], np.ascontiguousarray(Km.T))
+    assert o.norm_err(D[rows], R, P.shape[1], 1.0, 1.0) <= TOL_3X
+
+
+def test_arena_reuses_blocks(ctx):
+    p = ctx.malloc(1 << 20)
+    ctx.free(p)
+    before = ctx.arena_stats().n_reuses
+    q = ctx.malloc(1 << 20)
+    assert ctx.arena_stats().n_reuses == before + 1
+    ctx.free(q)
+    big = ctx.malloc(3 << 30)      # beyond the reference pool's 2 GiB int-shift limit
+    ctx.free(big)
+    ctx.release_cached()
+    assert ctx.arena_stats().bytes_cached == 0
