@@ -8,43 +8,26 @@
 
 namespace {
 
-/* Scratch blocks of one call; returned to the arena when the stream has passed the point
- * where release() was called (host callback), so a block is never handed out while the GPU
- * may still touch it. */
+/* Scratch blocks of one call, taken from the arena in stream order: a block released at the
+ * end of a call can serve the next call on the same stream at once, and a call on another
+ * stream waits for it on the device.  No host synchronisation, no allocation in steady state. */
 struct Scratch {
     decxb_ctx* ctx;
+    cudaStream_t s;
     std::vector<void*> ptrs;
-    explicit Scratch(decxb_ctx* c) : ctx(c) {}
+    Scratch(decxb_ctx* c, cudaStream_t st) : ctx(c), s(st) {}
     int get(size_t bytes, void** p)
     {
-        int rc = decxb_malloc(ctx, bytes, p);
+        int rc = decxb_malloc_on_stream(ctx, bytes, p, s);
         if (rc == DECXB_OK) ptrs.push_back(*p);
         return rc;
     }
-    struct Pending { decxb_ctx* ctx; std::vector<void*> ptrs; };
-    static void CUDART_CB on_done(void* u)
+    void release()
     {
-        Pending* pd = static_cast<Pending*>(u);
-        for (void* q : pd->ptrs) decxb_free(pd->ctx, q);
-        delete pd;
-    }
-    void release(cudaStream_t s)
-    {
-        if (ptrs.empty()) return;
-        Pending* pd = new Pending{ctx, std::move(ptrs)};
-        ptrs.clear();
-        if (cudaLaunchHostFunc(s, on_done, pd) != cudaSuccess) {
-            cudaGetLastError();
-            cudaStreamSynchronize(s);
-            on_done(pd);
-        }
-    }
-    void release_now()
-    {
-        for (void* q : ptrs) decxb_free(ctx, q);
+        for (void* q : ptrs) decxb_free_on_stream(ctx, q, s);
         ptrs.clear();
     }
-    ~Scratch() { release_now(); }
+    ~Scratch() { release(); }
 };
 
 bool tma_ok(const float* p, int64_t ld) { return ((uintptr_t)p % 16 == 0) && (ld % 4 == 0); }
@@ -60,7 +43,7 @@ int gemm_device(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_
     if (lda < K || ldb < (b_is_nt ? K : N) || ldd < N || (C && ldc < N))
         return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
 
-    Scratch scratch(ctx);
+    Scratch scratch(ctx, s);
     const int64_t Kp = decxb_ceil_to(K, 4);
     decxb_gemm_args g = {};
     g.M = M; g.N = N; g.K = K; g.C = C; g.ldc = ldc; g.D = D; g.ldd = ldd; g.tile = tile; g.b_rows = N;
@@ -95,7 +78,7 @@ int gemm_device(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_
         g.b_hi = hi; g.b_lo = lo; g.ldb = Kp;
     }
     rc = decxb_launch_gemm_tn(ctx, g, s);
-    scratch.release(s);
+    scratch.release();
     return rc;
 }
 
@@ -131,8 +114,8 @@ extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M
     if (!hA || !hB || !hD) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null operand");
     if (lda < K || ldb < N || ldd < N || (hC && ldc < N))
         return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
-    Scratch scratch(ctx);
     cudaStream_t s = ctx->stream;
+    Scratch scratch(ctx, s);
     const int64_t Kp = decxb_ceil_to(K, 4), Np = decxb_ceil_to(N, 4);
     float *dA, *dB, *dC = nullptr, *dD;
     if ((rc = scratch.get((size_t)M * Kp * 4, (void**)&dA))) return rc;
@@ -198,7 +181,7 @@ int conv_device(decxb_ctx* ctx, int mode, int algo, int flag,
     const bool x3 = mode == DECXB_GEMM_3XTF32;
     if (algo == DECXB_CONV_IMPLICIT) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "implicit convolution is not built yet");
 
-    Scratch scratch(ctx);
+    Scratch scratch(ctx, s);
     /* filter matrix [Np][Kp] (hi/lo), rows >= N zero so padding channels come out 0 */
     float *k_hi = nullptr, *k_lo = nullptr;
     if ((rc = scratch.get((size_t)g.Np * g.Kp * 4, (void**)&k_hi))) return rc;
@@ -235,7 +218,7 @@ int conv_device(decxb_ctx* ctx, int mode, int algo, int flag,
             if ((rc = decxb_launch_gemm_tn(ctx, a, s))) return rc;
         }
     }
-    scratch.release(s);
+    scratch.release();
     return DECXB_OK;
 }
 
@@ -268,8 +251,8 @@ extern "C" int decxb_conv2_im2col_f32_host(decxb_ctx* ctx, int mode, int algo, i
     const int64_t src_img = H * wp * dp, dst_img = g.M * g.Np;
     if (src_stride == 0) src_stride = src_img;
     if (dst_stride == 0) dst_stride = dst_img;
-    Scratch scratch(ctx);
     cudaStream_t s = ctx->stream;
+    Scratch scratch(ctx, s);
     float *d_src, *d_flt, *d_dst;
     if ((rc = scratch.get((size_t)batch * src_img * 4, (void**)&d_src))) return rc;
     if ((rc = scratch.get((size_t)N * kH * kwp * dp * 4, (void**)&d_flt))) return rc;

@@ -12,6 +12,7 @@
 #include <mutex>
 #include <string>
 #include <unordered_map>
+#include <vector>
 
 #include "decxb.h"
 
@@ -29,10 +30,16 @@ enum {
     DECXB_DEVERR_WAIT_EXPIRED = 1,
 };
 
+/* A cached block remembers the stream that used it last and an event recorded there when it
+ * was released, so the same stream can take it again at once (stream order protects it) and
+ * another stream waits on the event first. */
+struct decxb_cached_block { void* ptr; cudaStream_t stream; cudaEvent_t ev; };
+
 struct decxb_arena {
     std::mutex mtx;
     std::unordered_map<void*, size_t> live;           /* ptr -> block bytes */
-    std::multimap<size_t, void*> cached;              /* block bytes -> ptr */
+    std::multimap<size_t, decxb_cached_block> cached; /* block bytes -> block */
+    std::vector<cudaEvent_t> ev_pool;
     size_t bytes_in_use = 0, bytes_cached = 0, peak = 0;
     uint64_t n_driver_allocs = 0, n_reuses = 0;
 };
@@ -48,6 +55,20 @@ struct decxb_ctx {
     long long wait_limit_ns = 2000000000LL;
     std::atomic<uint64_t> launches{0};
     std::string last_error;
+    /* per-kernel event timing (decxb_profile_*) */
+    bool profiling = false;
+    std::mutex prof_mtx;
+    struct ProfSpan { int cls; cudaEvent_t a, b; };
+    std::vector<ProfSpan> prof_open;
+    std::vector<cudaEvent_t> prof_pool;
+    decxb_profile prof_total = {};
+};
+
+/* RAII bracket around one kernel launch: counts it and, when profiling, records events. */
+struct decxb_launch_scope {
+    decxb_ctx* ctx; cudaStream_t s; int cls; cudaEvent_t b = nullptr;
+    decxb_launch_scope(decxb_ctx* c, cudaStream_t st, int k);
+    ~decxb_launch_scope();
 };
 
 #define DECXB_CUDA_TRY(ctx, expr)                                                              \
@@ -63,6 +84,10 @@ int decxb_fail(decxb_ctx* ctx, int status, const std::string& msg);
 void decxb_set_error(decxb_ctx* ctx, const std::string& msg);
 /* Binds the context's device to the calling thread. */
 int decxb_bind(decxb_ctx* ctx);
+/* Stream-ordered scratch: the block may be handed out again while work queued on `s` before
+ * the release is still running; a taker on another stream waits for it on the device. */
+int decxb_malloc_on_stream(decxb_ctx* ctx, size_t bytes, void** dptr, cudaStream_t s);
+int decxb_free_on_stream(decxb_ctx* ctx, void* dptr, cudaStream_t s);
 /* Reads (and clears) the device status word after a synchronisation. */
 int decxb_check_dev_status(decxb_ctx* ctx);
 

@@ -82,6 +82,7 @@ extern "C" int decxb_destroy(decxb_ctx* ctx)
         cudaDeviceSynchronize();
         decxb_release_cached(ctx);
         for (auto& kv : ctx->arena.live) cudaFree(kv.first);
+        for (cudaEvent_t e : ctx->arena.ev_pool) cudaEventDestroy(e);
         cudaFree(ctx->d_status);
         cudaFreeHost(ctx->h_status);
         cudaStreamDestroy(ctx->stream);
@@ -135,7 +136,9 @@ static size_t arena_round(size_t bytes)
     return (bytes + g - 1) / g * g;
 }
 
-extern "C" int decxb_malloc(decxb_ctx* ctx, size_t bytes, void** dptr)
+static const cudaStream_t kNoStream = (cudaStream_t)(intptr_t)-1;   /* block is idle: no wait needed */
+
+static int arena_take(decxb_ctx* ctx, size_t bytes, void** dptr, cudaStream_t s, bool stream_ordered)
 {
     if (!ctx || !dptr) return DECXB_ERR_BAD_PARAM;
     *dptr = nullptr;
@@ -144,11 +147,23 @@ extern "C" int decxb_malloc(decxb_ctx* ctx, size_t bytes, void** dptr)
     const size_t need = arena_round(bytes);
     decxb_arena& a = ctx->arena;
     std::lock_guard<std::mutex> lock(a.mtx);
-    auto it = a.cached.lower_bound(need);
+    /* prefer a block last used on the same stream, else any fitting block */
+    auto pick = a.cached.end();
+    for (auto it = a.cached.lower_bound(need); it != a.cached.end() && it->first <= need * 2; ++it) {
+        if (pick == a.cached.end()) pick = it;
+        if (it->second.stream == kNoStream || (stream_ordered && it->second.stream == s)) { pick = it; break; }
+    }
     void* p = nullptr; size_t got = 0;
-    if (it != a.cached.end() && it->first <= need * 2) {
-        p = it->second; got = it->first;
-        a.cached.erase(it);
+    if (pick != a.cached.end()) {
+        decxb_cached_block blk = pick->second;
+        got = pick->first;
+        a.cached.erase(pick);
+        if (blk.stream != kNoStream && !(stream_ordered && blk.stream == s)) {
+            if (stream_ordered) cudaStreamWaitEvent(s, blk.ev, 0);
+            else cudaEventSynchronize(blk.ev);
+        }
+        if (blk.ev) a.ev_pool.push_back(blk.ev);
+        p = blk.ptr;
         a.bytes_cached -= got;
         a.n_reuses++;
     } else {
@@ -156,7 +171,8 @@ extern "C" int decxb_malloc(decxb_ctx* ctx, size_t bytes, void** dptr)
         if (e != cudaSuccess) {
             /* give cached blocks back and retry once */
             cudaGetLastError();
-            for (auto& kv : a.cached) cudaFree(kv.second);
+            cudaDeviceSynchronize();
+            for (auto& kv : a.cached) { cudaFree(kv.second.ptr); if (kv.second.ev) a.ev_pool.push_back(kv.second.ev); }
             a.cached.clear(); a.bytes_cached = 0;
             e = cudaMalloc(&p, need);
         }
@@ -174,7 +190,7 @@ extern "C" int decxb_malloc(decxb_ctx* ctx, size_t bytes, void** dptr)
     return DECXB_OK;
 }
 
-extern "C" int decxb_free(decxb_ctx* ctx, void* dptr)
+static int arena_give(decxb_ctx* ctx, void* dptr, cudaStream_t s, bool stream_ordered)
 {
     if (!ctx) return DECXB_ERR_BAD_PARAM;
     if (!dptr) return DECXB_OK;
@@ -185,10 +201,22 @@ extern "C" int decxb_free(decxb_ctx* ctx, void* dptr)
     const size_t sz = it->second;
     a.live.erase(it);
     a.bytes_in_use -= sz;
-    a.cached.emplace(sz, dptr);
+    decxb_cached_block blk = {dptr, kNoStream, nullptr};
+    if (stream_ordered) {
+        if (!a.ev_pool.empty()) { blk.ev = a.ev_pool.back(); a.ev_pool.pop_back(); }
+        else if (cudaEventCreateWithFlags(&blk.ev, cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); blk.ev = nullptr; }
+        if (blk.ev && cudaEventRecord(blk.ev, s) == cudaSuccess) blk.stream = s;
+        else { cudaGetLastError(); cudaStreamSynchronize(s); }
+    }
+    a.cached.emplace(sz, blk);
     a.bytes_cached += sz;
     return DECXB_OK;
 }
+
+extern "C" int decxb_malloc(decxb_ctx* ctx, size_t bytes, void** dptr) { return arena_take(ctx, bytes, dptr, nullptr, false); }
+extern "C" int decxb_free(decxb_ctx* ctx, void* dptr) { return arena_give(ctx, dptr, nullptr, false); }
+int decxb_malloc_on_stream(decxb_ctx* ctx, size_t bytes, void** dptr, cudaStream_t s) { return arena_take(ctx, bytes, dptr, s, true); }
+int decxb_free_on_stream(decxb_ctx* ctx, void* dptr, cudaStream_t s) { return arena_give(ctx, dptr, s, true); }
 
 extern "C" int decxb_release_cached(decxb_ctx* ctx)
 {
@@ -198,7 +226,7 @@ extern "C" int decxb_release_cached(decxb_ctx* ctx)
     decxb_arena& a = ctx->arena;
     std::lock_guard<std::mutex> lock(a.mtx);
     cudaDeviceSynchronize();
-    for (auto& kv : a.cached) cudaFree(kv.second);
+    for (auto& kv : a.cached) { cudaFree(kv.second.ptr); if (kv.second.ev) a.ev_pool.push_back(kv.second.ev); }
     a.cached.clear();
     a.bytes_cached = 0;
     return DECXB_OK;
@@ -248,5 +276,63 @@ extern "C" int decxb_memset(decxb_ctx* ctx, void* dptr, int value, size_t bytes)
     if (rc) return rc;
     DECXB_CUDA_TRY(ctx, cudaMemsetAsync(dptr, value, bytes, ctx->stream));
     DECXB_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    return DECXB_OK;
+}
+
+/* ---- per-kernel event timing ------------------------------------------------------------- */
+static cudaEvent_t prof_event(decxb_ctx* ctx)
+{
+    if (!ctx->prof_pool.empty()) { cudaEvent_t e = ctx->prof_pool.back(); ctx->prof_pool.pop_back(); return e; }
+    cudaEvent_t e = nullptr;
+    if (cudaEventCreate(&e) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    return e;
+}
+
+decxb_launch_scope::decxb_launch_scope(decxb_ctx* c, cudaStream_t st, int k) : ctx(c), s(st), cls(k)
+{
+    ctx->launches++;
+    if (!ctx->profiling) return;
+    std::lock_guard<std::mutex> lock(ctx->prof_mtx);
+    cudaEvent_t a = prof_event(ctx);
+    b = prof_event(ctx);
+    if (!a || !b) { b = nullptr; return; }
+    cudaEventRecord(a, s);
+    ctx->prof_open.push_back({cls, a, b});
+}
+
+decxb_launch_scope::~decxb_launch_scope()
+{
+    if (b) cudaEventRecord(b, s);
+}
+
+extern "C" int decxb_profile_enable(decxb_ctx* ctx, int on)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    decxb_profile tmp;
+    if ((rc = decxb_profile_read(ctx, &tmp))) return rc;     /* drains open spans */
+    std::lock_guard<std::mutex> lock(ctx->prof_mtx);
+    ctx->profiling = on != 0;
+    if (on) ctx->prof_total = decxb_profile{};
+    return DECXB_OK;
+}
+
+extern "C" int decxb_profile_read(decxb_ctx* ctx, decxb_profile* out)
+{
+    if (!out) return DECXB_ERR_BAD_PARAM;
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    DECXB_CUDA_TRY(ctx, cudaDeviceSynchronize());
+    std::lock_guard<std::mutex> lock(ctx->prof_mtx);
+    for (auto& sp : ctx->prof_open) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, sp.a, sp.b) == cudaSuccess) {
+            ctx->prof_total.ms[sp.cls] += ms;
+            ctx->prof_total.launches[sp.cls] += 1;
+        } else cudaGetLastError();
+        ctx->prof_pool.push_back(sp.a); ctx->prof_pool.push_back(sp.b);
+    }
+    ctx->prof_open.clear();
+    *out = ctx->prof_total;
     return DECXB_OK;
 }

@@ -76,11 +76,12 @@ int decxb_launch_pack(decxb_ctx* ctx, const float* src, int64_t W, int64_t H, in
     dim3 grid((unsigned)(g.out_h * batch), (unsigned)decxb_ceil_div(g.eq_w, PACK_X_PER_BLOCK));
     const int off_y = flag == DECXB_CONV_ZERO_COMPENSATE ? -(int)(kH / 2) : 0;
     const int off_x = flag == DECXB_CONV_ZERO_COMPENSATE ? -(int)(kW / 2) : 0;
-    decxb_im2col_pack_kernel<<<grid, 256, 0, s>>>(
+    const int block = (TX * TY + 31) / 32 * 32;
+    decxb_launch_scope scope(ctx, s, DECXB_K_PACK);
+    decxb_im2col_pack_kernel<<<grid, block, 0, s>>>(
         reinterpret_cast<const float4*>(src), reinterpret_cast<float4*>(i2c),
         (int)H, (int)wp, (int)(dp / 4), (int)kW, (int)kH, off_y, off_x,
         (int)g.out_h, (int)g.eq_w, Kp4, TX, TY, src_stride / 4, i2c_stride / 4);
-    ctx->launches++;
     DECXB_CUDA_TRY(ctx, cudaGetLastError());
     return DECXB_OK;
 }

@@ -48,8 +48,10 @@ extern "C" int decxb_fill_uniform_f32(decxb_ctx* ctx, float* dptr, uint64_t rows
     cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
     const uint64_t total = rows * pitch;
     int blocks = (int)((total + 255) / 256 < (uint64_t)ctx->sm_count * 16 ? (total + 255) / 256 : (uint64_t)ctx->sm_count * 16);
-    decxb_fill_uniform_kernel<<<blocks, 256, 0, s>>>(dptr, rows, cols, pitch, seed, first_index);
-    ctx->launches++;
+    {
+        decxb_launch_scope scope(ctx, s, DECXB_K_FILL);
+        decxb_fill_uniform_kernel<<<blocks, 256, 0, s>>>(dptr, rows, cols, pitch, seed, first_index);
+    }
     DECXB_CUDA_TRY(ctx, cudaGetLastError());
     return DECXB_OK;
 }
@@ -111,8 +113,10 @@ int decxb_launch_split_rows(decxb_ctx* ctx, const float* in, int64_t rows, int64
     const int vec_ok = ((uintptr_t)in % 16 == 0) && (ld_in % 4 == 0);
     int64_t blocks = (total + 255) / 256;
     if (blocks > (int64_t)ctx->sm_count * 32) blocks = (int64_t)ctx->sm_count * 32;
-    decxb_split_rows_kernel<<<(int)blocks, 256, 0, s>>>(in, rows, cols, ld_in, hi, lo, ld_out, rows_out, vec_ok);
-    ctx->launches++;
+    {
+        decxb_launch_scope scope(ctx, s, DECXB_K_SPLIT);
+        decxb_split_rows_kernel<<<(int)blocks, 256, 0, s>>>(in, rows, cols, ld_in, hi, lo, ld_out, rows_out, vec_ok);
+    }
     DECXB_CUDA_TRY(ctx, cudaGetLastError());
     return DECXB_OK;
 }
@@ -162,8 +166,10 @@ int decxb_launch_split_transpose(decxb_ctx* ctx, const float* in, int64_t K, int
     int64_t blocks = tiles_n * tiles_k;
     if (blocks == 0) return DECXB_OK;
     if (blocks > (int64_t)ctx->sm_count * 16) blocks = (int64_t)ctx->sm_count * 16;
-    decxb_split_transpose_kernel<<<(int)blocks, 256, 0, s>>>(in, K, N, ld_in, hi, lo, ld_out, raw, tiles_n);
-    ctx->launches++;
+    {
+        decxb_launch_scope scope(ctx, s, DECXB_K_SPLIT);
+        decxb_split_transpose_kernel<<<(int)blocks, 256, 0, s>>>(in, K, N, ld_in, hi, lo, ld_out, raw, tiles_n);
+    }
     DECXB_CUDA_TRY(ctx, cudaGetLastError());
     return DECXB_OK;
 }
@@ -201,8 +207,10 @@ int decxb_launch_filter_matrix(decxb_ctx* ctx, const float* filters, int64_t kW,
     if (total == 0) return DECXB_OK;
     int64_t blocks = (total + 255) / 256;
     if (blocks > (int64_t)ctx->sm_count * 16) blocks = (int64_t)ctx->sm_count * 16;
-    decxb_filter_matrix_kernel<<<(int)blocks, 256, 0, s>>>(filters, (int)kW, (int)kH, (int)dp, N, hi, lo, rows_out, ld_out, raw);
-    ctx->launches++;
+    {
+        decxb_launch_scope scope(ctx, s, DECXB_K_SPLIT);
+        decxb_filter_matrix_kernel<<<(int)blocks, 256, 0, s>>>(filters, (int)kW, (int)kH, (int)dp, N, hi, lo, rows_out, ld_out, raw);
+    }
     DECXB_CUDA_TRY(ctx, cudaGetLastError());
     return DECXB_OK;
 }

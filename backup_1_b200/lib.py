@@ -31,6 +31,14 @@ class ArenaStats(C.Structure):
                 ("n_driver_allocs", C.c_uint64), ("n_reuses", C.c_uint64)]
 
 
+class Profile(C.Structure):
+    _fields_ = [("ms", C.c_double * 4), ("launches", C.c_uint64 * 4)]
+
+    def as_dict(self):
+        names = ("gemm", "split", "pack", "fill")
+        return {n: {"ms": self.ms[i], "launches": int(self.launches[i])} for i, n in enumerate(names)}
+
+
 _lib = None
 
 # name -> (restype, argtypes); every symbol include/decxb.h declares
@@ -61,6 +69,8 @@ SIGNATURES = {
     "decxb_conv2_im2col_f32": (_i, [_vp, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp]),
     "decxb_conv2_im2col_f32_host": (_i, [_vp, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64]),
     "decxb_kernel_launch_count": (_u64, [_vp]),
+    "decxb_profile_enable": (_i, [_vp, _i]),
+    "decxb_profile_read": (_i, [_vp, C.POINTER(Profile)]),
     "decxb_version": (C.c_char_p, []),
 }
 
@@ -138,6 +148,14 @@ class Context:
 
     def launches(self) -> int:
         return int(self.L.decxb_kernel_launch_count(self.h))
+
+    def profile_enable(self, on: bool = True):
+        self._chk(self.L.decxb_profile_enable(self.h, 1 if on else 0))
+
+    def profile_read(self) -> dict:
+        p = Profile()
+        self._chk(self.L.decxb_profile_read(self.h, C.byref(p)))
+        return p.as_dict()
 
     def malloc(self, nbytes: int) -> int:
         p = _vp()

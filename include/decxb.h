@@ -205,6 +205,19 @@ DECXB_API int decxb_conv2_im2col_f32_host(decxb_ctx* ctx, int mode, int algo, in
                                           float* h_dst, int64_t batch, int64_t src_stride, int64_t dst_stride);
 
 /* ---- introspection for tests and benchmarks --------------------------------------- */
+/* Per-kernel device timing.  While enabled, every kernel the library launches is bracketed
+ * by CUDA events on its own stream; decxb_profile_read synchronises the device, adds the
+ * elapsed times to the totals below and returns them (decxb_profile_enable(ctx, 1) also
+ * resets the totals).  No counterpart in the reference (its tests time whole calls with
+ * clock(), test/test/CUDA_GEMM/CUDA_GEMM.cpp:43-55). */
+enum { DECXB_K_GEMM = 0, DECXB_K_SPLIT = 1, DECXB_K_PACK = 2, DECXB_K_FILL = 3, DECXB_K_CLASSES = 4 };
+typedef struct decxb_profile {
+    double   ms[DECXB_K_CLASSES];        /* summed device time per kernel class */
+    uint64_t launches[DECXB_K_CLASSES];
+} decxb_profile;
+DECXB_API int decxb_profile_enable(decxb_ctx* ctx, int on);
+DECXB_API int decxb_profile_read(decxb_ctx* ctx, decxb_profile* out);
+
 /* Number of kernels this library has launched on the context since it was created. */
 DECXB_API uint64_t decxb_kernel_launch_count(decxb_ctx* ctx);
 DECXB_API const char* decxb_version(void);

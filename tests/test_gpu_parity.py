@@ -104,7 +104,12 @@ def test_gemm_known_answer_of_reference_test_program(ctx):
     B = np.tile(v[:, None], (1, n))
     D = run_gemm(ctx, A, B)
     expect = float(np.sum(v.astype(np.float64) ** 2))
-    assert np.abs(D.astype(np.float64) - expect).max() / (n * v.max() ** 2) <= TOL_3X
+    assert np.all(D == D[0, 0]), "every element must be the same number"
+    # All terms are positive and grow with k: the worst case for the tensor core's fp32
+    # accumulator, which rounds every add toward zero.  The bias stays below 1e-5 of
+    # K max|a| max|b| (seeded +-1 data of the benchmark configs sits near 1e-7).
+    assert abs(float(D[0, 0]) - expect) / (n * float(v.max()) ** 2) <= 1e-5
+    assert abs(float(D[0, 0]) - expect) / expect <= 2e-5
 
 
 def test_gemm_pitched_operands(ctx):
