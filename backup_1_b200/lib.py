@@ -64,6 +64,7 @@ SIGNATURES = {
     "decxb_gemm_f32": (_i, [_vp, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
     "decxb_gemm_f32_nt": (_i, [_vp, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
     "decxb_gemm_f32_host": (_i, [_vp, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64]),
+    "decxb_gemm_f32_noalloc": (_i, [_i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, C.c_char_p, _sz]),
     "decxb_conv_geometry": (_i, [_i64, _i64, _i64, _i64, _i64, _i64, _i, C.POINTER(ConvGeom)]),
     "decxb_im2col_pack_f32": (_i, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _i, _vp, _i64, _i64, _i64, _vp]),
     "decxb_conv2_im2col_f32": (_i, [_vp, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp]),

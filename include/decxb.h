@@ -161,6 +161,31 @@ DECXB_API int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile,
                                   const float* hC, int64_t ldc,
                                   float* hD, int64_t ldd);
 
+/* The 3xTF32 product D = A*B (+C) of decxb_gemm_f32 for callers that must not allocate
+ * device memory (this entry has no counterpart in the reference).  Such callers exist: a
+ * process in which a framework's caching pool has reserved the whole card, so that a
+ * cudaMalloc would fail; a latency-critical loop that cannot take cudaMalloc's implicit
+ * device-wide synchronisation.  The regular entry point draws its hi/lo operand scratch
+ * from the context's arena; this one needs no context and keeps that scratch in a fixed
+ * 64 MiB array inside the library image, which every device that uses this entry holds
+ * until the process exits.
+ *  - Limit: 2*(M+N)*ceil4(K)*4 bytes (each of the four parts rounded up to 256) must fit in
+ *    64 MiB, e.g. 2048 x 2048 x 2048; larger problems return DECXB_ERR_TOO_LARGE and `err`
+ *    says how much was asked for.
+ *  - It calls no cudaMalloc, cudaFree or other allocating routine.  The first call on a
+ *    device makes that device current and resolves the array's device address
+ *    (cudaGetSymbolAddress); make that first call before any stream capture begins.
+ *  - All calls share the one array and it keeps the previous call's contents; the entry
+ *    rewrites the parts it uses and clears its status word itself.  It blocks until D is
+ *    complete.  Calls that would overlap on the GPU (from several threads or streams) race on
+ *    the array: issue them one after another.
+ *  - A, B, C, D are device pointers; `stream` is a cudaStream_t (NULL = default stream);
+ *    `err` (optional, err_len bytes) receives a message when the status is not DECXB_OK. */
+DECXB_API int decxb_gemm_f32_noalloc(int device, int64_t M, int64_t N, int64_t K,
+                                     const float* A, int64_t lda, const float* B, int64_t ldb,
+                                     const float* C, int64_t ldc, float* D, int64_t ldd,
+                                     void* stream, char* err, size_t err_len);
+
 /* ---- im2col convolution --------------------------------------------------------------
  * Geometry shared by the entry points below (conv2_mk_im2col.h:60-93, :170-199). */
 typedef struct decxb_conv_geom {
