@@ -179,9 +179,44 @@ int conv_device(decxb_ctx* ctx, int mode, int algo, int flag,
     if (src_stride == 0) src_stride = H * wp * dp;
     if (dst_stride == 0) dst_stride = g.M * g.Np;
     const bool x3 = mode == DECXB_GEMM_3XTF32;
-    if (algo == DECXB_CONV_IMPLICIT) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "implicit convolution is not built yet");
-
     Scratch scratch(ctx, s);
+    if (algo == DECXB_CONV_IMPLICIT) {
+        /* The column matrix is never written: the GEMM's A tiles are TMA boxes of the (split)
+         * source tensor, one filter tap and 32 channels per k-block. */
+        if (((uintptr_t)src % 16) || (src_stride % 4) || ((uintptr_t)dst % 16) || (dst_stride % 4))
+            return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "implicit convolution needs 16-byte aligned tensors");
+        if (H * wp * dp > 0x7fffffffffLL || batch > 0x7fffffffLL) return decxb_fail(ctx, DECXB_ERR_TOO_LARGE, "tensor");
+        const int64_t cp = decxb_ceil_to(dp, 32), Kc = kW * kH * cp;
+        float *k_hi = nullptr, *k_lo = nullptr, *s_hi = nullptr, *s_lo = nullptr;
+        if ((rc = scratch.get((size_t)g.Np * Kc * 4, (void**)&k_hi))) return rc;
+        if (x3 && (rc = scratch.get((size_t)g.Np * Kc * 4, (void**)&k_lo))) return rc;
+        if ((rc = decxb_launch_filter_matrix(ctx, filters, kW, kH, depth, N, k_hi, k_lo, g.Np, Kc, x3 ? 0 : 1, s, cp))) return rc;
+        decxb_conv_gemm_args a = {};
+        const int64_t img = H * wp * dp;
+        if (x3) {
+            if ((rc = scratch.get((size_t)batch * img * 4, (void**)&s_hi))) return rc;
+            if ((rc = scratch.get((size_t)batch * img * 4, (void**)&s_lo))) return rc;
+            if (src_stride == img) {
+                if ((rc = decxb_launch_split_rows(ctx, src, batch * H * wp, dp, dp, s_hi, s_lo, dp, batch * H * wp, s))) return rc;
+            } else {
+                for (int64_t b0 = 0; b0 < batch; ++b0)
+                    if ((rc = decxb_launch_split_rows(ctx, src + b0 * src_stride, H * wp, dp, dp, s_hi + b0 * img, s_lo + b0 * img,
+                                                      dp, H * wp, s))) return rc;
+            }
+            a.src_hi = s_hi; a.src_lo = s_lo; a.src_img_stride = img;
+        } else { a.src_hi = src; a.src_lo = nullptr; a.src_img_stride = src_stride; }
+        a.dp = dp; a.wp = wp; a.H = H; a.batch = batch;
+        a.k_hi = k_hi; a.k_lo = k_lo; a.k_rows = g.Np; a.k_cols = Kc; a.ldk = Kc;
+        a.kW = kW; a.kH = kH;
+        a.off_x = flag == DECXB_CONV_ZERO_COMPENSATE ? -(int)(kW / 2) : 0;
+        a.off_y = flag == DECXB_CONV_ZERO_COMPENSATE ? -(int)(kH / 2) : 0;
+        a.out_h = g.out_h; a.eq_w = g.eq_w; a.Np = g.Np;
+        a.dst = dst; a.dst_img_stride = dst_stride;
+        rc = decxb_launch_conv_implicit(ctx, a, s);
+        scratch.release();
+        return rc;
+    }
+
     /* filter matrix [Np][Kp] (hi/lo), rows >= N zero so padding channels come out 0 */
     float *k_hi = nullptr, *k_lo = nullptr;
     if ((rc = scratch.get((size_t)g.Np * g.Kp * 4, (void**)&k_hi))) return rc;

@@ -116,6 +116,19 @@ struct decxb_gemm_args {
 };
 int decxb_launch_gemm_tn(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s);
 
+/* Implicit-GEMM convolution: the A tiles are boxes of the (split) source tensor, the filter
+ * matrix is [k_rows][ldk] with one 32-channel-padded block row per tap: column
+ * (tap * cblocks + cb) * 32 + c'. */
+struct decxb_conv_gemm_args {
+    const float *src_hi, *src_lo;     /* [batch][H][wp][dp]; lo NULL for plain TF32 */
+    int64_t dp, wp, H, batch, src_img_stride;
+    const float *k_hi, *k_lo; int64_t k_rows, k_cols, ldk;
+    int64_t kW, kH; int off_x, off_y;
+    int64_t out_h, eq_w, Np;
+    float* dst; int64_t dst_img_stride;
+};
+int decxb_launch_conv_implicit(decxb_ctx* ctx, const decxb_conv_gemm_args& a, cudaStream_t s);
+
 int decxb_launch_pack(decxb_ctx* ctx, const float* src, int64_t W, int64_t H, int64_t depth,
                       int64_t kW, int64_t kH, int flag, float* i2c, int64_t batch,
                       int64_t src_stride, int64_t i2c_stride, cudaStream_t s);
@@ -123,6 +136,6 @@ int decxb_launch_pack(decxb_ctx* ctx, const float* src, int64_t W, int64_t H, in
 /* Filter bank (TensorArray layout) -> hi/lo [rows_out][ld_out] matrices, filter n in row n. */
 int decxb_launch_filter_matrix(decxb_ctx* ctx, const float* filters, int64_t kW, int64_t kH, int64_t depth,
                                int64_t N, float* hi, float* lo, int64_t rows_out, int64_t ld_out, int raw,
-                               cudaStream_t s);
+                               cudaStream_t s, int64_t chan_pitch = 0);
 
 #endif

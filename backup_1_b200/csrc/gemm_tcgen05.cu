@@ -108,6 +108,22 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
         :: "r"(dst), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y) : "memory");
 }
 
+/* 4-D tiled loads (channel, x, y, image) for the implicit-GEMM convolution: the box is
+ * 32 channels x BX pixels x BY rows of one image, out-of-range pixels read as zero. */
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c, int x, int y, int n)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        :: "r"(dst), "l"(map), "r"(bar), "r"(c), "r"(x), "r"(y), "r"(n) : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c, int x, int y, int n)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        :: "r"(dst), "l"(map), "r"(bar_cluster_addr), "r"(c), "r"(x), "r"(y), "r"(n) : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -209,6 +225,14 @@ struct GemmParams {
     int tiles_m, tiles_n, num_kb;
     long long wait_limit_ns;
     decxb_dev_status* status;
+    /* implicit-GEMM convolution only: an M tile of one CTA is a BX x BY patch of output
+     * pixels of one image; a k-block is 32 channels of one filter tap */
+    int bx, by;                 /* patch size, bx * by = 128                                    */
+    int tiles_x, tiles_y;       /* patches per image row / CTA-group patches per image column    */
+    int out_h, eq_w;            /* output rows, pixels per output row (= wpitch of destination)  */
+    int kw, off_x, off_y;       /* filter width, source offset of tap (0,0)                      */
+    int cblocks;                /* 32-channel blocks per tap                                     */
+    int64_t dst_img_stride;     /* floats between destination images                             */
 };
 
 /* Bounded wait.  Returns false when it gave up (or another role already had). */
@@ -270,7 +294,7 @@ struct Cfg {
     static_assert(TMEM_COLS_RAW <= 512, "two accumulators must fit in TMEM");
 };
 
-template <int CTAS, int BN, int NSPLIT>
+template <int CTAS, int BN, int NSPLIT, bool CONV>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                        const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
@@ -321,29 +345,46 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
                 int tm, tn; tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
                 const int row_a = tm * C::UMMA_M + (int)cta_rank * BM_CTA;
                 const int row_b = tn * C::UMMA_N + (int)cta_rank * BN;
+                /* convolution: this CTA's patch of output pixels */
+                int img = 0, px0 = 0, py0 = 0;
+                if (CONV) {
+                    const int per_img = p.tiles_x * p.tiles_y;
+                    img = tm / per_img;
+                    const int r = tm - img * per_img;
+                    py0 = ((r / p.tiles_x) * CTAS + (int)cta_rank) * p.by;
+                    px0 = (r % p.tiles_x) * p.bx;
+                }
+                int tap = 0, cb = 0;       /* convolution: filter tap and channel block of this k-block */
                 for (int kb = 0; kb < p.num_kb; ++kb) {
                     if (!wait_bounded(empty_bar(stage), phase ^ 1u, p, 100 + stage, t)) { alive = false; break; }
                     const int kx = kb * BK;
+                    const int ky_t = CONV ? tap / p.kw : 0;
+                    const int cc = cb * BK, xx = px0 + (tap - ky_t * p.kw) + p.off_x, yy = py0 + ky_t + p.off_y;
                     if (CTAS == 1) {
                         const uint32_t fb = full_bar(stage);
                         mbar_arrive_expect_tx(fb, C::STAGE_BYTES);
-                        tma_load_2d(stage_a(stage, 0), &map_a_hi, fb, kx, row_a);
+                        if (CONV) tma_load_4d(stage_a(stage, 0), &map_a_hi, fb, cc, xx, yy, img);
+                        else      tma_load_2d(stage_a(stage, 0), &map_a_hi, fb, kx, row_a);
                         tma_load_2d(stage_b(stage, 0), &map_b_hi, fb, kx, row_b);
                         if (NSPLIT == 3) {
-                            tma_load_2d(stage_a(stage, 1), &map_a_lo, fb, kx, row_a);
+                            if (CONV) tma_load_4d(stage_a(stage, 1), &map_a_lo, fb, cc, xx, yy, img);
+                            else      tma_load_2d(stage_a(stage, 1), &map_a_lo, fb, kx, row_a);
                             tma_load_2d(stage_b(stage, 1), &map_b_lo, fb, kx, row_b);
                         }
                     } else {
                         /* Both CTAs' bytes are counted on the leader's barrier. */
                         if (is_leader) mbar_arrive_expect_tx(full_bar(stage), 2 * C::STAGE_BYTES);
                         const uint32_t fb = mapa(full_bar(stage), 0);
-                        tma_load_2d_pair(stage_a(stage, 0), &map_a_hi, fb, kx, row_a);
+                        if (CONV) tma_load_4d_pair(stage_a(stage, 0), &map_a_hi, fb, cc, xx, yy, img);
+                        else      tma_load_2d_pair(stage_a(stage, 0), &map_a_hi, fb, kx, row_a);
                         tma_load_2d_pair(stage_b(stage, 0), &map_b_hi, fb, kx, row_b);
                         if (NSPLIT == 3) {
-                            tma_load_2d_pair(stage_a(stage, 1), &map_a_lo, fb, kx, row_a);
+                            if (CONV) tma_load_4d_pair(stage_a(stage, 1), &map_a_lo, fb, cc, xx, yy, img);
+                            else      tma_load_2d_pair(stage_a(stage, 1), &map_a_lo, fb, kx, row_a);
                             tma_load_2d_pair(stage_b(stage, 1), &map_b_lo, fb, kx, row_b);
                         }
                     }
+                    if (CONV && ++cb == p.cblocks) { cb = 0; ++tap; }
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -400,18 +441,30 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
             const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
             if (!wait_bounded(tfull_bar(acc), acc_phase, p, 400 + acc, t)) { alive = false; break; }
             tc_fence_after();
-            const int64_t row = (int64_t)tm * C::UMMA_M + (int64_t)cta_rank * BM_CTA + q * 32 + lane;
+            int64_t row = (int64_t)tm * C::UMMA_M + (int64_t)cta_rank * BM_CTA + q * 32 + lane;
+            bool row_ok = row < p.M;
             const int64_t col0 = (int64_t)tn * C::UMMA_N;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * C::UMMA_N);
             float* __restrict__ drow = p.D + row * p.ldd;
-            const float* __restrict__ crow = p.C ? p.C + row * p.ldc : nullptr;
+            if (CONV) {
+                /* tile row i is pixel (px0 + i % bx, py0 + i / bx) of image img */
+                const int per_img = p.tiles_x * p.tiles_y;
+                const int img = tm / per_img;
+                const int r = tm - img * per_img;
+                const int i = q * 32 + lane;
+                const int y = ((r / p.tiles_x) * CTAS + (int)cta_rank) * p.by + i / p.bx;
+                const int x = (r % p.tiles_x) * p.bx + i % p.bx;
+                row_ok = (x < p.eq_w) && (y < p.out_h);
+                drow = p.D + (int64_t)img * p.dst_img_stride + ((int64_t)y * p.eq_w + x) * p.ldd;
+            }
+            const float* __restrict__ crow = (p.C && !CONV) ? p.C + row * p.ldc : nullptr;
 #pragma unroll 1
             for (int c = 0; c < C::UMMA_N; c += 32) {
                 if (col0 + c >= p.N) break;           /* warp-uniform */
                 float v[32];
                 tmem_ld_32x32(taddr + (uint32_t)c, v);
                 tmem_ld_wait();
-                if (row < p.M) {
+                if (row_ok) {
 #pragma unroll
                     for (int j = 0; j < 32; j += 4) {
                         const int64_t col = col0 + c + j;
@@ -484,11 +537,31 @@ int make_map(decxb_ctx* ctx, CUtensorMap* map, const float* base, int64_t rows, 
     return DECXB_OK;
 }
 
-template <int CTAS, int BN, int NSPLIT>
-int launch_cfg(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s)
+/* Source tensor [nb][H][wp][dp] as a 4-D map (channel, x, y, image); box = 32 x bx x by x 1. */
+int make_map_conv(decxb_ctx* ctx, CUtensorMap* map, const float* base, int64_t dp, int64_t wp, int64_t H, int64_t nb,
+                  int64_t img_stride, int bx, int by)
+{
+    auto fn = get_encode_fn();
+    if (!fn) return decxb_fail(ctx, DECXB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
+    if ((reinterpret_cast<uintptr_t>(base) & 15) || (dp % 4) || (img_stride % 4))
+        return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "TMA tensor operand must be 16-byte aligned");
+    cuuint64_t dims[4] = {(cuuint64_t)dp, (cuuint64_t)wp, (cuuint64_t)H, (cuuint64_t)nb};
+    cuuint64_t strides[3] = {(cuuint64_t)dp * 4, (cuuint64_t)wp * dp * 4, (cuuint64_t)img_stride * 4};
+    cuuint32_t box[4] = {(cuuint32_t)BK, (cuuint32_t)bx, (cuuint32_t)by, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return decxb_fail(ctx, DECXB_ERR_CUDA, "cuTensorMapEncodeTiled (4-D) failed: " + std::to_string((int)r));
+    return DECXB_OK;
+}
+
+template <int CTAS, int BN, int NSPLIT, bool CONV>
+int launch_kernel(decxb_ctx* ctx, const CUtensorMap& ma_hi, const CUtensorMap& ma_lo, const CUtensorMap& mb_hi,
+                  const CUtensorMap& mb_lo, const GemmParams& p, cudaStream_t s)
 {
     using C = Cfg<CTAS, BN, NSPLIT>;
-    auto kernel = decxb_gemm_tf32_kernel<CTAS, BN, NSPLIT>;
+    auto kernel = decxb_gemm_tf32_kernel<CTAS, BN, NSPLIT, CONV>;
     static std::once_flag once[16];
     static cudaError_t attr_err[16];
     const int dev = ctx->device & 15;
@@ -497,30 +570,10 @@ int launch_cfg(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s)
     });
     if (attr_err[dev] != cudaSuccess)
         return decxb_fail(ctx, DECXB_ERR_CUDA, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(attr_err[dev]));
-
-    CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
-    int rc;
-    if ((rc = make_map(ctx, &ma_hi, a.a_hi, a.M, a.K, a.lda, BM_CTA))) return rc;
-    if ((rc = make_map(ctx, &mb_hi, a.b_hi, a.b_rows, a.K, a.ldb, BN))) return rc;
-    if (NSPLIT == 3) {
-        if ((rc = make_map(ctx, &ma_lo, a.a_lo, a.M, a.K, a.lda, BM_CTA))) return rc;
-        if ((rc = make_map(ctx, &mb_lo, a.b_lo, a.b_rows, a.K, a.ldb, BN))) return rc;
-    } else { ma_lo = ma_hi; mb_lo = mb_hi; }
-
-    GemmParams p;
-    p.M = a.M; p.N = a.N; p.K = a.K;
-    p.C = a.C; p.ldc = a.ldc; p.D = a.D; p.ldd = a.ldd;
-    p.tiles_m = (int)decxb_ceil_div(a.M, C::UMMA_M);
-    p.tiles_n = (int)decxb_ceil_div(a.N, C::UMMA_N);
-    p.num_kb = (int)decxb_ceil_div(a.K, BK);
-    p.wait_limit_ns = ctx->wait_limit_ns;
-    p.status = ctx->d_status;
-
     const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
     int64_t clusters = ctx->sm_count / CTAS;
     if (clusters > tiles) clusters = tiles;
     if (clusters < 1) clusters = 1;
-
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(clusters * CTAS), 1, 1);
     cfg.blockDim = dim3(NUM_THREADS, 1, 1);
@@ -535,6 +588,71 @@ int launch_cfg(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s)
         DECXB_CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kernel, ma_hi, ma_lo, mb_hi, mb_lo, p));
     }
     return DECXB_OK;
+}
+
+template <int CTAS, int BN, int NSPLIT>
+int launch_conv_cfg(decxb_ctx* ctx, const decxb_conv_gemm_args& a, cudaStream_t s)
+{
+    using C = Cfg<CTAS, BN, NSPLIT>;
+    /* patch shape: bx * by = 128, the one that wastes the fewest rows on ragged edges */
+    int best_bx = 128; int64_t best_area = -1;
+    for (int bx = 128; bx >= 1; bx >>= 1) {
+        const int by = 128 / bx;
+        const int64_t area = decxb_ceil_to(a.eq_w, bx) * decxb_ceil_to(a.out_h, (int64_t)by * CTAS);
+        if (best_area < 0 || area < best_area) { best_area = area; best_bx = bx; }
+    }
+    const int bx = best_bx, by = 128 / best_bx;
+    const int64_t dp = a.dp, cblocks = decxb_ceil_div(dp, BK);
+    CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
+    int rc;
+    if ((rc = make_map_conv(ctx, &ma_hi, a.src_hi, dp, a.wp, a.H, a.batch, a.src_img_stride, bx, by))) return rc;
+    if ((rc = make_map(ctx, &mb_hi, a.k_hi, a.k_rows, a.k_cols, a.ldk, BN))) return rc;
+    if (NSPLIT == 3) {
+        if ((rc = make_map_conv(ctx, &ma_lo, a.src_lo, dp, a.wp, a.H, a.batch, a.src_img_stride, bx, by))) return rc;
+        if ((rc = make_map(ctx, &mb_lo, a.k_lo, a.k_rows, a.k_cols, a.ldk, BN))) return rc;
+    } else { ma_lo = ma_hi; mb_lo = mb_hi; }
+    GemmParams p = {};
+    p.bx = bx; p.by = by;
+    p.tiles_x = (int)decxb_ceil_div(a.eq_w, bx);
+    p.tiles_y = (int)decxb_ceil_div(a.out_h, (int64_t)by * CTAS);
+    p.out_h = (int)a.out_h; p.eq_w = (int)a.eq_w; p.kw = (int)a.kW; p.off_x = a.off_x; p.off_y = a.off_y;
+    p.cblocks = (int)cblocks;
+    p.dst_img_stride = a.dst_img_stride;
+    p.M = (int64_t)a.batch * p.tiles_x * p.tiles_y * C::UMMA_M;   /* rows of the tiled problem; real bounds are per pixel */
+    p.N = a.Np; p.K = a.k_cols;
+    p.C = nullptr; p.ldc = 0; p.D = a.dst; p.ldd = a.Np;
+    const int64_t tiles_m = (int64_t)a.batch * p.tiles_x * p.tiles_y;
+    if (tiles_m > 0x7fffffffLL) return decxb_fail(ctx, DECXB_ERR_TOO_LARGE, "convolution tiles");
+    p.tiles_m = (int)tiles_m;
+    p.tiles_n = (int)decxb_ceil_div(a.Np, C::UMMA_N);
+    p.num_kb = (int)(a.kW * a.kH * cblocks);
+    p.wait_limit_ns = ctx->wait_limit_ns;
+    p.status = ctx->d_status;
+    return launch_kernel<CTAS, BN, NSPLIT, true>(ctx, ma_hi, ma_lo, mb_hi, mb_lo, p, s);
+}
+
+template <int CTAS, int BN, int NSPLIT>
+int launch_cfg(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s)
+{
+    using C = Cfg<CTAS, BN, NSPLIT>;
+    CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
+    int rc;
+    if ((rc = make_map(ctx, &ma_hi, a.a_hi, a.M, a.K, a.lda, BM_CTA))) return rc;
+    if ((rc = make_map(ctx, &mb_hi, a.b_hi, a.b_rows, a.K, a.ldb, BN))) return rc;
+    if (NSPLIT == 3) {
+        if ((rc = make_map(ctx, &ma_lo, a.a_lo, a.M, a.K, a.lda, BM_CTA))) return rc;
+        if ((rc = make_map(ctx, &mb_lo, a.b_lo, a.b_rows, a.K, a.ldb, BN))) return rc;
+    } else { ma_lo = ma_hi; mb_lo = mb_hi; }
+
+    GemmParams p = {};
+    p.M = a.M; p.N = a.N; p.K = a.K;
+    p.C = a.C; p.ldc = a.ldc; p.D = a.D; p.ldd = a.ldd;
+    p.tiles_m = (int)decxb_ceil_div(a.M, C::UMMA_M);
+    p.tiles_n = (int)decxb_ceil_div(a.N, C::UMMA_N);
+    p.num_kb = (int)decxb_ceil_div(a.K, BK);
+    p.wait_limit_ns = ctx->wait_limit_ns;
+    p.status = ctx->d_status;
+    return launch_kernel<CTAS, BN, NSPLIT, false>(ctx, ma_hi, ma_lo, mb_hi, mb_lo, p, s);
 }
 
 }  // namespace
@@ -557,4 +675,12 @@ int decxb_launch_gemm_tn(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t 
     case DECXB_TILE_1CTA_128x64:  return x3 ? launch_cfg<1, 64, 3>(ctx, a, s)  : launch_cfg<1, 64, 1>(ctx, a, s);
     default: return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "unknown gemm tile");
     }
+}
+
+int decxb_launch_conv_implicit(decxb_ctx* ctx, const decxb_conv_gemm_args& a, cudaStream_t s)
+{
+    const bool x3 = a.src_lo != nullptr;
+    if (a.Np <= 64)  return x3 ? launch_conv_cfg<1, 64, 3>(ctx, a, s)  : launch_conv_cfg<1, 64, 1>(ctx, a, s);
+    if (a.Np <= 128) return x3 ? launch_conv_cfg<1, 128, 3>(ctx, a, s) : launch_conv_cfg<1, 128, 1>(ctx, a, s);
+    return x3 ? launch_conv_cfg<2, 128, 3>(ctx, a, s) : launch_conv_cfg<2, 128, 1>(ctx, a, s);
 }

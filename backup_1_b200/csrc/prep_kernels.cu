@@ -174,13 +174,15 @@ int decxb_launch_split_transpose(decxb_ctx* ctx, const float* in, int64_t K, int
     return DECXB_OK;
 }
 
-/* Filter bank -> matrix.  Row n, column (ky*kW + kx)*dp + c  <-  filters[n][ky][kx][c]
- * (TensorArray layout [N][kH][ceil4(kW)][dp]).  Rows n >= N and columns >= Kp are zero. */
+/* Filter bank -> matrix.  Row n, column (ky*kW + kx)*cp + c  <-  filters[n][ky][kx][c]
+ * (TensorArray layout [N][kH][ceil4(kW)][dp]); cp = dp for the explicit path, cp = ceil32(dp)
+ * for the implicit path (one 32-channel-padded block row per tap).  Rows n >= N, channels
+ * c >= dp and columns >= kW*kH*cp are zero. */
 __global__ void __launch_bounds__(256)
-decxb_filter_matrix_kernel(const float* __restrict__ filters, int kW, int kH, int dp, int64_t N,
+decxb_filter_matrix_kernel(const float* __restrict__ filters, int kW, int kH, int dp, int cp, int64_t N,
                            float* __restrict__ hi, float* __restrict__ lo, int64_t rows_out, int64_t ld_out, int raw)
 {
-    const int64_t Kp = (int64_t)kW * kH * dp;
+    const int64_t Kp = (int64_t)kW * kH * cp;
     const int64_t kwp = (kW + 3) / 4 * 4;
     const int64_t gap = (int64_t)dp * kwp * kH;
     const int64_t total = rows_out * ld_out;
@@ -189,9 +191,9 @@ decxb_filter_matrix_kernel(const float* __restrict__ filters, int kW, int kH, in
         const int64_t n = i / ld_out, k = i - n * ld_out;
         float a = 0.0f;
         if (n < N && k < Kp) {
-            const int64_t tap = k / dp, c = k - tap * dp;
+            const int64_t tap = k / cp, c = k - tap * cp;
             const int64_t ky = tap / kW, kx = tap - ky * kW;
-            a = __ldg(filters + n * gap + (ky * kwp + kx) * dp + c);
+            if (c < dp) a = __ldg(filters + n * gap + (ky * kwp + kx) * dp + c);
         }
         if (raw) { hi[i] = a; }
         else { float h, l; split1(a, h, l); hi[i] = h; lo[i] = l; }
@@ -200,16 +202,17 @@ decxb_filter_matrix_kernel(const float* __restrict__ filters, int kW, int kH, in
 
 int decxb_launch_filter_matrix(decxb_ctx* ctx, const float* filters, int64_t kW, int64_t kH, int64_t depth,
                                int64_t N, float* hi, float* lo, int64_t rows_out, int64_t ld_out, int raw,
-                               cudaStream_t s)
+                               cudaStream_t s, int64_t chan_pitch)
 {
     const int64_t dp = decxb_ceil_to(depth, 4);
+    const int64_t cp = chan_pitch > 0 ? chan_pitch : dp;
     const int64_t total = rows_out * ld_out;
     if (total == 0) return DECXB_OK;
     int64_t blocks = (total + 255) / 256;
     if (blocks > (int64_t)ctx->sm_count * 16) blocks = (int64_t)ctx->sm_count * 16;
     {
         decxb_launch_scope scope(ctx, s, DECXB_K_SPLIT);
-        decxb_filter_matrix_kernel<<<(int)blocks, 256, 0, s>>>(filters, (int)kW, (int)kH, (int)dp, N, hi, lo, rows_out, ld_out, raw);
+        decxb_filter_matrix_kernel<<<(int)blocks, 256, 0, s>>>(filters, (int)kW, (int)kH, (int)dp, (int)cp, N, hi, lo, rows_out, ld_out, raw);
     }
     DECXB_CUDA_TRY(ctx, cudaGetLastError());
     return DECXB_OK;

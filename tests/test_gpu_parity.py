@@ -240,18 +240,34 @@ def run_conv(ctx, src, W, depth, flt, kW, flag, mode=b.GEMM_3XTF32, algo=b.CONV_
     return r if src.ndim == 4 else r[0]
 
 
-@pytest.mark.parametrize("case", CONV_CASES)
-def test_conv_matches_oracle(ctx, case):
+ALGOS = [b.CONV_EXPLICIT, b.CONV_IMPLICIT]
+
+
+@pytest.mark.parametrize("algo", ALGOS)
+@pytest.mark.parametrize("case", CONV_CASES + [(130, 37, 40, 3, 3, 200, 1), (33, 70, 132, 5, 5, 300, 0)])
+def test_conv_matches_oracle(ctx, case, algo):
     W, H, C, kW, kH, N, flag = case
     src = o.make_tensor(W, H, C, 4)
     flt = o.make_filters(kW, kH, C, N, 5)
     R = o.conv2_im2col(src, W, C, flt, kW, flag)
     K = kW * kH * o.ceil4(C)
-    D = run_conv(ctx, src, W, C, flt, kW, flag)
+    D = run_conv(ctx, src, W, C, flt, kW, flag, algo=algo)
+    assert not np.isnan(D).any(), "every element of the padded destination must be written"
     assert o.norm_err(D, R, K, 1.0, 1.0) <= TOL_3X
     assert np.all(D[..., N:] == 0), "padding channels must be zero"
-    Dh = run_conv(ctx, src, W, C, flt, kW, flag, host=True)
+    Dh = run_conv(ctx, src, W, C, flt, kW, flag, algo=algo, host=True)
     assert np.array_equal(D, Dh), "host-resident path must give the device path's bits"
+
+
+@pytest.mark.parametrize("algo", ALGOS)
+def test_conv_plain_tf32_is_opt_in(ctx, algo):
+    W, H, C, kW, N = 40, 24, 48, 3, 96
+    src = o.make_tensor(W, H, C, 4)
+    flt = o.make_filters(kW, kW, C, N, 5)
+    R = o.conv2_im2col(src, W, C, flt, kW, 1)
+    e1 = o.norm_err(run_conv(ctx, src, W, C, flt, kW, 1, mode=b.GEMM_1XTF32, algo=algo), R, kW * kW * C, 1.0, 1.0)
+    e3 = o.norm_err(run_conv(ctx, src, W, C, flt, kW, 1, algo=algo), R, kW * kW * C, 1.0, 1.0)
+    assert e3 <= TOL_3X < e1 <= TOL_1X
 
 
 def test_conv_golden_vectors_of_reference_driver(ctx, golden):
@@ -267,22 +283,39 @@ def test_conv_golden_vectors_of_reference_driver(ctx, golden):
         assert o.norm_err(D, z[name], K, 1.0, 1.0) <= TOL_3X, name
 
 
-def test_conv_batched_equals_per_image(ctx):
+@pytest.mark.parametrize("algo", ALGOS)
+def test_conv_batched_equals_per_image(ctx, algo):
     W, H, C, kW, N, nb = 20, 12, 16, 3, 24, 6
     imgs = np.stack([o.make_tensor(W, H, C, 4, first_index=i * 7919) for i in range(nb)])
     flt = o.make_filters(kW, kW, C, N, 5)
-    D = run_conv(ctx, imgs, W, C, flt, kW, 1)
+    D = run_conv(ctx, imgs, W, C, flt, kW, 1, algo=algo)
+    assert not np.isnan(D).any()
     for i in range(nb):
-        assert np.array_equal(D[i], run_conv(ctx, imgs[i], W, C, flt, kW, 1))
+        assert np.array_equal(D[i], run_conv(ctx, imgs[i], W, C, flt, kW, 1, algo=algo))
 
 
-def test_conv_config3_full_size(ctx):
+def test_conv_config4_shape_batched_implicit(ctx):
+    """BASELINE config 4's per-image shape (56x56x256 -> 256 filters 3x3) on 4 images; one
+    image against the oracle (the 2-CTA tile path of the implicit kernel)."""
+    W = H = 56; C = 256; N = 256; kW = 3; nb = 4
+    imgs = np.stack([o.make_tensor(W, H, C, 4, first_index=i * 1000003) for i in range(nb)])
+    flt = o.make_filters(kW, kW, C, N, 5)
+    D = run_conv(ctx, imgs, W, C, flt, kW, 1, algo=b.CONV_IMPLICIT)
+    De = run_conv(ctx, imgs, W, C, flt, kW, 1, algo=b.CONV_EXPLICIT)
+    R = o.conv2_im2col(imgs[2], W, C, flt, kW, 1)
+    K = kW * kW * C
+    assert o.norm_err(D[2], R, K, 1.0, 1.0) <= TOL_3X
+    assert o.norm_err(D, De, K, 1.0, 1.0) <= TOL_3X
+
+
+@pytest.mark.parametrize("algo", ALGOS)
+def test_conv_config3_full_size(ctx, algo):
     """BASELINE config 3: 224x224x64 -> 64 filters 3x3, zero border.  Sampled output rows
     against the oracle GEMM over the oracle pack."""
     W = H = 224; C = 64; N = 64; kW = 3
     src = o.make_tensor(W, H, C, 4)
     flt = o.make_filters(kW, kW, C, N, 5)
-    D = run_conv(ctx, src, W, C, flt, kW, 1).reshape(-1, N)
+    D = run_conv(ctx, src, W, C, flt, kW, 1, algo=algo).reshape(-1, N)
     P = o.im2col_pack(src, W, C, kW, kW, 1)
     Km = o.kernel_matrix(flt, kW, C)
     rows = np.arange(0, P.shape[0], 97)
