@@ -32,6 +32,49 @@ struct Scratch {
 
 bool tma_ok(const float* p, int64_t ld) { return ((uintptr_t)p % 16 == 0) && (ld % 4 == 0); }
 
+/* B operand as the kernel wants it: K-contiguous hi (and lo) parts. */
+struct PreparedB { const float* hi; const float* lo; int64_t ld; };
+
+int prepare_b(decxb_ctx* ctx, Scratch& scratch, bool x3, int64_t N, int64_t K,
+              const float* B, int64_t ldb, bool b_is_nt, cudaStream_t s, PreparedB* out)
+{
+    const int64_t Kp = decxb_ceil_to(K, 4);
+    int rc;
+    if (b_is_nt && !x3 && tma_ok(B, ldb)) { out->hi = B; out->lo = nullptr; out->ld = ldb; return DECXB_OK; }
+    float *hi = nullptr, *lo = nullptr;
+    if ((rc = scratch.get((size_t)N * Kp * sizeof(float), (void**)&hi))) return rc;
+    if (x3 && (rc = scratch.get((size_t)N * Kp * sizeof(float), (void**)&lo))) return rc;
+    if (b_is_nt) {
+        if (x3) { if ((rc = decxb_launch_split_rows(ctx, B, N, K, ldb, hi, lo, Kp, N, s))) return rc; }
+        else    { DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(hi, Kp * 4, B, ldb * 4, K * 4, N, cudaMemcpyDeviceToDevice, s)); }
+    } else {
+        if ((rc = decxb_launch_split_transpose(ctx, B, K, N, ldb, hi, lo, Kp, x3 ? 0 : 1, s))) return rc;
+    }
+    out->hi = hi; out->lo = lo; out->ld = Kp;
+    return DECXB_OK;
+}
+
+/* D = A * B (+C) with B already prepared; A is split (3xTF32) or used in place. */
+int gemm_prepared(decxb_ctx* ctx, Scratch& scratch, bool x3, int tile, int64_t M, int64_t N, int64_t K,
+                  const float* A, int64_t lda, const PreparedB& pb,
+                  const float* C, int64_t ldc, float* D, int64_t ldd, cudaStream_t s)
+{
+    const int64_t Kp = decxb_ceil_to(K, 4);
+    decxb_gemm_args g = {};
+    g.M = M; g.N = N; g.K = K; g.C = C; g.ldc = ldc; g.D = D; g.ldd = ldd; g.tile = tile; g.b_rows = N;
+    g.b_hi = pb.hi; g.b_lo = pb.lo; g.ldb = pb.ld;
+    int rc;
+    if (x3 || !tma_ok(A, lda)) {
+        float *hi = nullptr, *lo = nullptr;
+        if ((rc = scratch.get((size_t)M * Kp * sizeof(float), (void**)&hi))) return rc;
+        if (x3 && (rc = scratch.get((size_t)M * Kp * sizeof(float), (void**)&lo))) return rc;
+        if (x3) { if ((rc = decxb_launch_split_rows(ctx, A, M, K, lda, hi, lo, Kp, M, s))) return rc; }
+        else    { DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(hi, Kp * 4, A, lda * 4, K * 4, M, cudaMemcpyDeviceToDevice, s)); }
+        g.a_hi = hi; g.a_lo = lo; g.lda = Kp;
+    } else { g.a_hi = A; g.a_lo = nullptr; g.lda = lda; }
+    return decxb_launch_gemm_tn(ctx, g, s);
+}
+
 /* D = A * op(B) (+C).  b_is_nt: B given as Bt[N][K]. */
 int gemm_device(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_t K,
                 const float* A, int64_t lda, const float* B, int64_t ldb, bool b_is_nt,
@@ -42,44 +85,45 @@ int gemm_device(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_
     if (!A || !B || !D) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null operand");
     if (lda < K || ldb < (b_is_nt ? K : N) || ldd < N || (C && ldc < N))
         return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
-
     Scratch scratch(ctx, s);
-    const int64_t Kp = decxb_ceil_to(K, 4);
-    decxb_gemm_args g = {};
-    g.M = M; g.N = N; g.K = K; g.C = C; g.ldc = ldc; g.D = D; g.ldd = ldd; g.tile = tile; g.b_rows = N;
-    int rc;
     const bool x3 = mode == DECXB_GEMM_3XTF32;
-
-    /* A operand */
-    if (x3 || !tma_ok(A, lda)) {
-        float *hi = nullptr, *lo = nullptr;
-        if ((rc = scratch.get((size_t)M * Kp * sizeof(float), (void**)&hi))) return rc;
-        if (x3 && (rc = scratch.get((size_t)M * Kp * sizeof(float), (void**)&lo))) return rc;
-        if (x3) { if ((rc = decxb_launch_split_rows(ctx, A, M, K, lda, hi, lo, Kp, M, s))) return rc; }
-        else    { DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(hi, Kp * 4, A, lda * 4, K * 4, M, cudaMemcpyDeviceToDevice, s)); }
-        g.a_hi = hi; g.a_lo = lo; g.lda = Kp;
-    } else { g.a_hi = A; g.a_lo = nullptr; g.lda = lda; }
-
-    /* B operand */
-    if (b_is_nt) {
-        if (x3 || !tma_ok(B, ldb)) {
-            float *hi = nullptr, *lo = nullptr;
-            if ((rc = scratch.get((size_t)N * Kp * sizeof(float), (void**)&hi))) return rc;
-            if (x3 && (rc = scratch.get((size_t)N * Kp * sizeof(float), (void**)&lo))) return rc;
-            if (x3) { if ((rc = decxb_launch_split_rows(ctx, B, N, K, ldb, hi, lo, Kp, N, s))) return rc; }
-            else    { DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(hi, Kp * 4, B, ldb * 4, K * 4, N, cudaMemcpyDeviceToDevice, s)); }
-            g.b_hi = hi; g.b_lo = lo; g.ldb = Kp;
-        } else { g.b_hi = B; g.b_lo = nullptr; g.ldb = ldb; }
-    } else {
-        float *hi = nullptr, *lo = nullptr;
-        if ((rc = scratch.get((size_t)N * Kp * sizeof(float), (void**)&hi))) return rc;
-        if (x3 && (rc = scratch.get((size_t)N * Kp * sizeof(float), (void**)&lo))) return rc;
-        if ((rc = decxb_launch_split_transpose(ctx, B, K, N, ldb, hi, lo, Kp, x3 ? 0 : 1, s))) return rc;
-        g.b_hi = hi; g.b_lo = lo; g.ldb = Kp;
-    }
-    rc = decxb_launch_gemm_tn(ctx, g, s);
+    PreparedB pb;
+    int rc = prepare_b(ctx, scratch, x3, N, K, B, ldb, b_is_nt, s, &pb);
+    if (rc == DECXB_OK) rc = gemm_prepared(ctx, scratch, x3, tile, M, N, K, A, lda, pb, C, ldc, D, ldd, s);
     scratch.release();
     return rc;
+}
+
+/* Events of one host-resident call: upload of chunk i done / compute of chunk i done. */
+struct ChunkEvents {
+    std::vector<cudaEvent_t> ev;
+    cudaEvent_t make()
+    {
+        cudaEvent_t e = nullptr;
+        if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        ev.push_back(e);
+        return e;
+    }
+    ~ChunkEvents() { for (cudaEvent_t e : ev) cudaEventDestroy(e); }
+};
+
+/* Makes the two copy streams start after whatever is queued on the compute stream. */
+int fence_copy_streams(decxb_ctx* ctx, ChunkEvents& evs)
+{
+    cudaEvent_t e = evs.make();
+    if (!e) return decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate");
+    DECXB_CUDA_TRY(ctx, cudaEventRecord(e, ctx->stream));
+    DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->copy_stream[0], e, 0));
+    DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->copy_stream[1], e, 0));
+    return DECXB_OK;
+}
+
+int sync_all_streams(decxb_ctx* ctx)
+{
+    DECXB_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->copy_stream[0]));
+    DECXB_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    DECXB_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->copy_stream[1]));
+    return DECXB_OK;
 }
 
 cudaStream_t pick_stream(decxb_ctx* ctx, void* stream) { return stream ? (cudaStream_t)stream : ctx->stream; }
@@ -114,21 +158,50 @@ extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M
     if (!hA || !hB || !hD) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null operand");
     if (lda < K || ldb < N || ldd < N || (hC && ldc < N))
         return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
-    cudaStream_t s = ctx->stream;
+    if (mode != DECXB_GEMM_3XTF32 && mode != DECXB_GEMM_1XTF32) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "gemm mode");
+    /* Three streams: uploads, compute, downloads.  B goes up first and is prepared once; A
+     * (and C) go up in row-blocks, each multiplied as soon as it has landed while the next one
+     * is in flight and the previous result block is on its way back.  (The reference does the
+     * three phases one after the other on one stream, GEMM.h:106-123.) */
+    cudaStream_t s = ctx->stream, up = ctx->copy_stream[0], down = ctx->copy_stream[1];
     Scratch scratch(ctx, s);
+    ChunkEvents evs;
+    const bool x3 = mode == DECXB_GEMM_3XTF32;
     const int64_t Kp = decxb_ceil_to(K, 4), Np = decxb_ceil_to(N, 4);
     float *dA, *dB, *dC = nullptr, *dD;
     if ((rc = scratch.get((size_t)M * Kp * 4, (void**)&dA))) return rc;
     if ((rc = scratch.get((size_t)K * Np * 4, (void**)&dB))) return rc;
     if ((rc = scratch.get((size_t)M * Np * 4, (void**)&dD))) return rc;
     if (hC && (rc = scratch.get((size_t)M * Np * 4, (void**)&dC))) return rc;
-    DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dA, Kp * 4, hA, lda * 4, K * 4, M, cudaMemcpyHostToDevice, s));
-    DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dB, Np * 4, hB, ldb * 4, N * 4, K, cudaMemcpyHostToDevice, s));
-    if (hC) DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dC, Np * 4, hC, ldc * 4, N * 4, M, cudaMemcpyHostToDevice, s));
-    rc = gemm_device(ctx, mode, tile, M, N, K, dA, Kp, dB, Np, false, dC, Np, dD, Np, s);
-    if (rc) { cudaStreamSynchronize(s); return rc; }
-    DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(hD, ldd * 4, dD, Np * 4, N * 4, M, cudaMemcpyDeviceToHost, s));
-    DECXB_CUDA_TRY(ctx, cudaStreamSynchronize(s));
+    if ((rc = fence_copy_streams(ctx, evs))) return rc;
+    /* row-blocks of about 1/8 of M, multiples of 256 rows, at least 512 */
+    int64_t rows = decxb_ceil_to(decxb_ceil_div(M, 8), 256);
+    if (rows < 512) rows = 512;
+    if (rows > M) rows = M;
+    cudaEvent_t eb = evs.make();
+    if (!eb) return decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate");
+    DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dB, Np * 4, hB, ldb * 4, N * 4, K, cudaMemcpyHostToDevice, up));
+    DECXB_CUDA_TRY(ctx, cudaEventRecord(eb, up));
+    DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(s, eb, 0));
+    PreparedB pb;
+    if ((rc = prepare_b(ctx, scratch, x3, N, K, dB, Np, false, s, &pb))) { sync_all_streams(ctx); return rc; }
+    for (int64_t r0 = 0; r0 < M; r0 += rows) {
+        const int64_t nr = M - r0 < rows ? M - r0 : rows;
+        cudaEvent_t e_up = evs.make(), e_done = evs.make();
+        if (!e_up || !e_done) { sync_all_streams(ctx); return decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"); }
+        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dA + r0 * Kp, Kp * 4, hA + r0 * lda, lda * 4, K * 4, nr, cudaMemcpyHostToDevice, up));
+        if (hC) DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dC + r0 * Np, Np * 4, hC + r0 * ldc, ldc * 4, N * 4, nr, cudaMemcpyHostToDevice, up));
+        DECXB_CUDA_TRY(ctx, cudaEventRecord(e_up, up));
+        DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(s, e_up, 0));
+        rc = gemm_prepared(ctx, scratch, x3, tile, nr, N, K, dA + r0 * Kp, Kp, pb, dC ? dC + r0 * Np : nullptr, Np,
+                           dD + r0 * Np, Np, s);
+        if (rc) { sync_all_streams(ctx); return rc; }
+        DECXB_CUDA_TRY(ctx, cudaEventRecord(e_done, s));
+        DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(down, e_done, 0));
+        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(hD + r0 * ldd, ldd * 4, dD + r0 * Np, Np * 4, N * 4, nr, cudaMemcpyDeviceToHost, down));
+    }
+    if ((rc = sync_all_streams(ctx))) return rc;
+    scratch.release();
     return decxb_check_dev_status(ctx);
 }
 
@@ -286,19 +359,39 @@ extern "C" int decxb_conv2_im2col_f32_host(decxb_ctx* ctx, int mode, int algo, i
     const int64_t src_img = H * wp * dp, dst_img = g.M * g.Np;
     if (src_stride == 0) src_stride = src_img;
     if (dst_stride == 0) dst_stride = dst_img;
-    cudaStream_t s = ctx->stream;
+    /* uploads, compute and downloads on three streams, pipelined over groups of images; the
+     * filter bank goes up in one copy (the reference issues one 2-D copy per filter,
+     * conv2_mk_im2col.h:226-231) */
+    cudaStream_t s = ctx->stream, up = ctx->copy_stream[0], down = ctx->copy_stream[1];
     Scratch scratch(ctx, s);
+    ChunkEvents evs;
     float *d_src, *d_flt, *d_dst;
     if ((rc = scratch.get((size_t)batch * src_img * 4, (void**)&d_src))) return rc;
     if ((rc = scratch.get((size_t)N * kH * kwp * dp * 4, (void**)&d_flt))) return rc;
     if ((rc = scratch.get((size_t)batch * dst_img * 4, (void**)&d_dst))) return rc;
-    /* one copy for the whole filter bank (the reference issues one 2-D copy per filter,
-     * conv2_mk_im2col.h:226-231), one strided copy for all images */
-    DECXB_CUDA_TRY(ctx, cudaMemcpyAsync(d_flt, h_filters, (size_t)N * kH * kwp * dp * 4, cudaMemcpyHostToDevice, s));
-    DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(d_src, src_img * 4, h_src, src_stride * 4, src_img * 4, batch, cudaMemcpyHostToDevice, s));
-    rc = conv_device(ctx, mode, algo, flag, d_src, W, H, depth, d_flt, kW, kH, N, d_dst, batch, src_img, dst_img, s);
-    if (rc) { cudaStreamSynchronize(s); return rc; }
-    DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(h_dst, dst_stride * 4, d_dst, dst_img * 4, dst_img * 4, batch, cudaMemcpyDeviceToHost, s));
-    DECXB_CUDA_TRY(ctx, cudaStreamSynchronize(s));
+    if ((rc = fence_copy_streams(ctx, evs))) return rc;
+    DECXB_CUDA_TRY(ctx, cudaMemcpyAsync(d_flt, h_filters, (size_t)N * kH * kwp * dp * 4, cudaMemcpyHostToDevice, up));
+    int64_t group = decxb_ceil_div(batch, 8);
+    const int64_t min_group = decxb_ceil_div((int64_t)8 << 20, src_img * 4);      /* at least 8 MiB per upload */
+    if (group < min_group) group = min_group;
+    if (group > batch) group = batch;
+    for (int64_t b0 = 0; b0 < batch; b0 += group) {
+        const int64_t nb = batch - b0 < group ? batch - b0 : group;
+        cudaEvent_t e_up = evs.make(), e_done = evs.make();
+        if (!e_up || !e_done) { sync_all_streams(ctx); return decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"); }
+        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(d_src + b0 * src_img, src_img * 4, h_src + b0 * src_stride, src_stride * 4,
+                                             src_img * 4, nb, cudaMemcpyHostToDevice, up));
+        DECXB_CUDA_TRY(ctx, cudaEventRecord(e_up, up));
+        DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(s, e_up, 0));
+        rc = conv_device(ctx, mode, algo, flag, d_src + b0 * src_img, W, H, depth, d_flt, kW, kH, N, d_dst + b0 * dst_img,
+                         nb, src_img, dst_img, s);
+        if (rc) { sync_all_streams(ctx); return rc; }
+        DECXB_CUDA_TRY(ctx, cudaEventRecord(e_done, s));
+        DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(down, e_done, 0));
+        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(h_dst + b0 * dst_stride, dst_stride * 4, d_dst + b0 * dst_img, dst_img * 4,
+                                             dst_img * 4, nb, cudaMemcpyDeviceToHost, down));
+    }
+    if ((rc = sync_all_streams(ctx))) return rc;
+    scratch.release();
     return decxb_check_dev_status(ctx);
 }

@@ -664,9 +664,19 @@ int decxb_launch_gemm_tn(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t 
     const bool x3 = a.a_lo != nullptr;
     int tile = a.tile;
     if (tile == DECXB_TILE_AUTO) {
-        if (a.N <= 64) tile = DECXB_TILE_1CTA_128x64;
-        else if (a.N <= 128 || a.M <= 128) tile = DECXB_TILE_1CTA_128x128;
-        else tile = DECXB_TILE_2CTA_256x256;
+        /* cost = waves x accumulator area per SM x relative cost per unit of area; the relative
+         * costs were measured on B200 at M=8192 N=4096 K=2048 and at 1024^3 (bigger tiles move
+         * fewer shared-memory bytes per flop; small problems need more tiles than SMs) */
+        struct Cand { int tile, tm, tn, sms_per_tile; double area, rel; };
+        const Cand cands[4] = {{DECXB_TILE_2CTA_256x256, 256, 256, 2, 32768, 1.00}, {DECXB_TILE_1CTA_128x256, 128, 256, 1, 32768, 1.18},
+                               {DECXB_TILE_1CTA_128x128, 128, 128, 1, 16384, 1.24}, {DECXB_TILE_1CTA_128x64, 128, 64, 1, 8192, 2.20}};
+        double best = -1;
+        for (const Cand& c : cands) {
+            const int64_t tiles = decxb_ceil_div(a.M, c.tm) * decxb_ceil_div(a.N, c.tn);
+            const int64_t slots = ctx->sm_count / c.sms_per_tile > 0 ? ctx->sm_count / c.sms_per_tile : 1;
+            const double cost = (double)decxb_ceil_div(tiles, slots) * c.area * c.rel;
+            if (best < 0 || cost < best * 0.999) { best = cost; tile = c.tile; }
+        }
     }
     switch (tile) {
     case DECXB_TILE_1CTA_128x128: return x3 ? launch_cfg<1, 128, 3>(ctx, a, s) : launch_cfg<1, 128, 1>(ctx, a, s);

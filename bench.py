@@ -154,7 +154,7 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--mode", default="3xtf32", choices=["3xtf32", "1xtf32"])
     ap.add_argument("--tile", type=int, default=0)
-    ap.add_argument("--algo", default="explicit", choices=["explicit", "implicit"])
+    ap.add_argument("--algo", default="implicit", choices=["explicit", "implicit"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--gather", action="store_true", help="also all-gather the C row-blocks over NCCL (timed separately)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -170,6 +170,7 @@ def main():
     import torch.distributed as dist
 
     import backup_1_b200 as b
+    from backup_1_b200 import shard
 
     rank, world, local = dist_env()
     if world > 1:
@@ -192,8 +193,8 @@ def main():
     if wl["kind"] == "gemm":
         M, N, K = wl["M"], wl["N"], wl["K"]
         if wl["scaling"] == "strong":
-            assert M % world == 0
-            M_rank, row0 = M // world, rank * (M // world)
+            r0, r1 = shard.gemm_row_shard(M, world, rank)
+            M_rank, row0 = r1 - r0, r0
         else:
             M_rank, row0 = M, rank * M
         dA = torch.empty((M_rank, K), device=dev); dB = torch.empty((K, N), device=dev); dD = torch.empty((M_rank, N), device=dev)
@@ -215,8 +216,8 @@ def main():
     else:
         W, H, C, kW, kH, F, batch = (wl[k] for k in ("W", "H", "C", "kW", "kH", "F", "batch"))
         if wl["scaling"] == "strong":
-            assert batch % world == 0
-            nb, img0 = batch // world, rank * (batch // world)
+            b0, b1 = shard.conv_batch_shard(batch, world, rank)
+            nb, img0 = b1 - b0, b0
         else:
             nb, img0 = batch, rank * batch
         g = b.conv_geometry(W, H, C, kW, kH, F, 1)
