@@ -128,13 +128,22 @@ def run_reference(args, wl, name):
     # bounded sample: a row-block of the workload sized so that steps+warmup stay within ~2 minutes
     tx, ty = o.ref_cpu_threads(4096, N)
     probe_m = 128 * tx
-    t_probe = o.ref_cpu_gemm(probe_m, N, K, reps=2, split=(tx, ty))["best_s"]
+    try:
+        t_probe = o.ref_cpu_gemm(probe_m, N, K, reps=2, split=(tx, ty))["best_s"]
+    except Exception as ex:
+        print(json.dumps({"impl": "reference", "unavailable": f"reference CPU GEMM did not run: {str(ex)[:160]}"}))
+        return
     budget_s = 120.0 / max(args.steps + args.warmup, 1)
     rows = int(min(M, max(probe_m, budget_s / max(t_probe, 1e-6) * probe_m)))
     rows = max(probe_m, rows // (32 * tx) * (32 * tx))
     if wl["kind"] == "conv":
         rows = min(rows, (M // (32 * tx)) * (32 * tx)) or probe_m
-    r = o.ref_cpu_gemm(rows, N, K, reps=args.steps + args.warmup, split=(tx, ty), timeout=900)
+    try:
+        r = o.ref_cpu_gemm(rows, N, K, reps=args.steps + args.warmup, split=(tx, ty), timeout=900)
+    except Exception as ex:
+        print(json.dumps({"impl": "reference", "unavailable": f"reference CPU GEMM did not run: {str(ex)[:160]}"}))
+        return
+    tx, ty = (int(v) for v in r["split"].split("x"))
     tflops = 2.0 * rows * N * K / r["median_s"] / 1e12
     sample = f"{rows} of {M} rows x N={N} x K={K}, decx::sgemm_caller<{tx},{ty}>, median of {args.steps + args.warmup} runs"
     base.update(value=tflops, ms_per_step=r["median_s"] * 1e3 * (M / rows),

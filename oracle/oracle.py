@@ -258,12 +258,23 @@ def ref_cpu_gemm(M: int, N: int, K: int, A="seed:1", B="seed:2", reps: int = 3, 
     """Run the reference's CPU GEMM in a child process limited to <=16 CPUs.
     A/B are 'seed:<n>' or file names of raw float32 data."""
     tx, ty = split or ref_cpu_threads(M, N)
-    cpus = sorted(os.sched_getaffinity(0))[: max(tx * ty, 1)]
-    cmd = [str(HERE / "_ref" / "decx_ref_cpu"), "gemm", str(M), str(N), str(K), f"{tx}x{ty}", str(reps), A, B, out]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout,
-                       preexec_fn=lambda: os.sched_setaffinity(0, cpus))
-    if r.returncode != 0:
-        raise RuntimeError(f"decx_ref_cpu failed rc={r.returncode}: {r.stderr.strip()}")
+    # The reference's thread pool has start-up races of its own (its mutexes are never taken,
+    # srcs/core/memory_management/MemoryPool_D.h:24; workers start while queues are still being
+    # constructed, thread_pool.h:126-137) and occasionally aborts inside glibc.  Such a run is
+    # repeated, then retried with fewer workers.
+    attempts = [(tx, ty)] * 3 + [(a, b) for a, b in ((4, 2), (2, 2), (1, 1))
+                                  if a * b < tx * ty and M % a == 0 and (M // a) % 32 == 0 and (N // 16) // b >= 1]
+    err = ""
+    for tx, ty in attempts:
+        cpus = sorted(os.sched_getaffinity(0))[: max(tx * ty, 1)]
+        cmd = [str(HERE / "_ref" / "decx_ref_cpu"), "gemm", str(M), str(N), str(K), f"{tx}x{ty}", str(reps), A, B, out]
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout,
+                           preexec_fn=lambda: os.sched_setaffinity(0, cpus))
+        if r.returncode == 0:
+            break
+        err = f"decx_ref_cpu failed rc={r.returncode}: {r.stderr.strip()}"
+    else:
+        raise RuntimeError(err)
     res = json.loads(r.stdout.strip().splitlines()[-1])
     res["split"] = f"{tx}x{ty}"
     return res
