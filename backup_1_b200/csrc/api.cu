@@ -205,6 +205,80 @@ extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M
     return decxb_check_dev_status(ctx);
 }
 
+/* ---- batched GEMM over arrays of equally sized matrices -------------------------------------- */
+extern "C" int decxb_gemm_f32_batched(decxb_ctx* ctx, int mode, int tile, int64_t batch, int64_t M, int64_t N, int64_t K,
+                                      const float* A, int64_t lda, int64_t strideA,
+                                      const float* B, int64_t ldb, int64_t strideB,
+                                      const float* C, int64_t ldc, int64_t strideC,
+                                      float* D, int64_t ldd, int64_t strideD, void* stream)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    if (batch < 0) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "negative batch");
+    cudaStream_t s = pick_stream(ctx, stream);
+    for (int64_t i = 0; i < batch; ++i) {
+        rc = gemm_device(ctx, mode, tile, M, N, K, A + i * strideA, lda, B + i * strideB, ldb, false,
+                         C ? C + i * strideC : nullptr, ldc, D + i * strideD, ldd, s);
+        if (rc) return rc;
+    }
+    return DECXB_OK;
+}
+
+extern "C" int decxb_gemm_f32_batched_host(decxb_ctx* ctx, int mode, int tile, int64_t batch, int64_t M, int64_t N, int64_t K,
+                                           const float* hA, int64_t lda, int64_t strideA,
+                                           const float* hB, int64_t ldb, int64_t strideB,
+                                           const float* hC, int64_t ldc, int64_t strideC,
+                                           float* hD, int64_t ldd, int64_t strideD)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    if (batch < 0 || M <= 0 || N <= 0 || K <= 0) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "gemm dims must be positive");
+    if (batch == 0) return DECXB_OK;
+    if (!hA || !hB || !hD) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null operand");
+    if (lda < K || ldb < N || ldd < N || (hC && ldc < N))
+        return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
+    /* A ring of three device slots; matrix i is uploaded while matrix i-1 is multiplied and the
+     * result of matrix i-2 travels back (the reference pipelines the same three phases over two
+     * slots and three streams, GEMM3_macros.h:140-248). */
+    constexpr int SLOTS = 3;
+    cudaStream_t s = ctx->stream, up = ctx->copy_stream[0], down = ctx->copy_stream[1];
+    Scratch scratch(ctx, s);
+    ChunkEvents evs;
+    const int64_t Kp = decxb_ceil_to(K, 4), Np = decxb_ceil_to(N, 4);
+    const int nslots = batch < SLOTS ? (int)batch : SLOTS;
+    float *dA[SLOTS], *dB[SLOTS], *dC[SLOTS] = {nullptr, nullptr, nullptr}, *dD[SLOTS];
+    for (int k = 0; k < nslots; ++k) {
+        if ((rc = scratch.get((size_t)M * Kp * 4, (void**)&dA[k]))) return rc;
+        if ((rc = scratch.get((size_t)K * Np * 4, (void**)&dB[k]))) return rc;
+        if ((rc = scratch.get((size_t)M * Np * 4, (void**)&dD[k]))) return rc;
+        if (hC && (rc = scratch.get((size_t)M * Np * 4, (void**)&dC[k]))) return rc;
+    }
+    if ((rc = fence_copy_streams(ctx, evs))) return rc;
+    std::vector<cudaEvent_t> e_done(batch, nullptr), e_down(batch, nullptr);
+    for (int64_t i = 0; i < batch; ++i) {
+        const int k = (int)(i % nslots);
+        cudaEvent_t e_up = evs.make();
+        e_done[i] = evs.make(); e_down[i] = evs.make();
+        if (!e_up || !e_done[i] || !e_down[i]) { sync_all_streams(ctx); return decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"); }
+        if (i >= nslots) DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(up, e_done[i - nslots], 0));      /* operands of the slot consumed */
+        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dA[k], Kp * 4, hA + i * strideA, lda * 4, K * 4, M, cudaMemcpyHostToDevice, up));
+        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dB[k], Np * 4, hB + i * strideB, ldb * 4, N * 4, K, cudaMemcpyHostToDevice, up));
+        if (hC) DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dC[k], Np * 4, hC + i * strideC, ldc * 4, N * 4, M, cudaMemcpyHostToDevice, up));
+        DECXB_CUDA_TRY(ctx, cudaEventRecord(e_up, up));
+        DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(s, e_up, 0));
+        if (i >= nslots) DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(s, e_down[i - nslots], 0));       /* result slot drained */
+        rc = gemm_device(ctx, mode, tile, M, N, K, dA[k], Kp, dB[k], Np, false, dC[k], Np, dD[k], Np, s);
+        if (rc) { sync_all_streams(ctx); return rc; }
+        DECXB_CUDA_TRY(ctx, cudaEventRecord(e_done[i], s));
+        DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(down, e_done[i], 0));
+        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(hD + i * strideD, ldd * 4, dD[k], Np * 4, N * 4, M, cudaMemcpyDeviceToHost, down));
+        DECXB_CUDA_TRY(ctx, cudaEventRecord(e_down[i], down));
+    }
+    if ((rc = sync_all_streams(ctx))) return rc;
+    scratch.release();
+    return decxb_check_dev_status(ctx);
+}
+
 /* ---- convolution ------------------------------------------------------------------------ */
 extern "C" int decxb_conv_geometry(int64_t W, int64_t H, int64_t depth, int64_t kW, int64_t kH, int64_t N,
                                    int flag, decxb_conv_geom* g)

@@ -101,6 +101,40 @@ public:
     }
 };
 
+class _MatrixArray : public de::MatrixArray<float> {
+public:
+    uint width = 0, height = 0, pitch = 0;
+    size_t ArrayNumber = 0, plane = 0, _plane = 0, total_bytes = 0;
+    int _store_type = Page_Default;
+    std::shared_ptr<float> MatArr;
+    void _attribute_assign(uint w, uint h, uint n, int flag)
+    {
+        width = w; height = h; ArrayNumber = n; _store_type = flag;
+        pitch = ceil_to(w, 8);                                      /* MatrixArray.h:230 */
+        plane = (size_t)w * h; _plane = (size_t)pitch * h;
+        total_bytes = _plane * n * sizeof(float);
+    }
+    void construct(uint w, uint h, uint n, int flag) { _attribute_assign(w, h, n, flag); MatArr = host_block(total_bytes, flag); }
+    void re_construct(uint w, uint h, uint n, int flag)
+    {
+        if (w != width || h != height || n != ArrayNumber || flag != _store_type || !MatArr) construct(w, h, n, flag);
+    }
+    _MatrixArray() { _attribute_assign(0, 0, 0, Page_Default); }
+    _MatrixArray(uint w, uint h, uint n, int flag) { construct(w, h, n, flag); }
+    uint Width() override { return width; }
+    uint Height() override { return height; }
+    uint MatrixNumber() override { return (uint)ArrayNumber; }
+    float& index(uint row, uint col, size_t _seq) override { return MatArr.get()[_seq * _plane + (size_t)row * pitch + col]; }
+    de::MatrixArray<float>& operator=(de::MatrixArray<float>& src) override
+    {
+        _MatrixArray& s = dynamic_cast<_MatrixArray&>(src);
+        _attribute_assign(s.width, s.height, (uint)s.ArrayNumber, s._store_type);
+        MatArr = s.MatArr;
+        return *this;
+    }
+    void release() override { MatArr.reset(); }
+};
+
 class _GPU_Matrix : public de::GPU_Matrix<float> {
 public:
     uint width = 0, height = 0, pitch = 0;
@@ -287,6 +321,10 @@ template <> Matrix<float>& CreateMatrixRef<float>() { return *(new decx::_Matrix
 template <> Matrix<float>* CreateMatrixPtr<float>() { return new decx::_Matrix(); }
 template <> Matrix<float>& CreateMatrixRef<float>(const uint w, const uint h, const int st) { return *(new decx::_Matrix(w, h, st)); }
 template <> Matrix<float>* CreateMatrixPtr<float>(const uint w, const uint h, const int st) { return new decx::_Matrix(w, h, st); }
+template <> MatrixArray<float>& CreateMatrixArrayRef<float>() { return *(new decx::_MatrixArray()); }
+template <> MatrixArray<float>* CreateMatrixArrayPtr<float>() { return new decx::_MatrixArray(); }
+template <> MatrixArray<float>& CreateMatrixArrayRef<float>(uint w, uint h, uint n, const int f) { return *(new decx::_MatrixArray(w, h, n, f)); }
+template <> MatrixArray<float>* CreateMatrixArrayPtr<float>(uint w, uint h, uint n, const int f) { return new decx::_MatrixArray(w, h, n, f); }
 template <> GPU_Matrix<float>& CreateGPUMatrixRef<float>() { return *(new decx::_GPU_Matrix()); }
 template <> GPU_Matrix<float>* CreateGPUMatrixPtr<float>() { return new decx::_GPU_Matrix(); }
 template <> GPU_Matrix<float>& CreateGPUMatrixRef<float>(const uint w, const uint h) { return *(new decx::_GPU_Matrix(w, h)); }
@@ -368,6 +406,35 @@ DH GEMM(Matrix<float>& A, Matrix<float>& B, Matrix<float>& dst) { return gemm_ho
 DH GEMM(Matrix<float>& A, Matrix<float>& B, Matrix<float>& C, Matrix<float>& dst) { return gemm_host(A, B, &C, dst); }
 DH GEMM(GPU_Matrix<float>& A, GPU_Matrix<float>& B, GPU_Matrix<float>& dst) { return gemm_dev(A, B, nullptr, dst); }
 DH GEMM(GPU_Matrix<float>& A, GPU_Matrix<float>& B, GPU_Matrix<float>& C, GPU_Matrix<float>& dst) { return gemm_dev(A, B, &C, dst); }
+
+static DH gemm3(MatrixArray<float>& A, MatrixArray<float>& B, MatrixArray<float>* C, MatrixArray<float>& dst)
+{
+    DH handle;
+    if (!decx::cuP.is_init) { decx::Not_init(&handle); return handle; }
+    decx::_MatrixArray* _A = dynamic_cast<decx::_MatrixArray*>(&A);
+    decx::_MatrixArray* _B = dynamic_cast<decx::_MatrixArray*>(&B);
+    decx::_MatrixArray* _C = C ? dynamic_cast<decx::_MatrixArray*>(C) : nullptr;
+    decx::_MatrixArray* _dst = dynamic_cast<decx::_MatrixArray*>(&dst);
+    if (_A->ArrayNumber != _B->ArrayNumber || (_C && _C->ArrayNumber != _A->ArrayNumber)) {
+        decx::set_handle(&handle, decx::DECX_FAIL_MNumNotMatching, "The number of matrices don't match each other");
+        return handle;
+    }
+    if (_A->width != _B->height || (_C && (_C->width != _B->width || _C->height != _A->height))) {
+        decx::MDim_Not_Matching(&handle); return handle;
+    }
+    _dst->re_construct(_B->width, _A->height, (uint)_A->ArrayNumber, decx::Page_Locked);
+    int rc = decxb_gemm_f32_batched_host(decx::cuP.ctx, gemm_mode(), DECXB_TILE_AUTO, (int64_t)_A->ArrayNumber,
+                                         _A->height, _B->width, _A->width,
+                                         _A->MatArr.get(), _A->pitch, (int64_t)_A->_plane,
+                                         _B->MatArr.get(), _B->pitch, (int64_t)_B->_plane,
+                                         _C ? _C->MatArr.get() : nullptr, _C ? _C->pitch : 0, _C ? (int64_t)_C->_plane : 0,
+                                         _dst->MatArr.get(), _dst->pitch, (int64_t)_dst->_plane);
+    decx::from_status(&handle, rc);
+    return handle;
+}
+
+DH GEMM3(MatrixArray<float>& A, MatrixArray<float>& B, MatrixArray<float>& dst) { return gemm3(A, B, nullptr, dst); }
+DH GEMM3(MatrixArray<float>& A, MatrixArray<float>& B, MatrixArray<float>& C, MatrixArray<float>& dst) { return gemm3(A, B, &C, dst); }
 
 DH Conv2_MK_im2col(Tensor<float>& src, TensorArray<float>& kernel, Tensor<float>& dst, const int flag)
 {

@@ -64,6 +64,8 @@ SIGNATURES = {
     "decxb_gemm_f32": (_i, [_vp, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
     "decxb_gemm_f32_nt": (_i, [_vp, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
     "decxb_gemm_f32_host": (_i, [_vp, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64]),
+    "decxb_gemm_f32_batched": (_i, [_vp, _i, _i, _i64, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp]),
+    "decxb_gemm_f32_batched_host": (_i, [_vp, _i, _i, _i64, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64]),
     "decxb_gemm_f32_noalloc": (_i, [_i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, C.c_char_p, _sz]),
     "decxb_conv_geometry": (_i, [_i64, _i64, _i64, _i64, _i64, _i64, _i, C.POINTER(ConvGeom)]),
     "decxb_im2col_pack_f32": (_i, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _i, _vp, _i64, _i64, _i64, _vp]),
@@ -189,6 +191,16 @@ class Context:
     def gemm_host(self, M, N, K, A, lda, B, ldb, D, ldd, Cin=None, ldc=0, mode=GEMM_3XTF32, tile=TILE_AUTO):
         self._chk(self.L.decxb_gemm_f32_host(self.h, mode, tile, M, N, K, _ptr(A), lda, _ptr(B), ldb,
                                              _ptr(Cin), ldc, _ptr(D), ldd))
+
+    def gemm_batched(self, batch, M, N, K, A, lda, sA, B, ldb, sB, D, ldd, sD, Cin=None, ldc=0, sC=0,
+                     mode=GEMM_3XTF32, tile=TILE_AUTO, stream=None):
+        self._chk(self.L.decxb_gemm_f32_batched(self.h, mode, tile, batch, M, N, K, _ptr(A), lda, sA, _ptr(B), ldb, sB,
+                                                _ptr(Cin), ldc, sC, _ptr(D), ldd, sD, stream))
+
+    def gemm_batched_host(self, batch, M, N, K, A, lda, sA, B, ldb, sB, D, ldd, sD, Cin=None, ldc=0, sC=0,
+                          mode=GEMM_3XTF32, tile=TILE_AUTO):
+        self._chk(self.L.decxb_gemm_f32_batched_host(self.h, mode, tile, batch, M, N, K, _ptr(A), lda, sA, _ptr(B), ldb, sB,
+                                                     _ptr(Cin), ldc, sC, _ptr(D), ldd, sD))
 
     # -- convolution ----------------------------------------------------------------------
     def im2col_pack(self, src, W, H, depth, kW, kH, flag, i2c, batch=1, src_stride=0, i2c_stride=0, stream=None):

@@ -20,7 +20,7 @@ namespace decx {
 /* srcs/handles/decx_handles.h:6-38 */
 enum DECX_error_types {
     DECX_SUCCESS = 0x00, DECX_FAIL_not_init = 0x01, DECX_FAIL_DimsNotMatching = 0x03, DECX_FAIL_ConvBadKernel = 0x05,
-    DECX_FAIL_ErrorFlag = 0x0b, DECX_FAIL_ErrorParams = 0x0d, DECX_FAIL_ALLOCATION = 0x10
+    DECX_FAIL_ErrorFlag = 0x0b, DECX_FAIL_ErrorParams = 0x0d, DECX_FAIL_MNumNotMatching = 0x0f, DECX_FAIL_ALLOCATION = 0x10
 };
 /* srcs/classes/store_types.h:24-28 */
 enum DATA_STORE_TYPE { Page_Locked = 0x00, Page_Default = 0x01 };
@@ -58,6 +58,24 @@ template <typename T> Matrix<T>& CreateMatrixRef();
 template <typename T> Matrix<T>* CreateMatrixPtr();
 template <typename T> Matrix<T>& CreateMatrixRef(const uint width, const uint height, const int store_type);
 template <typename T> Matrix<T>* CreateMatrixPtr(const uint width, const uint height, const int store_type);
+
+/* ---- srcs/classes/MatrixArray.h:27-53: MatrixNum matrices of one size, contiguous,
+ *      pitch*height floats apart (:222-237); index(row, col, matrix) (:367-370) ----------------- */
+template <typename T>
+class MatrixArray {
+public:
+    virtual uint Width() = 0;
+    virtual uint Height() = 0;
+    virtual uint MatrixNumber() = 0;
+    virtual T& index(uint row, uint col, size_t _seq) = 0;
+    virtual MatrixArray<T>& operator=(MatrixArray<T>& src) = 0;
+    virtual void release() = 0;
+    virtual ~MatrixArray() {}
+};
+template <typename T> MatrixArray<T>& CreateMatrixArrayRef();
+template <typename T> MatrixArray<T>* CreateMatrixArrayPtr();
+template <typename T> MatrixArray<T>& CreateMatrixArrayRef(uint width, uint height, uint MatrixNum, const int flag);
+template <typename T> MatrixArray<T>* CreateMatrixArrayPtr(uint width, uint height, uint MatrixNum, const int flag);
 
 /* ---- srcs/classes/GPU_Matrix.h:21-50 ---------------------------------------------------------- */
 template <typename T>
@@ -157,6 +175,11 @@ DH GEMM(Matrix<float>& A, Matrix<float>& B, Matrix<float>& dst);
 DH GEMM(Matrix<float>& A, Matrix<float>& B, Matrix<float>& C, Matrix<float>& dst);
 DH GEMM(GPU_Matrix<float>& A, GPU_Matrix<float>& B, GPU_Matrix<float>& dst);
 DH GEMM(GPU_Matrix<float>& A, GPU_Matrix<float>& B, GPU_Matrix<float>& C, GPU_Matrix<float>& dst);
+
+/* srcs/GEMM/CUDA/large_squares/GEMM3.h:27-37: dst[i] = A[i]*B[i] (+ C[i]) for every matrix of
+ * the arrays, uploads, products and downloads overlapped. */
+DH GEMM3(MatrixArray<float>& A, MatrixArray<float>& B, MatrixArray<float>& dst);
+DH GEMM3(MatrixArray<float>& A, MatrixArray<float>& B, MatrixArray<float>& C, MatrixArray<float>& dst);
 
 /* srcs/convolution/CUDA/im2col/conv2_mk_im2col.h:25: cross-correlation of src with every
  * tensor of `kernel`, stride 1; flag = decx::conv_property.  dst is re-constructed by the callee. */

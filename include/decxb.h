@@ -161,6 +161,22 @@ DECXB_API int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile,
                                   const float* hC, int64_t ldc,
                                   float* hD, int64_t ldd);
 
+/* Batched product over arrays of equally sized matrices, D[i] = A[i]*B[i] (+C[i]); matrix i of
+ * an array starts stride* elements after matrix i-1.  Replaces de::cuda::GEMM3 on MatrixArray
+ * (srcs/GEMM/CUDA/large_squares/GEMM3.h:45-114 and, with C, :120-200; its copy/compute
+ * pipeline is the macro GEMM3_part, GEMM3_macros.h:140-248).  The host-resident form uploads
+ * matrix i while matrix i-1 is multiplied and result i-2 is downloaded, and blocks until done. */
+DECXB_API int decxb_gemm_f32_batched(decxb_ctx* ctx, int mode, int tile, int64_t batch, int64_t M, int64_t N, int64_t K,
+                                     const float* A, int64_t lda, int64_t strideA,
+                                     const float* B, int64_t ldb, int64_t strideB,
+                                     const float* C, int64_t ldc, int64_t strideC,
+                                     float* D, int64_t ldd, int64_t strideD, void* stream);
+DECXB_API int decxb_gemm_f32_batched_host(decxb_ctx* ctx, int mode, int tile, int64_t batch, int64_t M, int64_t N, int64_t K,
+                                          const float* hA, int64_t lda, int64_t strideA,
+                                          const float* hB, int64_t ldb, int64_t strideB,
+                                          const float* hC, int64_t ldc, int64_t strideC,
+                                          float* hD, int64_t ldd, int64_t strideD);
+
 /* The 3xTF32 product D = A*B (+C) of decxb_gemm_f32 for callers that must not allocate
  * device memory (this entry has no counterpart in the reference).  Such callers exist: a
  * process in which a framework's caching pool has reserved the whole card, so that a

@@ -153,6 +153,35 @@ static void test_gemm_random_and_errors()
     CHECK(h.error_type == decx::DECX_SUCCESS && max_err(D2, R) / K <= 1e-6);
 }
 
+static void test_gemm3()
+{
+    /* batched product over MatrixArrays (GEMM3.h:45-114), 5 matrices, nothing aligned */
+    unsigned s = 4242;
+    const int M = 150, K = 90, N = 70, nb = 5;
+    de::MatrixArray<float>& A = de::CreateMatrixArrayRef<float>(K, M, nb, decx::Page_Locked);
+    de::MatrixArray<float>& B = de::CreateMatrixArrayRef<float>(N, K, nb, decx::Page_Default);
+    de::MatrixArray<float>& C = de::CreateMatrixArrayRef<float>(N, M, nb, decx::Page_Default);
+    de::MatrixArray<float>& D = de::CreateMatrixArrayRef<float>();
+    for (int b = 0; b < nb; ++b) {
+        for (int i = 0; i < M; ++i) for (int k = 0; k < K; ++k) A.index(i, k, b) = rnd(s);
+        for (int k = 0; k < K; ++k) for (int j = 0; j < N; ++j) B.index(k, j, b) = rnd(s);
+        for (int i = 0; i < M; ++i) for (int j = 0; j < N; ++j) C.index(i, j, b) = rnd(s);
+    }
+    for (int with_c = 0; with_c <= 1; ++with_c) {
+        de::DH h = with_c ? de::cuda::GEMM3(A, B, C, D) : de::cuda::GEMM3(A, B, D);
+        CHECK(h.error_type == decx::DECX_SUCCESS && D.MatrixNumber() == (uint)nb && D.Width() == (uint)N && D.Height() == (uint)M);
+        double m = 0;
+        for (int b = 0; b < nb; ++b) for (int i = 0; i < M; ++i) for (int j = 0; j < N; ++j) {
+            float c = with_c ? C.index(i, j, b) : 0.f;
+            for (int k = 0; k < K; ++k) c = fmaf(A.index(i, k, b), B.index(k, j, b), c);
+            m = fmax(m, fabs((double)D.index(i, j, b) - c));
+        }
+        CHECK(m / K <= 1e-6);
+    }
+    de::MatrixArray<float>& B2 = de::CreateMatrixArrayRef<float>(N, K, nb + 1, decx::Page_Default);
+    CHECK(de::cuda::GEMM3(A, B2, D).error_type == decx::DECX_FAIL_MNumNotMatching);
+}
+
 /* direct cross-correlation in the column order (ky, kx, c) of the reference's column matrix */
 static float conv_ref(de::Tensor<float>& S, de::TensorArray<float>& F, int n, int y, int x, int flag)
 {
@@ -232,6 +261,7 @@ int main(int argc, char** argv)
         de::InitCuda();
         test_gemm_known_answer();
         test_gemm_random_and_errors();
+        test_gemm3();
         test_conv();
         de::release_all_tmp();
     } else return 2;

@@ -139,6 +139,26 @@ def test_gemm_host_resident(ctx):
     assert o.norm_err(D, o.gemm_fmaf(A, B, Cin), K, 1.0, 1.0) <= TOL_3X
 
 
+def test_gemm_batched_device_and_host(ctx):
+    """Batched product over arrays of matrices (de::cuda::GEMM3): 7 matrices through the
+    three-slot upload/compute/download ring, with and without addend."""
+    nb, M, N, K = 7, 260, 136, 200
+    A = o.fill_uniform(nb * M * K, 1).reshape(nb, M, K)
+    B = o.fill_uniform(nb * K * N, 2).reshape(nb, K, N)
+    Cin = o.fill_uniform(nb * M * N, 3).reshape(nb, M, N)
+    R = np.stack([o.gemm_fmaf(A[i], B[i]) for i in range(nb)])
+    Rc = np.stack([o.gemm_fmaf(A[i], B[i], Cin[i]) for i in range(nb)])
+    D = np.full((nb, M, N), np.nan, dtype=np.float32)
+    ctx.gemm_batched_host(nb, M, N, K, A, K, M * K, B, N, K * N, D, N, M * N)
+    assert o.norm_err(D, R, K, 1.0, 1.0) <= TOL_3X
+    ctx.gemm_batched_host(nb, M, N, K, A, K, M * K, B, N, K * N, D, N, M * N, Cin=Cin, ldc=N, sC=M * N)
+    assert o.norm_err(D, Rc, K, 1.0, 1.0) <= TOL_3X
+    dD = torch.full((nb, M, N), float("nan"), device=DEV)
+    ctx.gemm_batched(nb, M, N, K, dev(A), K, M * K, dev(B), N, K * N, dD, N, M * N)
+    ctx.synchronize()
+    assert o.norm_err(dD.cpu().numpy(), R, K, 1.0, 1.0) <= TOL_3X
+
+
 def test_gemm_argument_errors(ctx):
     t = torch.zeros(64, device=DEV)
     with pytest.raises(b.DecxbError) as e:
