@@ -41,6 +41,10 @@ WORKLOADS = {
                  desc="im2col conv 256 x (56x56x256 -> 256 filters 3x3), batch sharded over ranks (BASELINE config 4)"),
 }
 
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel, from the ncu
+# captures summarised under profiles/ (gemm_tf32_kernel_cfg2.md, im2col_pack_kernel_cfg3.md)
+NCU_TRAFFIC_BYTES = {("cfg2", "3xtf32", "gemm"): 727.8e6, ("cfg3", "3xtf32", "pack"): 73.9e6}
+
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 
@@ -312,7 +316,7 @@ def main():
         tf32 = peaks["bf16_tflops"] / 2.0
         peak = tf32 / 3.0 if args.mode == "3xtf32" else tf32
         roofline = {"bound": "tensor", "kernel": "decxb_gemm_tf32_kernel", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
-                    "frac": ach / peak, "traffic": None,
+                    "frac": ach / peak, "traffic": NCU_TRAFFIC_BYTES.get((args.workload, args.mode, "gemm")) if args.tile == 0 else None,
                     "peak_basis": f"{peaks['basis']} bf16 dense burst {peaks['bf16_tflops']} TFLOP/s / 2 (TF32)"
                                   + (" / 3 (3xTF32)" if args.mode == "3xtf32" else ""),
                     "avg_launch_ms": avg_ms, "time_shares": shares}
@@ -332,7 +336,7 @@ def main():
             kname = "decxb_split_rows_kernel + decxb_split_transpose_kernel"
         ach = alg / (avg_ms * 1e-3) / 1e9 if alg else None
         roofline = {"bound": "hbm", "kernel": kname, "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                    "frac": ach / peaks["hbm_gbs"] if ach else None, "traffic": None,
+                    "frac": ach / peaks["hbm_gbs"] if ach else None, "traffic": NCU_TRAFFIC_BYTES.get((args.workload, args.mode, dom)),
                     "peak_basis": f"{peaks['basis']} copy bandwidth", "avg_launch_ms": avg_ms, "time_shares": shares,
                     "per_class_ms_per_step": {c: round(v["ms"] / args.steps, 5) for c, v in prof.items() if v["launches"]}}
 
