@@ -504,6 +504,19 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
     }
 }
 
+/* Self-test of the bounded wait: one thread waits on an mbarrier that nothing will ever arrive
+ * on.  The wait must give up after the limit, record itself in the status word and let the
+ * kernel return normally. */
+__global__ void decxb_wait_probe_kernel(const GemmParams p)
+{
+    __shared__ __align__(8) uint64_t bar;
+    const uint32_t b = smem_u32(&bar);
+    if (threadIdx.x == 0) { mbar_init(b, 1); fence_barrier_init(); }
+    __syncthreads();
+    if (threadIdx.x == 0) (void)wait_bounded(b, 0u, p, 900, 0);
+    __syncthreads();
+}
+
 /* ------------------------------------------------------------------ host side -------- */
 PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn()
 {
@@ -693,4 +706,21 @@ int decxb_launch_conv_implicit(decxb_ctx* ctx, const decxb_conv_gemm_args& a, cu
     if (a.Np <= 64)  return x3 ? launch_conv_cfg<1, 64, 3>(ctx, a, s)  : launch_conv_cfg<1, 64, 1>(ctx, a, s);
     if (a.Np <= 128) return x3 ? launch_conv_cfg<1, 128, 3>(ctx, a, s) : launch_conv_cfg<1, 128, 1>(ctx, a, s);
     return x3 ? launch_conv_cfg<2, 128, 3>(ctx, a, s) : launch_conv_cfg<2, 128, 1>(ctx, a, s);
+}
+
+extern "C" int decxb_selftest_bounded_wait(decxb_ctx* ctx, int limit_ms)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    if (limit_ms <= 0 || limit_ms > 1000) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "limit must be 1..1000 ms");
+    GemmParams p = {};
+    p.wait_limit_ns = (long long)limit_ms * 1000000LL;
+    p.status = ctx->d_status;
+    {
+        decxb_launch_scope scope(ctx, ctx->stream, DECXB_K_GEMM);
+        decxb_wait_probe_kernel<<<1, 32, 0, ctx->stream>>>(p);
+    }
+    DECXB_CUDA_TRY(ctx, cudaGetLastError());
+    DECXB_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    return decxb_check_dev_status(ctx);
 }

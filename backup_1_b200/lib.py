@@ -72,6 +72,7 @@ SIGNATURES = {
     "decxb_conv2_im2col_f32": (_i, [_vp, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp]),
     "decxb_conv2_im2col_f32_host": (_i, [_vp, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64]),
     "decxb_kernel_launch_count": (_u64, [_vp]),
+    "decxb_selftest_bounded_wait": (_i, [_vp, _i]),
     "decxb_profile_enable": (_i, [_vp, _i]),
     "decxb_profile_read": (_i, [_vp, C.POINTER(Profile)]),
     "decxb_version": (C.c_char_p, []),

@@ -261,6 +261,11 @@ DECXB_API int decxb_profile_read(decxb_ctx* ctx, decxb_profile* out);
 
 /* Number of kernels this library has launched on the context since it was created. */
 DECXB_API uint64_t decxb_kernel_launch_count(decxb_ctx* ctx);
+/* Failure-detection self-test: launches one tiny kernel whose only thread waits, with the
+ * library's bounded wait, on a barrier that nothing signals.  Returns DECXB_ERR_TIMEOUT after
+ * `limit_ms` (1..1000) when the mechanism works; the context stays usable.  No counterpart in
+ * the reference (its kernels have no device-side waits). */
+DECXB_API int decxb_selftest_bounded_wait(decxb_ctx* ctx, int limit_ms);
 DECXB_API const char* decxb_version(void);
 
 #ifdef __cplusplus

@@ -201,31 +201,59 @@ def ref_kernels():
     return _ref
 
 
-def ref_im2col_pack(src, W, depth, kW, kH, flag):
+_ref_gpu = None
+
+
+def ref_kernels_gpu():
+    """The reference's CUDA kernels compiled for sm_100a (real launches), or None when not
+    built.  Only for use on a machine with a GPU."""
+    global _ref_gpu
+    so = HERE / "_ref" / "libdecx_ref_kernels_gpu.so"
+    if _ref_gpu is None and so.exists():
+        L = C.CDLL(str(so))
+        u, fp = C.c_uint, C.c_void_p
+        L.decx_ref_im2col_pack.argtypes = [fp, u, u, u, u, u, C.c_int, fp]
+        L.decx_ref_conv2_im2col.argtypes = [fp, u, u, u, fp, u, u, u, C.c_int, fp]
+        L.decx_ref_gemm_spec.argtypes = [u, u, u, fp, u, fp, u, fp, u, fp, u]
+        L.decx_ref_last_kernel_ms.restype = C.c_float
+        _ref_gpu = L
+    return _ref_gpu
+
+
+def ref_last_kernel_ms() -> float:
+    """Device time of the kernel(s) of the last ref_* call made with gpu=True."""
+    return float(ref_kernels_gpu().decx_ref_last_kernel_ms())
+
+
+def _ref_lib(gpu: bool):
+    return ref_kernels_gpu() if gpu else ref_kernels()
+
+
+def ref_im2col_pack(src, W, depth, kW, kH, flag, gpu=False):
     src = np.ascontiguousarray(src, dtype=_F)
     H = src.shape[0]
     _, _, _, M, Kp = conv_geometry(W, H, depth, kW, kH, flag)
     out = np.empty((M, Kp), dtype=_F)
-    rc = ref_kernels().decx_ref_im2col_pack(_p(src), W, H, depth, kW, kH, flag, _p(out))
+    rc = _ref_lib(gpu).decx_ref_im2col_pack(_p(src), W, H, depth, kW, kH, flag, _p(out))
     if rc:
         raise ValueError(f"decx_ref_im2col_pack rc={rc}")
     return out
 
 
-def ref_conv2_im2col(src, W, depth, filters, kW, flag):
+def ref_conv2_im2col(src, W, depth, filters, kW, flag, gpu=False):
     src = np.ascontiguousarray(src, dtype=_F)
     filters = np.ascontiguousarray(filters, dtype=_F)
     H = src.shape[0]
     N, kH = filters.shape[0], filters.shape[1]
     _, oh, eq, _, _ = conv_geometry(W, H, depth, kW, kH, flag)
     out = np.empty((oh, eq, ceil4(N)), dtype=_F)
-    rc = ref_kernels().decx_ref_conv2_im2col(_p(src), W, H, depth, _p(filters), kW, kH, N, flag, _p(out))
+    rc = _ref_lib(gpu).decx_ref_conv2_im2col(_p(src), W, H, depth, _p(filters), kW, kH, N, flag, _p(out))
     if rc:
         raise ValueError(f"decx_ref_conv2_im2col rc={rc}")
     return out
 
 
-def ref_gemm_spec(A, B, Cin=None):
+def ref_gemm_spec(A, B, Cin=None, gpu=False):
     A = np.ascontiguousarray(A, dtype=_F)
     B = np.ascontiguousarray(B, dtype=_F)
     M, K = A.shape
@@ -233,7 +261,7 @@ def ref_gemm_spec(A, B, Cin=None):
     if Cin is not None:
         Cin = np.ascontiguousarray(Cin, dtype=_F)
     D = np.empty((M, N), dtype=_F)
-    rc = ref_kernels().decx_ref_gemm_spec(M, N, K, _p(A), K, _p(B), N, _p(Cin), N, _p(D), N)
+    rc = _ref_lib(gpu).decx_ref_gemm_spec(M, N, K, _p(A), K, _p(B), N, _p(Cin), N, _p(D), N)
     if rc:
         raise ValueError(f"decx_ref_gemm_spec rc={rc}")
     return D

@@ -18,6 +18,10 @@
  * classes/core_types.h) pull in windows.h and thrust and are skipped by
  * pre-defining their include guards; the kernels use nothing from them.
  *
+ * The same file builds a second way: compiled by nvcc with -DDECX_REF_GPU the kernels run as
+ * real launches on the GPU (buffers in managed memory, so the staging code below is shared),
+ * which gives the reference kernels' own output and timing on the same device as the new code.
+ *
  * The launch geometry and the staging buffers of the reference's host
  * drivers are reproduced here as plain arithmetic, each line citing the
  * driver line it follows.  Staging buffers are zero-initialised (the
@@ -36,12 +40,14 @@
 #include <thread>
 #include <vector>
 
+#ifndef DECX_REF_GPU
 #undef __shared__
 #define __shared__ static
 static thread_local uint3 threadIdx, blockIdx;
 static thread_local dim3 blockDim, gridDim;
 static pthread_barrier_t g_block_barrier;
 static inline void __syncthreads() { pthread_barrier_wait(&g_block_barrier); }
+#endif
 
 #define _BASIC_H_
 #define _INCLUDE_H_
@@ -50,6 +56,9 @@ static inline void __syncthreads() { pthread_barrier_wait(&g_block_barrier); }
 #include "convolution/CUDA/im2col/eq_GEMM.cuh"
 #include "GEMM/CUDA/large_squares/GEMM.cuh"
 
+static float g_last_kernel_ms = 0.f;     /* GPU build: device time of the last timed launch */
+
+#ifndef DECX_REF_GPU
 /* Emulated <<<grid, block>>>: persistent worker threads walk the blocks in
  * order with a barrier between blocks. */
 static void launch(dim3 grid, dim3 block, const std::function<void()>& kernel)
@@ -73,14 +82,35 @@ static void launch(dim3 grid, dim3 block, const std::function<void()>& kernel)
     for (auto& w : workers) w.join();
     pthread_barrier_destroy(&g_block_barrier);
 }
+#define DECX_LAUNCH(grid, block, kernel, ...) launch((grid), (block), [&] { kernel(__VA_ARGS__); })
+static void* ref_alloc(size_t bytes) { void* p = nullptr; return posix_memalign(&p, 64, bytes) ? nullptr : p; }
+static void ref_free(void* p) { free(p); }
+#else
+/* Real launches.  The kernel runs once to bring the managed pages to the device, then once
+ * more between two events: that second run is the timed one (same inputs, same outputs). */
+#define DECX_LAUNCH(grid, block, kernel, ...)                                          \
+    do {                                                                               \
+        cudaEvent_t e0, e1; cudaEventCreate(&e0); cudaEventCreate(&e1);                \
+        kernel<<<(grid), (block)>>>(__VA_ARGS__);                                      \
+        cudaDeviceSynchronize();                                                       \
+        cudaEventRecord(e0);                                                           \
+        kernel<<<(grid), (block)>>>(__VA_ARGS__);                                      \
+        cudaEventRecord(e1);                                                           \
+        cudaDeviceSynchronize();                                                       \
+        cudaEventElapsedTime(&g_last_kernel_ms, e0, e1);                               \
+        cudaEventDestroy(e0); cudaEventDestroy(e1);                                    \
+    } while (0)
+static void* ref_alloc(size_t bytes) { void* p = nullptr; return cudaMallocManaged(&p, bytes) == cudaSuccess ? p : nullptr; }
+static void ref_free(void* p) { cudaFree(p); }
+#endif
 
 static inline size_t ceil_to(size_t v, size_t m) { return (v + m - 1) / m * m; }
 
 static float4* zalloc4(size_t floats)
 {
-    void* p = nullptr;
     const size_t bytes = ceil_to(floats * sizeof(float), 64) + 64;
-    if (posix_memalign(&p, 64, bytes)) return nullptr;
+    void* p = ref_alloc(bytes);
+    if (!p) return nullptr;
     memset(p, 0, bytes);
     return (float4*)p;
 }
@@ -132,18 +162,16 @@ static float4* run_pack(const float* src, unsigned W, unsigned H, const ConvDims
     const size_t row_floats = d.src_buf_w;
     float4* src_buf = zalloc4(row_floats * rows_alloc + (size_t)96 * d.dp);
     float4* i2c = zalloc4(d.i2c_w * d.i2c_h);
-    if (!src_buf || !i2c) { free(src_buf); free(i2c); return nullptr; }
+    if (!src_buf || !i2c) { ref_free(src_buf); ref_free(i2c); return nullptr; }
     for (unsigned r = 0; r < H; ++r)
         memcpy((float*)src_buf + (size_t)(d.src_row0 + r) * row_floats + (size_t)d.src_col0 * d.dp,
                src + (size_t)r * d.wp * d.dp, (size_t)d.wp * d.dp * sizeof(float));
     int2 thread_bounds = make_int2(d.eq_src.x / 4, d.eq_src.y);
     dim3 block(16, 16);
     dim3 grid((thread_bounds.y + 15) / 16, (thread_bounds.x + 15) / 16);
-    launch(grid, block, [&] {
-        cu_sIm2Col_r8_within(src_buf, i2c, d.kernel_shift, thread_bounds, row_floats / 4, d.i2c_w / 4,
-                             make_int2((int)kW, (int)kH), (int)d.dp / 4);
-    });
-    free(src_buf);
+    DECX_LAUNCH(grid, block, cu_sIm2Col_r8_within, src_buf, i2c, d.kernel_shift, thread_bounds, row_floats / 4,
+                d.i2c_w / 4, make_int2((int)kW, (int)kH), (int)d.dp / 4);
+    ref_free(src_buf);
     return i2c;
 }
 
@@ -160,7 +188,7 @@ int decx_ref_im2col_pack(const float* src, unsigned W, unsigned H, unsigned dept
     float4* i2c = run_pack(src, W, H, d, kW, kH);
     if (!i2c) return 9;
     memcpy(i2c_out, i2c, d.i2c_w * d.i2c_h * sizeof(float));
-    free(i2c);
+    ref_free(i2c);
     return 0;
 }
 
@@ -177,7 +205,7 @@ int decx_ref_conv2_im2col(const float* src, unsigned W, unsigned H, unsigned dep
     float4* i2c = run_pack(src, W, H, d, kW, kH);
     float4* ker_buf = zalloc4((size_t)d.ker_buf_w * d.ker_buf_h);
     float4* dst_buf = zalloc4((size_t)d.actual_dst_buf_W * d.dst_buf_h);
-    if (!i2c || !ker_buf || !dst_buf) { free(i2c); free(ker_buf); free(dst_buf); return 9; }
+    if (!i2c || !ker_buf || !dst_buf) { ref_free(i2c); ref_free(ker_buf); ref_free(dst_buf); return 9; }
     /* :116-121, :226-231 -- one 2-D copy per filter */
     const size_t gap = (size_t)d.dp * d.kwp * kH;
     for (unsigned i = 0; i < N; ++i)
@@ -188,12 +216,13 @@ int decx_ref_conv2_im2col(const float* src, unsigned W, unsigned H, unsigned dep
     ulong2 bounds; bounds.x = d.i2c_w / 4; bounds.y = d.i2c_h / 4;
     dim3 block(32, 8);
     dim3 grid((unsigned)(d.dst_buf_h / 128), d.dst_buf_w / 32);
-    launch(grid, block, [&] {
-        cu_conv_eq_mm(i2c, ker_buf, dst_buf, bounds, d.actual_dst_buf_W / 4, d.ker_buf_w / 4, d.ker_buf_w / 128);
-    });
+    const float pack_ms = g_last_kernel_ms;
+    DECX_LAUNCH(grid, block, cu_conv_eq_mm, i2c, ker_buf, dst_buf, bounds, d.actual_dst_buf_W / 4, d.ker_buf_w / 4,
+                d.ker_buf_w / 128);
+    g_last_kernel_ms += pack_ms;        /* pack + equivalent GEMM */
     /* :156, :266 -- flat copy of the destination tensor's total_bytes */
     memcpy(dst, dst_buf, (size_t)d.out_h * d.eq_src.x * d.actual_dst_buf_W * sizeof(float));
-    free(i2c); free(ker_buf); free(dst_buf);
+    ref_free(i2c); ref_free(ker_buf); ref_free(dst_buf);
     return 0;
 }
 
@@ -218,11 +247,15 @@ int decx_ref_gemm_spec(unsigned M, unsigned N, unsigned K,
     dim3 grid(hA / (GEMM_BlockDim * 8), pitch_B / (GEMM_BlockDim * 8));
     dim3 block(GEMM_BlockDim * GEMM_BlockDim);
     const uint iter = pitch_A / GEMM_BlockDim;
-    if (C) launch(grid, block, [&] { cu_GEMM_fp32_ABC_spec(DA, DB, DC, DD, pitch_A / 4, pitch_B / 4, iter); });
-    else   launch(grid, block, [&] { cu_GEMM_fp32_spec(DA, DB, DD, pitch_A / 4, pitch_B / 4, iter); });
+    if (C) DECX_LAUNCH(grid, block, cu_GEMM_fp32_ABC_spec, DA, DB, DC, DD, pitch_A / 4, pitch_B / 4, iter);
+    else   DECX_LAUNCH(grid, block, cu_GEMM_fp32_spec, DA, DB, DD, pitch_A / 4, pitch_B / 4, iter);
     for (unsigned r = 0; r < M; ++r) memcpy(D + (size_t)r * ldd, (float*)DD + (size_t)r * pitch_B, N * sizeof(float));
-    free(DA); free(DB); free(DC); free(DD);
+    ref_free(DA); ref_free(DB); if (DC) ref_free(DC); ref_free(DD);
     return 0;
 }
+
+/* GPU build: device time in ms of the kernel(s) of the last call (0 in the host build). */
+__attribute__((visibility("default")))
+float decx_ref_last_kernel_ms(void) { return g_last_kernel_ms; }
 
 }  /* extern "C" */

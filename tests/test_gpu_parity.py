@@ -14,6 +14,7 @@ pytestmark = pytest.mark.gpu
 
 TOL_3X = 1e-6
 TOL_1X = 2e-3
+ALGOS = [b.CONV_EXPLICIT, b.CONV_IMPLICIT]
 DEV = "cuda:0"
 
 
@@ -227,6 +228,28 @@ def test_pack_golden_vectors_of_reference_kernel(ctx, golden):
             assert np.array_equal(P.view(np.uint32), z[name].view(np.uint32))
 
 
+@pytest.mark.skipif(o.ref_kernels_gpu() is None, reason="oracle/_ref GPU build of the reference kernels not present")
+def test_against_reference_kernels_on_this_gpu(ctx):
+    """The reference's own CUDA kernels, compiled for sm_100a and launched with the reference
+    drivers' geometry on this GPU: pack byte for byte, GEMM and convolution within the 3xTF32
+    bar of the reference's fp32 results."""
+    for (W, H, C, kW, kH, N, flag) in [(70, 18, 4, 3, 3, 33, 1), (22, 19, 6, 3, 5, 5, 0), (28, 28, 64, 3, 3, 64, 1)]:
+        src = o.make_tensor(W, H, C, 4)
+        flt = o.make_filters(kW, kH, C, N, 5)
+        Pref = o.ref_im2col_pack(src, W, C, kW, kH, flag, gpu=True)
+        assert np.array_equal(run_pack(ctx, src, W, C, kW, kH, flag).view(np.uint32), Pref.view(np.uint32))
+        Dref = o.ref_conv2_im2col(src, W, C, flt, kW, flag, gpu=True)
+        assert np.array_equal(Dref.view(np.uint32), o.conv2_im2col(src, W, C, flt, kW, flag).view(np.uint32))
+        for algo in ALGOS:
+            D = run_conv(ctx, src, W, C, flt, kW, flag, algo=algo)
+            assert o.norm_err(D, Dref, kW * kH * o.ceil4(C), 1.0, 1.0) <= TOL_3X
+    A = o.fill_uniform(384 * 160, 1).reshape(384, 160)
+    B = o.fill_uniform(160 * 256, 2).reshape(160, 256)
+    Rref = o.ref_gemm_spec(A, B, gpu=True)
+    assert np.array_equal(Rref, o.gemm_fmaf(A, B))
+    assert o.norm_err(run_gemm(ctx, A, B), Rref, 160, 1.0, 1.0) <= TOL_3X
+
+
 def test_pack_batched_equals_per_image(ctx):
     W, H, C, kW, kH, flag, nb = 14, 9, 8, 3, 3, 1, 5
     imgs = np.stack([o.make_tensor(W, H, C, 4, first_index=i * 10007) for i in range(nb)])
@@ -258,9 +281,6 @@ def run_conv(ctx, src, W, depth, flt, kW, flag, mode=b.GEMM_3XTF32, algo=b.CONV_
     ctx.synchronize()
     r = out.cpu().numpy()
     return r if src.ndim == 4 else r[0]
-
-
-ALGOS = [b.CONV_EXPLICIT, b.CONV_IMPLICIT]
 
 
 @pytest.mark.parametrize("algo", ALGOS)
@@ -341,6 +361,21 @@ def test_conv_config3_full_size(ctx, algo):
     rows = np.arange(0, P.shape[0], 97)
     R = o.gemm_fmaf(P[rows], np.ascontiguousarray(Km.T))
     assert o.norm_err(D[rows], R, P.shape[1], 1.0, 1.0) <= TOL_3X
+
+
+def test_bounded_wait_expires_and_context_survives(ctx):
+    """Failure detection without a fault: a wait on a barrier nothing signals gives up after
+    its limit, the host reads DECXB_ERR_TIMEOUT, and the next GEMM on the same context is fine."""
+    import time
+    L = b.load_library()
+    t0 = time.perf_counter()
+    rc = L.decxb_selftest_bounded_wait(ctx.h, 50)
+    dt = time.perf_counter() - t0
+    assert rc == 103 and b"gave up" in L.decxb_last_error(ctx.h)
+    assert 0.04 <= dt < 2.0
+    A = o.fill_uniform(256 * 64, 1).reshape(256, 64)
+    B = o.fill_uniform(64 * 256, 2).reshape(64, 256)
+    assert o.norm_err(run_gemm(ctx, A, B), o.gemm_fmaf(A, B), 64, 1.0, 1.0) <= TOL_3X
 
 
 def test_arena_reuses_blocks(ctx):
