@@ -11,6 +11,10 @@ from .lib import (  # noqa: F401
     DecxbError,
     GEMM_1XTF32,
     GEMM_3XTF32,
+    ACT_NONE,
+    ACT_RELU,
+    ACT_SIGMOID,
+    ACT_TANH,
     CONV_EXPLICIT,
     CONV_IMPLICIT,
     CONV_NO_COMPENSATE,

@@ -57,12 +57,14 @@ int prepare_b(decxb_ctx* ctx, Scratch& scratch, bool x3, int64_t N, int64_t K,
 /* D = A * B (+C) with B already prepared; A is split (3xTF32) or used in place. */
 int gemm_prepared(decxb_ctx* ctx, Scratch& scratch, bool x3, int tile, int64_t M, int64_t N, int64_t K,
                   const float* A, int64_t lda, const PreparedB& pb,
-                  const float* C, int64_t ldc, float* D, int64_t ldd, cudaStream_t s)
+                  const float* C, int64_t ldc, float* D, int64_t ldd, cudaStream_t s,
+                  const float* bias = nullptr, int act = DECXB_ACT_NONE)
 {
     const int64_t Kp = decxb_ceil_to(K, 4);
     decxb_gemm_args g = {};
     g.M = M; g.N = N; g.K = K; g.C = C; g.ldc = ldc; g.D = D; g.ldd = ldd; g.tile = tile; g.b_rows = N;
     g.b_hi = pb.hi; g.b_lo = pb.lo; g.ldb = pb.ld;
+    g.bias = bias; g.act = act;
     int rc;
     if (x3 || !tma_ok(A, lda)) {
         float *hi = nullptr, *lo = nullptr;
@@ -78,9 +80,11 @@ int gemm_prepared(decxb_ctx* ctx, Scratch& scratch, bool x3, int tile, int64_t M
 /* D = A * op(B) (+C).  b_is_nt: B given as Bt[N][K]. */
 int gemm_device(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_t K,
                 const float* A, int64_t lda, const float* B, int64_t ldb, bool b_is_nt,
-                const float* C, int64_t ldc, float* D, int64_t ldd, cudaStream_t s)
+                const float* C, int64_t ldc, float* D, int64_t ldd, cudaStream_t s,
+                const float* bias = nullptr, int act = DECXB_ACT_NONE)
 {
     if (mode != DECXB_GEMM_3XTF32 && mode != DECXB_GEMM_1XTF32) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "gemm mode");
+    if (act < DECXB_ACT_NONE || act > DECXB_ACT_TANH) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "activation");
     if (M <= 0 || N <= 0 || K <= 0) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "gemm dims must be positive");
     if (!A || !B || !D) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null operand");
     if (lda < K || ldb < (b_is_nt ? K : N) || ldd < N || (C && ldc < N))
@@ -89,7 +93,7 @@ int gemm_device(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_
     const bool x3 = mode == DECXB_GEMM_3XTF32;
     PreparedB pb;
     int rc = prepare_b(ctx, scratch, x3, N, K, B, ldb, b_is_nt, s, &pb);
-    if (rc == DECXB_OK) rc = gemm_prepared(ctx, scratch, x3, tile, M, N, K, A, lda, pb, C, ldc, D, ldd, s);
+    if (rc == DECXB_OK) rc = gemm_prepared(ctx, scratch, x3, tile, M, N, K, A, lda, pb, C, ldc, D, ldd, s, bias, act);
     scratch.release();
     return rc;
 }
@@ -137,6 +141,16 @@ extern "C" int decxb_gemm_f32(decxb_ctx* ctx, int mode, int tile, int64_t M, int
     int rc = decxb_bind(ctx);
     if (rc) return rc;
     return gemm_device(ctx, mode, tile, M, N, K, A, lda, B, ldb, false, C, ldc, D, ldd, pick_stream(ctx, stream));
+}
+
+extern "C" int decxb_gemm_f32_act(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_t K,
+                                  const float* A, int64_t lda, const float* B, int64_t ldb,
+                                  const float* C, int64_t ldc, const float* bias, int activation,
+                                  float* D, int64_t ldd, void* stream)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    return gemm_device(ctx, mode, tile, M, N, K, A, lda, B, ldb, false, C, ldc, D, ldd, pick_stream(ctx, stream), bias, activation);
 }
 
 extern "C" int decxb_gemm_f32_nt(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_t K,
@@ -313,9 +327,11 @@ namespace {
 int conv_device(decxb_ctx* ctx, int mode, int algo, int flag,
                 const float* src, int64_t W, int64_t H, int64_t depth,
                 const float* filters, int64_t kW, int64_t kH, int64_t N,
-                float* dst, int64_t batch, int64_t src_stride, int64_t dst_stride, cudaStream_t s)
+                float* dst, int64_t batch, int64_t src_stride, int64_t dst_stride, cudaStream_t s,
+                const float* bias = nullptr, int act = DECXB_ACT_NONE)
 {
     if (mode != DECXB_GEMM_3XTF32 && mode != DECXB_GEMM_1XTF32) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "gemm mode");
+    if (act < DECXB_ACT_NONE || act > DECXB_ACT_TANH) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "activation");
     if (algo != DECXB_CONV_EXPLICIT && algo != DECXB_CONV_IMPLICIT) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "conv algo");
     if (!src || !filters || !dst) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null tensor");
     decxb_conv_geom g;
@@ -359,6 +375,7 @@ int conv_device(decxb_ctx* ctx, int mode, int algo, int flag,
         a.off_y = flag == DECXB_CONV_ZERO_COMPENSATE ? -(int)(kH / 2) : 0;
         a.out_h = g.out_h; a.eq_w = g.eq_w; a.Np = g.Np;
         a.dst = dst; a.dst_img_stride = dst_stride;
+        a.bias = bias; a.act = act;
         rc = decxb_launch_conv_implicit(ctx, a, s);
         scratch.release();
         return rc;
@@ -397,6 +414,7 @@ int conv_device(decxb_ctx* ctx, int mode, int algo, int flag,
             a.C = nullptr; a.ldc = 0;
             a.D = dst + (b0 + j) * dst_stride; a.ldd = g.Np;
             a.tile = DECXB_TILE_AUTO;
+            a.bias = bias; a.act = act;
             if ((rc = decxb_launch_gemm_tn(ctx, a, s))) return rc;
         }
     }
@@ -415,6 +433,18 @@ extern "C" int decxb_conv2_im2col_f32(decxb_ctx* ctx, int mode, int algo, int fl
     if (rc) return rc;
     return conv_device(ctx, mode, algo, flag, src, W, H, depth, filters, kW, kH, N, dst, batch, src_stride, dst_stride,
                        pick_stream(ctx, stream));
+}
+
+extern "C" int decxb_conv2_im2col_f32_act(decxb_ctx* ctx, int mode, int algo, int flag,
+                                          const float* src, int64_t W, int64_t H, int64_t depth,
+                                          const float* filters, int64_t kW, int64_t kH, int64_t N,
+                                          const float* bias, int activation,
+                                          float* dst, int64_t batch, int64_t src_stride, int64_t dst_stride, void* stream)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    return conv_device(ctx, mode, algo, flag, src, W, H, depth, filters, kW, kH, N, dst, batch, src_stride, dst_stride,
+                       pick_stream(ctx, stream), bias, activation);
 }
 
 extern "C" int decxb_conv2_im2col_f32_host(decxb_ctx* ctx, int mode, int algo, int flag,

@@ -113,6 +113,7 @@ struct decxb_gemm_args {
     const float* C; int64_t ldc;
     float* D; int64_t ldd;
     int tile;
+    const float* bias; int act;      /* fused epilogue (NULL / DECXB_ACT_NONE = off) */
 };
 int decxb_launch_gemm_tn(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s);
 
@@ -126,6 +127,7 @@ struct decxb_conv_gemm_args {
     int64_t kW, kH; int off_x, off_y;
     int64_t out_h, eq_w, Np;
     float* dst; int64_t dst_img_stride;
+    const float* bias; int act;
 };
 int decxb_launch_conv_implicit(decxb_ctx* ctx, const decxb_conv_gemm_args& a, cudaStream_t s);
 

@@ -233,7 +233,23 @@ struct GemmParams {
     int kw, off_x, off_y;       /* filter width, source offset of tap (0,0)                      */
     int cblocks;                /* 32-channel blocks per tap                                     */
     int64_t dst_img_stride;     /* floats between destination images                             */
+    /* fused epilogue: D = act(acc (+C) (+bias[col])) */
+    const float* bias;          /* per output column (filter), or NULL                            */
+    int act;                    /* DECXB_ACT_*                                                    */
 };
+
+/* Activations with the reference's formulas (srcs/nn/operators/ReLU.h:48-75 keeps x when its
+ * sign bit is clear; sigmoid.h:45-46: 1 / (1 + __expf(-x)); tanh.h:41-42:
+ * (__expf(2x) - 1) / (__expf(2x) + 1)). */
+__device__ __forceinline__ float apply_act(float x, int act)
+{
+    switch (act) {
+    case DECXB_ACT_RELU: return x < 0.0f ? 0.0f : x;
+    case DECXB_ACT_SIGMOID: return __frcp_rn(__fadd_rn(1.0f, __expf(__fmul_rn(x, -1.0f))));
+    case DECXB_ACT_TANH: { const float e = __expf(__fmul_rn(x, 2.0f)); return __fdiv_rn(__fsub_rn(e, 1.0f), __fadd_rn(e, 1.0f)); }
+    default: return x;
+    }
+}
 
 /* Bounded wait.  Returns false when it gave up (or another role already had). */
 __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, const GemmParams& p, int where, int detail)
@@ -474,11 +490,23 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
                                 const float4 ci = __ldg(reinterpret_cast<const float4*>(crow + col));
                                 o.x += ci.x; o.y += ci.y; o.z += ci.z; o.w += ci.w;
                             }
+                            if (p.bias) {
+                                o.x += __ldg(p.bias + col); o.y += __ldg(p.bias + col + 1);
+                                o.z += __ldg(p.bias + col + 2); o.w += __ldg(p.bias + col + 3);
+                            }
+                            if (p.act) {
+                                o.x = apply_act(o.x, p.act); o.y = apply_act(o.y, p.act);
+                                o.z = apply_act(o.z, p.act); o.w = apply_act(o.w, p.act);
+                            }
                             *reinterpret_cast<float4*>(drow + col) = o;
                         } else {
 #pragma unroll
                             for (int e = 0; e < 4; ++e)
-                                if (col + e < p.N) drow[col + e] = v[j + e] + (crow ? __ldg(crow + col + e) : 0.0f);
+                                if (col + e < p.N) {
+                                    float x = v[j + e] + (crow ? __ldg(crow + col + e) : 0.0f);
+                                    if (p.bias) x += __ldg(p.bias + col + e);
+                                    drow[col + e] = p.act ? apply_act(x, p.act) : x;
+                                }
                         }
                     }
                 }
@@ -634,6 +662,7 @@ int launch_conv_cfg(decxb_ctx* ctx, const decxb_conv_gemm_args& a, cudaStream_t 
     p.M = (int64_t)a.batch * p.tiles_x * p.tiles_y * C::UMMA_M;   /* rows of the tiled problem; real bounds are per pixel */
     p.N = a.Np; p.K = a.k_cols;
     p.C = nullptr; p.ldc = 0; p.D = a.dst; p.ldd = a.Np;
+    p.bias = a.bias; p.act = a.act;
     const int64_t tiles_m = (int64_t)a.batch * p.tiles_x * p.tiles_y;
     if (tiles_m > 0x7fffffffLL) return decxb_fail(ctx, DECXB_ERR_TOO_LARGE, "convolution tiles");
     p.tiles_m = (int)tiles_m;
@@ -660,6 +689,7 @@ int launch_cfg(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s)
     GemmParams p = {};
     p.M = a.M; p.N = a.N; p.K = a.K;
     p.C = a.C; p.ldc = a.ldc; p.D = a.D; p.ldd = a.ldd;
+    p.bias = a.bias; p.act = a.act;
     p.tiles_m = (int)decxb_ceil_div(a.M, C::UMMA_M);
     p.tiles_n = (int)decxb_ceil_div(a.N, C::UMMA_N);
     p.num_kb = (int)decxb_ceil_div(a.K, BK);

@@ -8,6 +8,7 @@ GEMM_3XTF32, GEMM_1XTF32 = 0, 1
 TILE_AUTO, TILE_1CTA_128x128, TILE_2CTA_256x256, TILE_1CTA_128x256, TILE_1CTA_128x64 = 0, 1, 2, 3, 4
 CONV_NO_COMPENSATE, CONV_ZERO_COMPENSATE = 0, 1
 CONV_EXPLICIT, CONV_IMPLICIT = 0, 1
+ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_TANH = 0, 1, 2, 3
 
 _PKG = Path(__file__).resolve().parent
 
@@ -62,6 +63,7 @@ SIGNATURES = {
     "decxb_memset": (_i, [_vp, _vp, _i, _sz]),
     "decxb_fill_uniform_f32": (_i, [_vp, _vp, _u64, _u64, _u64, _u32, _u64, _vp]),
     "decxb_gemm_f32": (_i, [_vp, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
+    "decxb_gemm_f32_act": (_i, [_vp, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i, _vp, _i64, _vp]),
     "decxb_gemm_f32_nt": (_i, [_vp, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
     "decxb_gemm_f32_host": (_i, [_vp, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64]),
     "decxb_gemm_f32_batched": (_i, [_vp, _i, _i, _i64, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp]),
@@ -70,6 +72,7 @@ SIGNATURES = {
     "decxb_conv_geometry": (_i, [_i64, _i64, _i64, _i64, _i64, _i64, _i, C.POINTER(ConvGeom)]),
     "decxb_im2col_pack_f32": (_i, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _i, _vp, _i64, _i64, _i64, _vp]),
     "decxb_conv2_im2col_f32": (_i, [_vp, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp]),
+    "decxb_conv2_im2col_f32_act": (_i, [_vp, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i, _vp, _i64, _i64, _i64, _vp]),
     "decxb_conv2_im2col_f32_host": (_i, [_vp, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64]),
     "decxb_kernel_launch_count": (_u64, [_vp]),
     "decxb_selftest_bounded_wait": (_i, [_vp, _i]),
@@ -185,6 +188,11 @@ class Context:
         self._chk(self.L.decxb_gemm_f32(self.h, mode, tile, M, N, K, _ptr(A), lda, _ptr(B), ldb,
                                         _ptr(Cin), ldc, _ptr(D), ldd, stream))
 
+    def gemm_act(self, M, N, K, A, lda, B, ldb, D, ldd, Cin=None, ldc=0, bias=None, act=ACT_NONE,
+                 mode=GEMM_3XTF32, tile=TILE_AUTO, stream=None):
+        self._chk(self.L.decxb_gemm_f32_act(self.h, mode, tile, M, N, K, _ptr(A), lda, _ptr(B), ldb, _ptr(Cin), ldc,
+                                            _ptr(bias), act, _ptr(D), ldd, stream))
+
     def gemm_nt(self, M, N, K, A, lda, Bt, ldbt, D, ldd, Cin=None, ldc=0, mode=GEMM_3XTF32, tile=TILE_AUTO, stream=None):
         self._chk(self.L.decxb_gemm_f32_nt(self.h, mode, tile, M, N, K, _ptr(A), lda, _ptr(Bt), ldbt,
                                            _ptr(Cin), ldc, _ptr(D), ldd, stream))
@@ -212,6 +220,13 @@ class Context:
                      src_stride=0, dst_stride=0, mode=GEMM_3XTF32, algo=CONV_EXPLICIT, stream=None):
         self._chk(self.L.decxb_conv2_im2col_f32(self.h, mode, algo, flag, _ptr(src), W, H, depth, _ptr(filters),
                                                 kW, kH, N, _ptr(dst), batch, src_stride, dst_stride, stream))
+
+    def conv2_im2col_act(self, src, W, H, depth, filters, kW, kH, N, dst, bias=None, act=ACT_NONE,
+                         flag=CONV_ZERO_COMPENSATE, batch=1, src_stride=0, dst_stride=0, mode=GEMM_3XTF32,
+                         algo=CONV_IMPLICIT, stream=None):
+        self._chk(self.L.decxb_conv2_im2col_f32_act(self.h, mode, algo, flag, _ptr(src), W, H, depth, _ptr(filters),
+                                                    kW, kH, N, _ptr(bias), act, _ptr(dst), batch, src_stride,
+                                                    dst_stride, stream))
 
     def conv2_im2col_host(self, src, W, H, depth, filters, kW, kH, N, dst, flag=CONV_ZERO_COMPENSATE, batch=1,
                           src_stride=0, dst_stride=0, mode=GEMM_3XTF32, algo=CONV_EXPLICIT):

@@ -74,6 +74,13 @@ typedef enum decxb_conv_flag {
     DECXB_CONV_ZERO_COMPENSATE = 1    /* zero border: output W x H                      */
 } decxb_conv_flag;
 
+/* Activation fused into the GEMM / convolution epilogue, with the formulas of the reference's
+ * stand-alone operators de::nn::ReLU_f, sigmoid_f, tanh_f (srcs/nn/operators/ReLU.h:28,
+ * sigmoid.h:25, tanh.h:21). */
+typedef enum decxb_activation {
+    DECXB_ACT_NONE = 0, DECXB_ACT_RELU = 1, DECXB_ACT_SIGMOID = 2, DECXB_ACT_TANH = 3
+} decxb_activation;
+
 /* Convolution algorithm. */
 typedef enum decxb_conv_algo {
     DECXB_CONV_EXPLICIT = 0,  /* pack kernel writes the column matrix, then the GEMM (the reference's two steps) */
@@ -142,6 +149,14 @@ DECXB_API int decxb_gemm_f32(decxb_ctx* ctx, int mode, int tile,
                              const float* B, int64_t ldb,
                              const float* C, int64_t ldc,
                              float* D, int64_t ldd, void* stream);
+
+/* D = act(A*B (+C) + bias[column]): decxb_gemm_f32 with the fused epilogue described at
+ * decxb_conv2_im2col_f32_act (bias: N floats on the device, or NULL). */
+DECXB_API int decxb_gemm_f32_act(decxb_ctx* ctx, int mode, int tile,
+                                 int64_t M, int64_t N, int64_t K,
+                                 const float* A, int64_t lda, const float* B, int64_t ldb,
+                                 const float* C, int64_t ldc, const float* bias, int activation,
+                                 float* D, int64_t ldd, void* stream);
 
 /* Same product with B given K-contiguous: Bt[N][K] ("TN"), the orientation of the
  * convolution's filter matrix (cu_conv_eq_mm, srcs/convolution/CUDA/im2col/eq_GEMM.cuh:109-209). */
@@ -238,6 +253,17 @@ DECXB_API int decxb_conv2_im2col_f32(decxb_ctx* ctx, int mode, int algo, int fla
                                      const float* filters, int64_t kW, int64_t kH, int64_t N,
                                      float* dst, int64_t batch, int64_t src_stride, int64_t dst_stride,
                                      void* stream);
+
+/* The same convolution with a fused epilogue: dst = act(conv + bias[filter]).  bias (device,
+ * ceil4(N) floats, or NULL) and the activation are applied while the accumulator leaves tensor
+ * memory, so the tensor is not read and written again by a separate operator (the reference
+ * runs de::nn::ReLU_f / sigmoid_f / tanh_f as extra passes over the result). */
+DECXB_API int decxb_conv2_im2col_f32_act(decxb_ctx* ctx, int mode, int algo, int flag,
+                                         const float* src, int64_t W, int64_t H, int64_t depth,
+                                         const float* filters, int64_t kW, int64_t kH, int64_t N,
+                                         const float* bias, int activation,
+                                         float* dst, int64_t batch, int64_t src_stride, int64_t dst_stride,
+                                         void* stream);
 
 /* Host-resident tensors; blocks until dst is in host memory. */
 DECXB_API int decxb_conv2_im2col_f32_host(decxb_ctx* ctx, int mode, int algo, int flag,

@@ -341,6 +341,25 @@ DECXO_API int decxo_conv2_im2col(const float* src, int64_t W, int64_t H, int64_t
     return 0;
 }
 
+/* Activations applied after the GEMM / convolution, restating the reference's stand-alone
+ * operators: ReLU keeps x when its sign bit is clear and gives 0 otherwise
+ * (srcs/nn/operators/ReLU.h:48-75), sigmoid = 1 / (1 + exp(-x)) (sigmoid.h:45-46),
+ * tanh = (exp(2x) - 1) / (exp(2x) + 1) (tanh.h:41-42).  The reference uses the GPU's fast
+ * __expf; expf here, so the comparison carries __expf's documented error (2 ulp + a term
+ * growing with |x|).  act: 1 ReLU, 2 sigmoid, 3 tanh; bias (per column, may be NULL) is added
+ * first. */
+DECXO_API void decxo_bias_activation(float* x, int64_t rows, int64_t cols, int64_t ld, const float* bias, int act)
+{
+    for (int64_t r = 0; r < rows; ++r)
+        for (int64_t c = 0; c < cols; ++c) {
+            float v = x[r * ld + c] + (bias ? bias[c] : 0.0f);
+            if (act == 1) v = v < 0.0f ? 0.0f : v;
+            else if (act == 2) v = 1.0f / (1.0f + expf(-v));
+            else if (act == 3) { const float e = expf(2.0f * v); v = (e - 1.0f) / (e + 1.0f); }
+            x[r * ld + c] = v;
+        }
+}
+
 /* Normalised error of the parity rule: max|X - R| / (K * max|a| * max|b|). */
 DECXO_API double decxo_max_abs_diff(const float* x, const float* r, uint64_t n)
 {

@@ -51,6 +51,7 @@ def lib() -> C.CDLL:
         L.decxo_kernel_matrix.argtypes = [fp, i64, i64, i64, i64, i64, i64, fp]
         L.decxo_conv2_im2col.argtypes = [fp, i64, i64, i64, fp, i64, i64, i64, C.c_int, fp]
         L.decxo_conv2_im2col.restype = C.c_int
+        L.decxo_bias_activation.argtypes = [fp, i64, i64, i64, fp, C.c_int]
         L.decxo_num_threads.restype = C.c_int
         L.decxo_set_num_threads.argtypes = [C.c_int]
         _lib = L
@@ -173,6 +174,15 @@ def conv2_im2col(src: np.ndarray, W: int, depth: int, filters: np.ndarray, kW: i
     if rc:
         raise ValueError(f"decxo_conv2_im2col rc={rc}")
     return out
+
+
+def bias_activation(X: np.ndarray, bias: np.ndarray | None, act: int) -> np.ndarray:
+    """act(X + bias[column]) over the last axis, in place on a copy (1 ReLU, 2 sigmoid, 3 tanh)."""
+    Y = np.ascontiguousarray(X, dtype=_F).copy()
+    cols = Y.shape[-1]
+    b = None if bias is None else np.ascontiguousarray(bias, dtype=_F)
+    lib().decxo_bias_activation(_p(Y), Y.size // cols, cols, cols, _p(b), act)
+    return Y
 
 
 def norm_err(X: np.ndarray, R: np.ndarray, K: int, amax: float, bmax: float) -> float:

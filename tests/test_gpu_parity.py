@@ -323,6 +323,33 @@ def test_conv_golden_vectors_of_reference_driver(ctx, golden):
         assert o.norm_err(D, z[name], K, 1.0, 1.0) <= TOL_3X, name
 
 
+@pytest.mark.parametrize("act", [b.ACT_RELU, b.ACT_SIGMOID, b.ACT_TANH])
+def test_fused_bias_activation_epilogue(ctx, act):
+    """dst = act(conv + bias) and D = act(A*B + C + bias) in the epilogue, against the oracle's
+    restatement of the reference's stand-alone activation operators applied to the oracle result."""
+    W, H, C, kW, N = 30, 14, 20, 3, 37
+    src = o.make_tensor(W, H, C, 4)
+    flt = o.make_filters(kW, kW, C, N, 5) * 0.25           # keep sigmoid/tanh away from saturation
+    bias = np.zeros(o.ceil4(N), dtype=np.float32); bias[:N] = o.fill_uniform(N, 6)
+    R = o.bias_activation(o.conv2_im2col(src, W, C, flt, kW, 1), bias, act)
+    g = b.conv_geometry(W, H, C, kW, kW, N, 1)
+    for algo in ALGOS:
+        out = torch.full((g.out_h, g.eq_w, g.Np), float("nan"), device=DEV)
+        ctx.conv2_im2col_act(dev(src), W, H, C, dev(flt), kW, kW, N, out, bias=dev(bias), act=act, algo=algo)
+        ctx.synchronize()
+        assert np.abs(out.cpu().numpy() - R).max() <= 2e-5
+    M, Ng, K = 200, 90, 64
+    A = o.fill_uniform(M * K, 1).reshape(M, K) * 0.25
+    B = o.fill_uniform(K * Ng, 2).reshape(K, Ng)
+    Cin = o.fill_uniform(M * Ng, 3).reshape(M, Ng)
+    gb = o.fill_uniform(Ng, 7)
+    Rg = o.bias_activation(o.gemm_fmaf(A, B, Cin), gb, act)
+    dD = torch.full((M, Ng), float("nan"), device=DEV)
+    ctx.gemm_act(M, Ng, K, dev(A), K, dev(B), Ng, dD, Ng, Cin=dev(Cin), ldc=Ng, bias=dev(gb), act=act)
+    ctx.synchronize()
+    assert np.abs(dD.cpu().numpy() - Rg).max() <= 2e-5
+
+
 @pytest.mark.parametrize("algo", ALGOS)
 def test_conv_batched_equals_per_image(ctx, algo):
     W, H, C, kW, N, nb = 20, 12, 16, 3, 24, 6
