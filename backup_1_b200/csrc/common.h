@@ -53,6 +53,7 @@ struct decxb_ctx {
     decxb_dev_status* h_status = nullptr;   /* pinned host twin                     */
     decxb_dev_status* d_status = nullptr;   /* device word the kernels write        */
     long long wait_limit_ns = 2000000000LL;
+    int pack_variant = 0;               /* 0 = copy-engine (TMA) pack, 1 = shared-memory staged, 2 = direct */
     std::atomic<uint64_t> launches{0};
     std::string last_error;
     /* per-kernel event timing (decxb_profile_*) */
@@ -130,6 +131,9 @@ struct decxb_conv_gemm_args {
     const float* bias; int act;
 };
 int decxb_launch_conv_implicit(decxb_ctx* ctx, const decxb_conv_gemm_args& a, cudaStream_t s);
+
+/* cuTensorMapEncodeTiled, resolved through cudaGetDriverEntryPoint (NULL if unavailable). */
+void* decxb_tensor_map_encoder();
 
 int decxb_launch_pack(decxb_ctx* ctx, const float* src, int64_t W, int64_t H, int64_t depth,
                       int64_t kW, int64_t kH, int flag, float* i2c, int64_t batch,

@@ -104,6 +104,13 @@ extern "C" int decxb_set_wait_limit_ms(decxb_ctx* ctx, int ms)
     return DECXB_OK;
 }
 
+extern "C" int decxb_set_pack_variant(decxb_ctx* ctx, int variant)
+{
+    if (!ctx || variant < 0 || variant > 2) return DECXB_ERR_BAD_PARAM;
+    ctx->pack_variant = variant;
+    return DECXB_OK;
+}
+
 int decxb_check_dev_status(decxb_ctx* ctx)
 {
     DECXB_CUDA_TRY(ctx, cudaMemcpy(ctx->h_status, ctx->d_status, sizeof(decxb_dev_status), cudaMemcpyDeviceToHost));

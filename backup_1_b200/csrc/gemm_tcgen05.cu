@@ -700,6 +700,8 @@ int launch_cfg(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s)
 
 }  // namespace
 
+void* decxb_tensor_map_encoder() { return reinterpret_cast<void*>(get_encode_fn()); }
+
 int decxb_launch_gemm_tn(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s)
 {
     if (a.M <= 0 || a.N <= 0 || a.K <= 0) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "gemm dims must be positive");

@@ -71,6 +71,7 @@ SIGNATURES = {
     "decxb_gemm_f32_noalloc": (_i, [_i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, C.c_char_p, _sz]),
     "decxb_conv_geometry": (_i, [_i64, _i64, _i64, _i64, _i64, _i64, _i, C.POINTER(ConvGeom)]),
     "decxb_im2col_pack_f32": (_i, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _i, _vp, _i64, _i64, _i64, _vp]),
+    "decxb_set_pack_variant": (_i, [_vp, _i]),
     "decxb_conv2_im2col_f32": (_i, [_vp, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp]),
     "decxb_conv2_im2col_f32_act": (_i, [_vp, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i, _vp, _i64, _i64, _i64, _vp]),
     "decxb_conv2_im2col_f32_host": (_i, [_vp, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64]),
@@ -212,6 +213,9 @@ class Context:
                                                      _ptr(Cin), ldc, sC, _ptr(D), ldd, sD))
 
     # -- convolution ----------------------------------------------------------------------
+    def set_pack_variant(self, variant: int):
+        self._chk(self.L.decxb_set_pack_variant(self.h, variant))
+
     def im2col_pack(self, src, W, H, depth, kW, kH, flag, i2c, batch=1, src_stride=0, i2c_stride=0, stream=None):
         self._chk(self.L.decxb_im2col_pack_f32(self.h, _ptr(src), W, H, depth, kW, kH, flag, _ptr(i2c),
                                                batch, src_stride, i2c_stride, stream))

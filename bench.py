@@ -169,12 +169,17 @@ def main():
     ap.add_argument("--tile", type=int, default=0)
     ap.add_argument("--algo", default="implicit", choices=["explicit", "implicit"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--pack-variant", type=int, default=0, help="0 copy-engine pack, 1 staged, 2 direct (explicit convolution)")
+    ap.add_argument("--batch", type=int, default=0, help="override the image count of a convolution workload")
     ap.add_argument("--gather", action="store_true", help="also all-gather the C row-blocks over NCCL (timed separately)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the host-resident leg (default min(steps, 10))")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    wl = WORKLOADS[args.workload]
+    wl = dict(WORKLOADS[args.workload])
+    if args.batch > 0 and wl["kind"] == "conv":
+        wl["batch"] = args.batch
+        wl["desc"] += f" [batch overridden to {args.batch}]"
     if args.impl == "reference":
         return run_reference(args, wl, args.workload)
 
@@ -196,6 +201,7 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (no CPU fallback)")
     dev = torch.device(f"cuda:{local}")
     ctx = b.Context(local)
+    ctx.set_pack_variant(args.pack_variant)
     mode = b.GEMM_3XTF32 if args.mode == "3xtf32" else b.GEMM_1XTF32
     algo = b.CONV_EXPLICIT if args.algo == "explicit" else b.CONV_IMPLICIT
     ts = torch.cuda.Stream(device=dev)

@@ -241,6 +241,12 @@ DECXB_API int decxb_im2col_pack_f32(decxb_ctx* ctx, const float* src, int64_t W,
                                     float* i2c, int64_t batch, int64_t src_stride, int64_t i2c_stride,
                                     void* stream);
 
+/* Which of the three bit-identical pack kernels the context uses: 0 (default) copy-engine pack
+ * (TMA load of the source rows, bulk stores of the output runs; falls back when the rows do not
+ * fit shared memory), 1 threads copy out of shared-memory staged rows, 2 threads copy straight
+ * from global memory.  For measurement and tests. */
+DECXB_API int decxb_set_pack_variant(decxb_ctx* ctx, int variant);
+
 /* Whole convolution on device-resident tensors.  Replaces the pack and GEMM launches of
  * de::cuda::Conv2_MK_im2col (conv2_mk_im2col.h:278-306; drivers :57-162 and :167-274;
  * kernels cu_sIm2Col_r8_within and cu_conv_eq_mm).  dst is the destination tensor in its

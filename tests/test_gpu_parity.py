@@ -215,6 +215,29 @@ def test_pack_is_bit_exact(ctx, case):
     assert np.array_equal(P.view(np.uint32), R.view(np.uint32))
 
 
+@pytest.mark.parametrize("variant", [0, 1, 2])
+def test_pack_variants_are_bit_identical(ctx, variant):
+    """The three pack kernels (copy-engine, shared-memory staged, direct) write the same bytes."""
+    ctx.set_pack_variant(variant)
+    try:
+        for case in [(70, 18, 4, 3, 3, 1), (17, 33, 8, 7, 5, 0), (28, 28, 64, 3, 3, 1), (56, 9, 256, 3, 3, 1),
+                     (8, 8, 16, 17, 17, 1), (40, 3, 300, 3, 3, 1), (33, 5, 1, 1, 1, 0)]:
+            W, H, C, kW, kH, flag = case
+            src = o.make_tensor(W, H, C, 4)
+            assert np.array_equal(run_pack(ctx, src, W, C, kW, kH, flag).view(np.uint32),
+                                  o.im2col_pack(src, W, C, kW, kH, flag).view(np.uint32)), (variant, case)
+        W, H, C, nb = 14, 9, 8, 5
+        imgs = np.stack([o.make_tensor(W, H, C, 4, first_index=i * 10007) for i in range(nb)])
+        _, _, _, M, Kp = o.conv_geometry(W, H, C, 3, 3, 1)
+        out = torch.full((nb, M, Kp), float("nan"), device=DEV)
+        ctx.im2col_pack(dev(imgs), W, H, C, 3, 3, 1, out, batch=nb)
+        ctx.synchronize()
+        for i in range(nb):
+            assert np.array_equal(out[i].cpu().numpy().view(np.uint32), o.im2col_pack(imgs[i], W, C, 3, 3, 1).view(np.uint32))
+    finally:
+        ctx.set_pack_variant(0)
+
+
 def test_pack_golden_vectors_of_reference_kernel(ctx, golden):
     import hashlib
     z, cases = golden
