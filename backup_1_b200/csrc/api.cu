@@ -394,16 +394,32 @@ int conv_device(decxb_ctx* ctx, int mode, int algo, int flag,
     if (group > batch) group = batch;
     /* a group of images forms ONE tall GEMM when the destination images are densely packed */
     const bool dense_dst = dst_stride == g.M * g.Np;
-    float *i2c = nullptr, *a_hi = nullptr, *a_lo = nullptr;
-    if ((rc = scratch.get((size_t)group * i2c_bytes_img, (void**)&i2c))) return rc;
+    /* 3xTF32: the pack is pure indexing, so packing the hi and lo parts of the SOURCE gives the
+     * hi and lo parts of the column matrix; the fp32 column matrix itself is not needed here
+     * (decxb_im2col_pack_f32 is the entry that delivers it) and is neither written nor re-read. */
+    float *i2c = nullptr, *a_hi = nullptr, *a_lo = nullptr, *s_hi = nullptr, *s_lo = nullptr;
+    const int64_t img = H * wp * dp;
     if (x3) {
         if ((rc = scratch.get((size_t)group * i2c_bytes_img, (void**)&a_hi))) return rc;
         if ((rc = scratch.get((size_t)group * i2c_bytes_img, (void**)&a_lo))) return rc;
+        if ((rc = scratch.get((size_t)group * img * 4, (void**)&s_hi))) return rc;
+        if ((rc = scratch.get((size_t)group * img * 4, (void**)&s_lo))) return rc;
+    } else {
+        if ((rc = scratch.get((size_t)group * i2c_bytes_img, (void**)&i2c))) return rc;
     }
     for (int64_t b0 = 0; b0 < batch; b0 += group) {
         const int64_t nb = batch - b0 < group ? batch - b0 : group;
-        if ((rc = decxb_launch_pack(ctx, src + b0 * src_stride, W, H, depth, kW, kH, flag, i2c, nb, src_stride, g.M * g.Kp, s))) return rc;
-        if (x3 && (rc = decxb_launch_split_rows(ctx, i2c, nb * g.M, g.Kp, g.Kp, a_hi, a_lo, g.Kp, nb * g.M, s))) return rc;
+        if (x3) {
+            for (int64_t j = 0; j < (src_stride == img ? 1 : nb); ++j) {
+                const int64_t rows = (src_stride == img ? nb : 1) * H * wp;
+                if ((rc = decxb_launch_split_rows(ctx, src + (b0 + j) * src_stride, rows, dp, dp, s_hi + j * img, s_lo + j * img,
+                                                  dp, rows, s))) return rc;
+            }
+            if ((rc = decxb_launch_pack(ctx, s_hi, W, H, depth, kW, kH, flag, a_hi, nb, img, g.M * g.Kp, s))) return rc;
+            if ((rc = decxb_launch_pack(ctx, s_lo, W, H, depth, kW, kH, flag, a_lo, nb, img, g.M * g.Kp, s))) return rc;
+        } else {
+            if ((rc = decxb_launch_pack(ctx, src + b0 * src_stride, W, H, depth, kW, kH, flag, i2c, nb, src_stride, g.M * g.Kp, s))) return rc;
+        }
         const int64_t n_gemm = dense_dst ? 1 : nb;
         const int64_t rows_per = dense_dst ? nb * g.M : g.M;
         for (int64_t j = 0; j < n_gemm; ++j) {

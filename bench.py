@@ -332,8 +332,9 @@ def main():
         avg_ms = k["ms"] / k["launches"]
         per_step = k["launches"] / args.steps
         if dom == "pack":
-            alg = (H * wp * dp + g.M * g.Kp) * 4 * nb / per_step          # read tensor, write column matrix
-            kname = "decxb_im2col_pack_kernel"
+            packs = 2 if args.mode == "3xtf32" else 1                    # hi and lo parts are packed separately
+            alg = packs * (H * wp * dp + g.M * g.Kp) * 4 * nb / per_step   # read tensor, write column matrix
+            kname = "decxb_im2col_pack_tma_kernel"
         elif wl["kind"] == "conv":
             alg = 3 * g.M * g.Kp * 4 * nb / per_step                      # read column matrix, write hi and lo
             kname = "decxb_split_rows_kernel"
