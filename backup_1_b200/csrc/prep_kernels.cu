@@ -158,6 +158,57 @@ decxb_split_transpose_kernel(const float* __restrict__ in, int64_t K, int64_t N,
     }
 }
 
+/* Vectorised form for 16-byte aligned input with a pitch that is a multiple of 4: 128-bit
+ * loads along n into the tile, 128-bit stores along k out of it.  A thread of the store phase
+ * owns 4 consecutive k of one n, so a 16-thread group writes one 256-byte run of an output
+ * row.  (The tile pitch of 65 words keeps the column reads at most 2-way bank conflicted.) */
+__global__ void __launch_bounds__(256)
+decxb_split_transpose_vec_kernel(const float* __restrict__ in, int64_t K, int64_t N, int64_t ld_in,
+                                 float* __restrict__ hi, float* __restrict__ lo, int64_t ld_out, int raw,
+                                 int64_t tiles_n)
+{
+    __shared__ float tile[64][65];
+    const int tid = threadIdx.x;
+    const int64_t tiles_k = (ld_out + 63) / 64;
+    const int64_t n_tiles = tiles_k * tiles_n;
+    for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+        const int64_t k0 = (t / tiles_n) * 64, n0 = (t % tiles_n) * 64;
+        /* load: 64 k-rows x 16 float4 along n */
+#pragma unroll
+        for (int i = tid; i < 1024; i += 256) {
+            const int kr = i >> 4, n4 = (i & 15) << 2;
+            const int64_t k = k0 + kr, n = n0 + n4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (k < K) {
+                const float* p = in + k * ld_in + n;
+                if (n + 3 < N) v = __ldg(reinterpret_cast<const float4*>(p));
+                else {
+                    if (n < N) v.x = __ldg(p);
+                    if (n + 1 < N) v.y = __ldg(p + 1);
+                    if (n + 2 < N) v.z = __ldg(p + 2);
+                }
+            }
+            tile[kr][n4] = v.x; tile[kr][n4 + 1] = v.y; tile[kr][n4 + 2] = v.z; tile[kr][n4 + 3] = v.w;
+        }
+        __syncthreads();
+        /* store: 64 n-rows x 16 float4 along k */
+#pragma unroll
+        for (int i = tid; i < 1024; i += 256) {
+            const int nr = i >> 4, k4 = (i & 15) << 2;
+            const int64_t n = n0 + nr, k = k0 + k4;
+            if (n < N && k < ld_out) {
+                const float a0 = tile[k4][nr], a1 = tile[k4 + 1][nr], a2 = tile[k4 + 2][nr], a3 = tile[k4 + 3][nr];
+                float4 h, l;
+                if (raw) { h = make_float4(a0, a1, a2, a3); }
+                else { split1(a0, h.x, l.x); split1(a1, h.y, l.y); split1(a2, h.z, l.z); split1(a3, h.w, l.w); }
+                *reinterpret_cast<float4*>(hi + n * ld_out + k) = h;
+                if (!raw) *reinterpret_cast<float4*>(lo + n * ld_out + k) = l;
+            }
+        }
+        __syncthreads();
+    }
+}
+
 int decxb_launch_split_transpose(decxb_ctx* ctx, const float* in, int64_t K, int64_t N, int64_t ld_in,
                                  float* hi, float* lo, int64_t ld_out, int raw, cudaStream_t s)
 {
@@ -166,6 +217,12 @@ int decxb_launch_split_transpose(decxb_ctx* ctx, const float* in, int64_t K, int
     int64_t blocks = tiles_n * tiles_k;
     if (blocks == 0) return DECXB_OK;
     if (blocks > (int64_t)ctx->sm_count * 16) blocks = (int64_t)ctx->sm_count * 16;
+    if (((uintptr_t)in % 16 == 0) && (ld_in % 4 == 0) && ((uintptr_t)hi % 16 == 0) && (raw || (uintptr_t)lo % 16 == 0)) {
+        decxb_launch_scope scope(ctx, s, DECXB_K_SPLIT);
+        decxb_split_transpose_vec_kernel<<<(int)blocks, 256, 0, s>>>(in, K, N, ld_in, hi, lo, ld_out, raw, tiles_n);
+        DECXB_CUDA_TRY(ctx, cudaGetLastError());
+        return DECXB_OK;
+    }
     {
         decxb_launch_scope scope(ctx, s, DECXB_K_SPLIT);
         decxb_split_transpose_kernel<<<(int)blocks, 256, 0, s>>>(in, K, N, ld_in, hi, lo, ld_out, raw, tiles_n);

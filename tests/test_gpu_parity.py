@@ -192,6 +192,24 @@ def test_gemm_config2_full_size_sampled_rows_and_linearity(ctx):
     assert torch.equal(dD2, dD * 2.0)
 
 
+def test_gemm_more_than_2_31_output_elements(ctx):
+    """Index arithmetic beyond 32 bits: D has 70000 x 32768 = 2.29e9 elements (9.2 GB); the
+    reference's pool could not even allocate it (int shift, MemoryPool_D.h:129).  First and last
+    rows against the oracle."""
+    M, N, K = 70000, 32768, 32
+    dA = torch.empty((M, K), device=DEV); dB = torch.empty((K, N), device=DEV)
+    dD = torch.empty((M, N), device=DEV)
+    ctx.fill_uniform(dA, M, K, K, 1); ctx.fill_uniform(dB, K, N, N, 2)
+    ctx.gemm(M, N, K, dA, K, dB, N, dD, N)
+    ctx.synchronize()
+    rows = np.array([0, 1, 65535, 65536, 65537, 69998, 69999])
+    R = o.gemm_fmaf(dA[rows].cpu().numpy(), dB.cpu().numpy())
+    assert o.norm_err(dD[rows].cpu().numpy(), R, K, 1.0, 1.0) <= TOL_3X
+    del dD, dA, dB
+    torch.cuda.empty_cache()
+    ctx.release_cached()
+
+
 # ---- im2col pack ------------------------------------------------------------------------
 PACK_CASES = [(12, 20, 6, 5, 3, 1), (22, 19, 6, 3, 5, 0), (9, 7, 3, 3, 3, 1), (70, 18, 4, 3, 3, 1), (17, 33, 8, 7, 5, 0),
               (28, 28, 64, 3, 3, 1), (8, 8, 16, 17, 17, 1), (5, 4, 1, 1, 1, 1), (40, 3, 300, 3, 3, 1), (224, 224, 64, 3, 3, 1)]
