@@ -219,6 +219,72 @@ extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M
     return decxb_check_dev_status(ctx);
 }
 
+/* ---- fp16 GEMM ------------------------------------------------------------------------------- */
+namespace {
+int gemm_f16_device(decxb_ctx* ctx, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const void* B, int64_t ldb,
+                    const void* C, int64_t ldc, void* D, int64_t ldd, cudaStream_t s)
+{
+    if (M <= 0 || N <= 0 || K <= 0) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "gemm dims must be positive");
+    if (!A || !B || !D) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null operand");
+    if (lda < K || ldb < N || ldd < N || (C && ldc < N))
+        return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
+    Scratch scratch(ctx, s);
+    const int64_t Kp = decxb_ceil_to(K, 8);
+    decxb_gemm_f16_args g = {};
+    g.M = M; g.N = N; g.K = K; g.C = C; g.ldc = ldc; g.D = D; g.ldd = ldd; g.act = DECXB_ACT_NONE;
+    int rc;
+    void* bt = nullptr;
+    if ((rc = scratch.get((size_t)N * Kp * 2, &bt))) return rc;
+    if ((rc = decxb_launch_transpose_f16(ctx, B, K, N, ldb, bt, Kp, s))) return rc;
+    g.Bt = bt; g.ldbt = Kp;
+    if (((uintptr_t)A % 16) || (lda % 8)) {            /* TMA cannot address it: repack with a pitch of ceil8(K) */
+        void* a2 = nullptr;
+        if ((rc = scratch.get((size_t)M * Kp * 2, &a2))) return rc;
+        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(a2, Kp * 2, A, lda * 2, K * 2, M, cudaMemcpyDeviceToDevice, s));
+        g.A = a2; g.lda = Kp;
+    } else { g.A = A; g.lda = lda; }
+    rc = decxb_launch_gemm_f16_tn(ctx, g, s);
+    scratch.release();
+    return rc;
+}
+}  // namespace
+
+extern "C" int decxb_gemm_f16(decxb_ctx* ctx, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda,
+                              const void* B, int64_t ldb, const void* C, int64_t ldc, void* D, int64_t ldd, void* stream)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    return gemm_f16_device(ctx, M, N, K, A, lda, B, ldb, C, ldc, D, ldd, pick_stream(ctx, stream));
+}
+
+extern "C" int decxb_gemm_f16_host(decxb_ctx* ctx, int64_t M, int64_t N, int64_t K, const void* hA, int64_t lda,
+                                   const void* hB, int64_t ldb, const void* hC, int64_t ldc, void* hD, int64_t ldd)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    if (M <= 0 || N <= 0 || K <= 0) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "gemm dims must be positive");
+    if (!hA || !hB || !hD) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null operand");
+    if (lda < K || ldb < N || ldd < N || (hC && ldc < N))
+        return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
+    cudaStream_t s = ctx->stream;
+    Scratch scratch(ctx, s);
+    const int64_t Kp = decxb_ceil_to(K, 8), Np = decxb_ceil_to(N, 8);
+    void *dA, *dB, *dC = nullptr, *dD;
+    if ((rc = scratch.get((size_t)M * Kp * 2, &dA))) return rc;
+    if ((rc = scratch.get((size_t)K * Np * 2, &dB))) return rc;
+    if ((rc = scratch.get((size_t)M * Np * 2, &dD))) return rc;
+    if (hC && (rc = scratch.get((size_t)M * Np * 2, &dC))) return rc;
+    DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dA, Kp * 2, hA, lda * 2, K * 2, M, cudaMemcpyHostToDevice, s));
+    DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dB, Np * 2, hB, ldb * 2, N * 2, K, cudaMemcpyHostToDevice, s));
+    if (hC) DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dC, Np * 2, hC, ldc * 2, N * 2, M, cudaMemcpyHostToDevice, s));
+    rc = gemm_f16_device(ctx, M, N, K, dA, Kp, dB, Np, dC, Np, dD, Np, s);
+    if (rc) { cudaStreamSynchronize(s); return rc; }
+    DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(hD, ldd * 2, dD, Np * 2, N * 2, M, cudaMemcpyDeviceToHost, s));
+    DECXB_CUDA_TRY(ctx, cudaStreamSynchronize(s));
+    scratch.release();
+    return decxb_check_dev_status(ctx);
+}
+
 /* ---- batched GEMM over arrays of equally sized matrices -------------------------------------- */
 extern "C" int decxb_gemm_f32_batched(decxb_ctx* ctx, int mode, int tile, int64_t batch, int64_t M, int64_t N, int64_t K,
                                       const float* A, int64_t lda, int64_t strideA,

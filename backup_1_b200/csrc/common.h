@@ -118,6 +118,21 @@ struct decxb_gemm_args {
 };
 int decxb_launch_gemm_tn(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s);
 
+/* fp16 GEMM on K-contiguous operands: A [M][lda], Bt [N][ldbt] (halves), optional fp16 addend,
+ * fp16 result, fp32 accumulation. */
+struct decxb_gemm_f16_args {
+    int64_t M, N, K;
+    const void* A; int64_t lda;
+    const void* Bt; int64_t ldbt;
+    const void* C; int64_t ldc;
+    void* D; int64_t ldd;
+    int act;
+};
+int decxb_launch_gemm_f16_tn(decxb_ctx* ctx, const decxb_gemm_f16_args& a, cudaStream_t s);
+/* in[K][ld_in] halves (K rows, N columns) -> out[N][ld_out] halves, columns >= K zeroed. */
+int decxb_launch_transpose_f16(decxb_ctx* ctx, const void* in, int64_t K, int64_t N, int64_t ld_in,
+                               void* out, int64_t ld_out, cudaStream_t s);
+
 /* Implicit-GEMM convolution: the A tiles are boxes of the (split) source tensor, the filter
  * matrix is [k_rows][ldk] with one 32-channel-padded block row per tap: column
  * (tap * cblocks + cb) * 32 + c'. */

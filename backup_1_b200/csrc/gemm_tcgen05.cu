@@ -27,6 +27,7 @@
 #include "common.h"
 
 #include <cudaTypedefs.h>
+#include <cuda_fp16.h>
 
 namespace {
 
@@ -165,6 +166,22 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint
     }
 }
 
+template <int CTAS>
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
+{
+    if (CTAS == 1) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+    }
+}
+
 /* Make the barrier observe completion of every tcgen05.mma this thread issued so far.
  * In a CTA pair the arrival is delivered to the same barrier offset in both CTAs. */
 template <int CTAS>
@@ -213,6 +230,12 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr)
 
 /* Instruction descriptor: D fp32 (bits 4-5 = 1), A and B TF32 (bits 7-9, 10-12 = 2), both
  * K-major (bits 15, 16 = 0), N>>3 at bits 17-22, M>>4 at bits 24-28. */
+/* Same with fp16 operands (format code 0 at bits 7-9 and 10-12), fp32 accumulator. */
+__host__ __device__ constexpr uint32_t make_idesc_f16(int umma_m, int umma_n)
+{
+    return (1u << 4) | ((uint32_t)(umma_n >> 3) << 17) | ((uint32_t)(umma_m >> 4) << 24);
+}
+
 __host__ __device__ constexpr uint32_t make_idesc(int umma_m, int umma_n)
 {
     return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(umma_n >> 3) << 17) | ((uint32_t)(umma_m >> 4) << 24);
@@ -289,7 +312,9 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 /* --------------------------------------------------------------------------------------
  * CTAS   : 1 or 2 CTAs per tile (cta_group)
  * BN     : rows of the B operand (columns of D) loaded per CTA; UMMA N = BN * CTAS
- * NSPLIT : 3 = 3xTF32 (hi and lo parts of both operands), 1 = plain TF32
+ * NSPLIT : 3 = 3xTF32 (hi and lo parts of both operands), 1 = plain TF32,
+ *          16 = fp16 operands and fp16 result with fp32 accumulation (kind::f16); a k-block is
+ *          then 64 halves, still one 128-byte row, and a k-step 16 halves, still 32 bytes
  * ------------------------------------------------------------------------------------ */
 template <int CTAS, int BN, int NSPLIT>
 struct Cfg {
@@ -373,7 +398,7 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
                 int tap = 0, cb = 0;       /* convolution: filter tap and channel block of this k-block */
                 for (int kb = 0; kb < p.num_kb; ++kb) {
                     if (!wait_bounded(empty_bar(stage), phase ^ 1u, p, 100 + stage, t)) { alive = false; break; }
-                    const int kx = kb * BK;
+                    const int kx = kb * (NSPLIT == 16 ? 64 : BK);       /* elements per 128-byte k-block */
                     const int ky_t = CONV ? tap / p.kw : 0;
                     const int cc = cb * BK, xx = px0 + (tap - ky_t * p.kw) + p.off_x, yy = py0 + ky_t + p.off_y;
                     if (CTAS == 1) {
@@ -408,7 +433,7 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
     } else if (warp == 1) {
         /* ------------------------------------------------------------ MMA issuer ------ */
         if (is_leader && lane == 0) {
-            constexpr uint32_t idesc = make_idesc(C::UMMA_M, C::UMMA_N);
+            constexpr uint32_t idesc = NSPLIT == 16 ? make_idesc_f16(C::UMMA_M, C::UMMA_N) : make_idesc(C::UMMA_M, C::UMMA_N);
             int stage = 0; uint32_t phase = 0;
             int it = 0;
             bool alive = true;
@@ -434,6 +459,8 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
                             umma_tf32<CTAS>(tmem_d, da_lo + koff, db_hi + koff, idesc, first);
                             umma_tf32<CTAS>(tmem_d, da_hi + koff, db_lo + koff, idesc, 1u);
                             umma_tf32<CTAS>(tmem_d, da_hi + koff, db_hi + koff, idesc, 1u);
+                        } else if (NSPLIT == 16) {
+                            umma_f16<CTAS>(tmem_d, da_hi + koff, db_hi + koff, idesc, first);
                         } else {
                             umma_tf32<CTAS>(tmem_d, da_hi + koff, db_hi + koff, idesc, first);
                         }
@@ -480,7 +507,35 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
                 float v[32];
                 tmem_ld_32x32(taddr + (uint32_t)c, v);
                 tmem_ld_wait();
-                if (row_ok) {
+                if (NSPLIT == 16) {
+                    /* fp16 result (and addend): 8 halves = 16 bytes per store */
+                    if (row_ok) {
+                        __half* __restrict__ hrow = reinterpret_cast<__half*>(p.D) + row * p.ldd;
+                        const __half* __restrict__ hc = p.C ? reinterpret_cast<const __half*>(p.C) + row * p.ldc : nullptr;
+                        const bool hd_vec = ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) && (p.ldd % 8 == 0);
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            const int64_t col = col0 + c + j;
+                            float x[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                x[e] = v[j + e] + ((hc && col + e < p.N) ? __half2float(hc[col + e]) : 0.0f);
+                                if (p.act) x[e] = apply_act(x[e], p.act);
+                            }
+                            if (col + 7 < p.N && hd_vec) {
+                                uint4 o;
+                                __half2 h0 = __floats2half2_rn(x[0], x[1]), h1 = __floats2half2_rn(x[2], x[3]);
+                                __half2 h2 = __floats2half2_rn(x[4], x[5]), h3 = __floats2half2_rn(x[6], x[7]);
+                                o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
+                                o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
+                                *reinterpret_cast<uint4*>(hrow + col) = o;
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) if (col + e < p.N) hrow[col + e] = __float2half_rn(x[e]);
+                            }
+                        }
+                    }
+                } else if (row_ok) {
 #pragma unroll
                     for (int j = 0; j < 32; j += 4) {
                         const int64_t col = col0 + c + j;
@@ -561,6 +616,24 @@ PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn()
 }
 
 /* rows x K fp32 array with K contiguous and a row pitch of `ld` floats; box = 32 floats x box_rows. */
+/* rows x K fp16 array with K contiguous and a row pitch of `ld` halves; box = 64 halves x box_rows. */
+int make_map_f16(decxb_ctx* ctx, CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64_t ld, int box_rows)
+{
+    auto fn = get_encode_fn();
+    if (!fn) return decxb_fail(ctx, DECXB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
+    if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld % 8))
+        return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "TMA fp16 operand must be 16-byte aligned with a pitch that is a multiple of 8 halves");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return decxb_fail(ctx, DECXB_ERR_CUDA, "cuTensorMapEncodeTiled (fp16) failed: " + std::to_string((int)r));
+    return DECXB_OK;
+}
+
 int make_map(decxb_ctx* ctx, CUtensorMap* map, const float* base, int64_t rows, int64_t K, int64_t ld, int box_rows)
 {
     auto fn = get_encode_fn();
@@ -698,7 +771,39 @@ int launch_cfg(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s)
     return launch_kernel<CTAS, BN, NSPLIT, false>(ctx, ma_hi, ma_lo, mb_hi, mb_lo, p, s);
 }
 
+
+template <int CTAS, int BN>
+int launch_cfg_f16(decxb_ctx* ctx, const decxb_gemm_f16_args& a, cudaStream_t s)
+{
+    using C = Cfg<CTAS, BN, 16>;
+    CUtensorMap ma, mb;
+    int rc;
+    if ((rc = make_map_f16(ctx, &ma, a.A, a.M, a.K, a.lda, BM_CTA))) return rc;
+    if ((rc = make_map_f16(ctx, &mb, a.Bt, a.N, a.K, a.ldbt, BN))) return rc;
+    GemmParams p = {};
+    p.M = a.M; p.N = a.N; p.K = a.K;
+    p.C = reinterpret_cast<const float*>(a.C); p.ldc = a.ldc;
+    p.D = reinterpret_cast<float*>(a.D); p.ldd = a.ldd;
+    p.bias = nullptr; p.act = a.act;
+    p.tiles_m = (int)decxb_ceil_div(a.M, C::UMMA_M);
+    p.tiles_n = (int)decxb_ceil_div(a.N, C::UMMA_N);
+    p.num_kb = (int)decxb_ceil_div(a.K, 64);
+    p.wait_limit_ns = ctx->wait_limit_ns;
+    p.status = ctx->d_status;
+    return launch_kernel<CTAS, BN, 16, false>(ctx, ma, ma, mb, mb, p, s);
+}
+
 }  // namespace
+
+int decxb_launch_gemm_f16_tn(decxb_ctx* ctx, const decxb_gemm_f16_args& a, cudaStream_t s)
+{
+    if (a.M <= 0 || a.N <= 0 || a.K <= 0) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "gemm dims must be positive");
+    if (a.M > 0x7fffffffLL || a.N > 0x7fffffffLL || a.K > 0x7fffffffLL) return decxb_fail(ctx, DECXB_ERR_TOO_LARGE, "gemm dims");
+    const int64_t t2 = decxb_ceil_div(a.M, 256) * decxb_ceil_div(a.N, 256);
+    if (a.N <= 64) return launch_cfg_f16<1, 64>(ctx, a, s);
+    if (t2 * 2 < ctx->sm_count / 2 || a.N <= 128 || a.M <= 128) return launch_cfg_f16<1, 128>(ctx, a, s);
+    return launch_cfg_f16<2, 128>(ctx, a, s);
+}
 
 void* decxb_tensor_map_encoder() { return reinterpret_cast<void*>(get_encode_fn()); }
 

@@ -274,3 +274,47 @@ int decxb_launch_filter_matrix(decxb_ctx* ctx, const float* filters, int64_t kW,
     DECXB_CUDA_TRY(ctx, cudaGetLastError());
     return DECXB_OK;
 }
+
+/* fp16 transpose for the fp16 GEMM's B operand: in[K][ld_in] -> out[N][ld_out], 64x64 tiles of
+ * 16-bit words through shared memory; output columns k >= K (up to ld_out) are zero. */
+__global__ void __launch_bounds__(256)
+decxb_transpose_f16_kernel(const unsigned short* __restrict__ in, int64_t K, int64_t N, int64_t ld_in,
+                           unsigned short* __restrict__ out, int64_t ld_out, int64_t tiles_n)
+{
+    __shared__ unsigned short tile[64][66];
+    const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+    const int64_t tiles_k = (ld_out + 63) / 64;
+    const int64_t n_tiles = tiles_k * tiles_n;
+    for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+        const int64_t k0 = (t / tiles_n) * 64, n0 = (t % tiles_n) * 64;
+#pragma unroll 4
+        for (int j = ty; j < 64; j += 4) {
+            const int64_t k = k0 + j, n = n0 + tx;
+            tile[j][tx] = (k < K && n < N) ? in[k * ld_in + n] : (unsigned short)0;
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int j = ty; j < 64; j += 4) {
+            const int64_t n = n0 + j, k = k0 + tx;
+            if (n < N && k < ld_out) out[n * ld_out + k] = tile[tx][j];
+        }
+        __syncthreads();
+    }
+}
+
+int decxb_launch_transpose_f16(decxb_ctx* ctx, const void* in, int64_t K, int64_t N, int64_t ld_in,
+                               void* out, int64_t ld_out, cudaStream_t s)
+{
+    if (ld_out < K) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "transpose_f16 pitch");
+    const int64_t tiles_n = (N + 63) / 64, tiles_k = (ld_out + 63) / 64;
+    int64_t blocks = tiles_n * tiles_k;
+    if (blocks == 0) return DECXB_OK;
+    if (blocks > (int64_t)ctx->sm_count * 16) blocks = (int64_t)ctx->sm_count * 16;
+    {
+        decxb_launch_scope scope(ctx, s, DECXB_K_SPLIT);
+        decxb_transpose_f16_kernel<<<(int)blocks, 256, 0, s>>>(static_cast<const unsigned short*>(in), K, N, ld_in,
+                                                               static_cast<unsigned short*>(out), ld_out, tiles_n);
+    }
+    DECXB_CUDA_TRY(ctx, cudaGetLastError());
+    return DECXB_OK;
+}

@@ -65,41 +65,48 @@ static std::shared_ptr<float> device_block(size_t bytes)
     return std::shared_ptr<float>(static_cast<float*>(q), [ctx](float* x) { decxb_free(ctx, x); });
 }
 
-/* ---- Matrix ------------------------------------------------------------------------------------ */
-class _Matrix : public de::Matrix<float> {
+/* ---- Matrix (float: pitch = ceil8(width); Half: pitch = ceil16(width), Matrix.h:24-25) ----------- */
+template <typename T> struct mat_align { static constexpr uint value = 8; };
+template <> struct mat_align<de::Half> { static constexpr uint value = 16; };
+
+template <typename T>
+class _MatrixT : public de::Matrix<T> {
 public:
     uint width = 0, height = 0, pitch = 0;
     int Store_Type = Page_Default;
     size_t element_num = 0, total_bytes = 0, _element_num = 0, _total_bytes = 0;
-    std::shared_ptr<float> Mat;
+    std::shared_ptr<float> Mat;                     /* raw storage; data() views it as T */
 
+    T* data() { return reinterpret_cast<T*>(Mat.get()); }
     void _attribute_assign(uint w, uint h, int store)
     {
         width = w; height = h; Store_Type = store;
-        pitch = ceil_to(w, 8);                                     /* _MATRIX_ALIGN_4B_, Matrix.h:24 */
-        element_num = (size_t)w * h; total_bytes = element_num * sizeof(float);
-        _element_num = (size_t)pitch * h; _total_bytes = _element_num * sizeof(float);
+        pitch = ceil_to(w, mat_align<T>::value);
+        element_num = (size_t)w * h; total_bytes = element_num * sizeof(T);
+        _element_num = (size_t)pitch * h; _total_bytes = _element_num * sizeof(T);
     }
     void construct(uint w, uint h, int store) { _attribute_assign(w, h, store); Mat = host_block(_total_bytes, store); }
     void re_construct(uint w, uint h, int store)
     {
         if (w != width || h != height || store != Store_Type || !Mat) construct(w, h, store);   /* Matrix.h:239-248 */
     }
-    _Matrix() { _attribute_assign(0, 0, Page_Default); }
-    _Matrix(uint w, uint h, int store) { construct(w, h, store); }
+    _MatrixT() { _attribute_assign(0, 0, Page_Default); }
+    _MatrixT(uint w, uint h, int store) { construct(w, h, store); }
     uint Width() override { return width; }
     uint Height() override { return height; }
     size_t TotalBytes() override { return total_bytes; }
-    float& index(const int row, const int col) override { return Mat.get()[(size_t)pitch * row + col]; }
+    T& index(const int row, const int col) override { return data()[(size_t)pitch * row + col]; }
     void release() override { Mat.reset(); }
-    de::Matrix<float>& operator=(de::Matrix<float>& src) override
+    de::Matrix<T>& operator=(de::Matrix<T>& src) override
     {
-        _Matrix& s = dynamic_cast<_Matrix&>(src);
+        _MatrixT& s = dynamic_cast<_MatrixT&>(src);
         _attribute_assign(s.width, s.height, s.Store_Type);
         Mat = s.Mat;
         return *this;
     }
 };
+using _Matrix = _MatrixT<float>;
+using _MatrixH = _MatrixT<de::Half>;
 
 class _MatrixArray : public de::MatrixArray<float> {
 public:
@@ -135,45 +142,51 @@ public:
     void release() override { MatArr.reset(); }
 };
 
-class _GPU_Matrix : public de::GPU_Matrix<float> {
+template <typename T>
+class _GPU_MatrixT : public de::GPU_Matrix<T> {
 public:
     uint width = 0, height = 0, pitch = 0;
     size_t total_bytes = 0, _total_bytes = 0;
     std::shared_ptr<float> Mat;
 
+    T* data() { return reinterpret_cast<T*>(Mat.get()); }
     void _attribute_assign(uint w, uint h)
     {
-        width = w; height = h; pitch = ceil_to(w, 8);              /* GPU_Matrix.h:211-223 */
-        total_bytes = (size_t)w * h * sizeof(float); _total_bytes = (size_t)pitch * h * sizeof(float);
+        width = w; height = h; pitch = ceil_to(w, mat_align<T>::value);   /* GPU_Matrix.h:211-223, :264 */
+        total_bytes = (size_t)w * h * sizeof(T); _total_bytes = (size_t)pitch * h * sizeof(T);
     }
     void construct(uint w, uint h) { _attribute_assign(w, h); Mat = device_block(_total_bytes); }
     void re_construct(uint w, uint h) { if (w != width || h != height || !Mat) construct(w, h); }
-    _GPU_Matrix() { _attribute_assign(0, 0); }
-    _GPU_Matrix(uint w, uint h) { construct(w, h); }
+    _GPU_MatrixT() { _attribute_assign(0, 0); }
+    _GPU_MatrixT(uint w, uint h) { construct(w, h); }
     uint Width() override { return width; }
     uint Height() override { return height; }
     size_t TotalBytes() override { return total_bytes; }
-    void Load_from_host(de::Matrix<float>& src) override            /* GPU_Matrix.h:334-343 */
+    void Load_from_host(de::Matrix<T>& src) override            /* GPU_Matrix.h:334-343 */
     {
-        _Matrix& s = dynamic_cast<_Matrix&>(src);
+        _MatrixT<T>& s = dynamic_cast<_MatrixT<T>&>(src);
         if (s.width != width || s.height != height) return;
-        decxb_memcpy2d(cuP.ctx, Mat.get(), (size_t)pitch * 4, s.Mat.get(), (size_t)s.pitch * 4, (size_t)width * 4, height, 1);
+        decxb_memcpy2d(cuP.ctx, Mat.get(), (size_t)pitch * sizeof(T), s.Mat.get(), (size_t)s.pitch * sizeof(T),
+                       (size_t)width * sizeof(T), height, 1);
     }
-    void Load_to_host(de::Matrix<float>& dst) override              /* GPU_Matrix.h:345-354 */
+    void Load_to_host(de::Matrix<T>& dst) override              /* GPU_Matrix.h:345-354 */
     {
-        _Matrix& d = dynamic_cast<_Matrix&>(dst);
+        _MatrixT<T>& d = dynamic_cast<_MatrixT<T>&>(dst);
         if (d.width != width || d.height != height) return;
-        decxb_memcpy2d(cuP.ctx, d.Mat.get(), (size_t)d.pitch * 4, Mat.get(), (size_t)pitch * 4, (size_t)width * 4, height, 2);
+        decxb_memcpy2d(cuP.ctx, d.Mat.get(), (size_t)d.pitch * sizeof(T), Mat.get(), (size_t)pitch * sizeof(T),
+                       (size_t)width * sizeof(T), height, 2);
     }
     void release() override { Mat.reset(); }
-    de::GPU_Matrix<float>& operator=(de::GPU_Matrix<float>& src) override
+    de::GPU_Matrix<T>& operator=(de::GPU_Matrix<T>& src) override
     {
-        _GPU_Matrix& s = dynamic_cast<_GPU_Matrix&>(src);
+        _GPU_MatrixT& s = dynamic_cast<_GPU_MatrixT&>(src);
         _attribute_assign(s.width, s.height);
         Mat = s.Mat;
         return *this;
     }
 };
+using _GPU_Matrix = _GPU_MatrixT<float>;
+using _GPU_MatrixH = _GPU_MatrixT<de::Half>;
 
 /* ---- Tensor / TensorArray (host and device share the geometry) ------------------------------------ */
 struct TensorGeom {
@@ -325,6 +338,14 @@ template <> MatrixArray<float>& CreateMatrixArrayRef<float>() { return *(new dec
 template <> MatrixArray<float>* CreateMatrixArrayPtr<float>() { return new decx::_MatrixArray(); }
 template <> MatrixArray<float>& CreateMatrixArrayRef<float>(uint w, uint h, uint n, const int f) { return *(new decx::_MatrixArray(w, h, n, f)); }
 template <> MatrixArray<float>* CreateMatrixArrayPtr<float>(uint w, uint h, uint n, const int f) { return new decx::_MatrixArray(w, h, n, f); }
+template <> Matrix<Half>& CreateMatrixRef<Half>() { return *(new decx::_MatrixH()); }
+template <> Matrix<Half>* CreateMatrixPtr<Half>() { return new decx::_MatrixH(); }
+template <> Matrix<Half>& CreateMatrixRef<Half>(const uint w, const uint h, const int st) { return *(new decx::_MatrixH(w, h, st)); }
+template <> Matrix<Half>* CreateMatrixPtr<Half>(const uint w, const uint h, const int st) { return new decx::_MatrixH(w, h, st); }
+template <> GPU_Matrix<Half>& CreateGPUMatrixRef<Half>() { return *(new decx::_GPU_MatrixH()); }
+template <> GPU_Matrix<Half>* CreateGPUMatrixPtr<Half>() { return new decx::_GPU_MatrixH(); }
+template <> GPU_Matrix<Half>& CreateGPUMatrixRef<Half>(const uint w, const uint h) { return *(new decx::_GPU_MatrixH(w, h)); }
+template <> GPU_Matrix<Half>* CreateGPUMatrixPtr<Half>(const uint w, const uint h) { return new decx::_GPU_MatrixH(w, h); }
 template <> GPU_Matrix<float>& CreateGPUMatrixRef<float>() { return *(new decx::_GPU_Matrix()); }
 template <> GPU_Matrix<float>* CreateGPUMatrixPtr<float>() { return new decx::_GPU_Matrix(); }
 template <> GPU_Matrix<float>& CreateGPUMatrixRef<float>(const uint w, const uint h) { return *(new decx::_GPU_Matrix(w, h)); }
@@ -406,6 +427,46 @@ DH GEMM(Matrix<float>& A, Matrix<float>& B, Matrix<float>& dst) { return gemm_ho
 DH GEMM(Matrix<float>& A, Matrix<float>& B, Matrix<float>& C, Matrix<float>& dst) { return gemm_host(A, B, &C, dst); }
 DH GEMM(GPU_Matrix<float>& A, GPU_Matrix<float>& B, GPU_Matrix<float>& dst) { return gemm_dev(A, B, nullptr, dst); }
 DH GEMM(GPU_Matrix<float>& A, GPU_Matrix<float>& B, GPU_Matrix<float>& C, GPU_Matrix<float>& dst) { return gemm_dev(A, B, &C, dst); }
+
+static DH gemm_host_h(Matrix<Half>& A, Matrix<Half>& B, Matrix<Half>* C, Matrix<Half>& dst)
+{
+    DH handle;
+    decx::_MatrixH& _A = dynamic_cast<decx::_MatrixH&>(A);
+    decx::_MatrixH& _B = dynamic_cast<decx::_MatrixH&>(B);
+    decx::_MatrixH* _C = C ? dynamic_cast<decx::_MatrixH*>(C) : nullptr;
+    decx::_MatrixH& _dst = dynamic_cast<decx::_MatrixH&>(dst);
+    if (!decx::cuP.is_init) { decx::Not_init(&handle); return handle; }
+    if (_A.width != _B.height) { decx::MDim_Not_Matching(&handle); return handle; }
+    if (_C && (_C->width != _B.width || _C->height != _A.height)) { decx::MDim_Not_Matching(&handle); return handle; }
+    _dst.re_construct(_B.width, _A.height, decx::Page_Locked);
+    int rc = decxb_gemm_f16_host(decx::cuP.ctx, _A.height, _B.width, _A.width, _A.Mat.get(), _A.pitch, _B.Mat.get(), _B.pitch,
+                                 _C ? _C->Mat.get() : nullptr, _C ? _C->pitch : 0, _dst.Mat.get(), _dst.pitch);
+    decx::from_status(&handle, rc);
+    return handle;
+}
+
+static DH gemm_dev_h(GPU_Matrix<Half>& A, GPU_Matrix<Half>& B, GPU_Matrix<Half>* C, GPU_Matrix<Half>& dst)
+{
+    DH handle;
+    decx::_GPU_MatrixH& _A = dynamic_cast<decx::_GPU_MatrixH&>(A);
+    decx::_GPU_MatrixH& _B = dynamic_cast<decx::_GPU_MatrixH&>(B);
+    decx::_GPU_MatrixH* _C = C ? dynamic_cast<decx::_GPU_MatrixH*>(C) : nullptr;
+    decx::_GPU_MatrixH& _dst = dynamic_cast<decx::_GPU_MatrixH&>(dst);
+    if (!decx::cuP.is_init) { decx::Not_init(&handle); return handle; }
+    if (_A.width != _B.height) { decx::MDim_Not_Matching(&handle); return handle; }
+    if (_C && (_C->width != _B.width || _C->height != _A.height)) { decx::MDim_Not_Matching(&handle); return handle; }
+    _dst.re_construct(_B.width, _A.height);
+    int rc = decxb_gemm_f16(decx::cuP.ctx, _A.height, _B.width, _A.width, _A.Mat.get(), _A.pitch, _B.Mat.get(), _B.pitch,
+                            _C ? _C->Mat.get() : nullptr, _C ? _C->pitch : 0, _dst.Mat.get(), _dst.pitch, nullptr);
+    if (rc == DECXB_OK) rc = decxb_synchronize(decx::cuP.ctx);
+    decx::from_status(&handle, rc);
+    return handle;
+}
+
+DH GEMM(Matrix<Half>& A, Matrix<Half>& B, Matrix<Half>& dst) { return gemm_host_h(A, B, nullptr, dst); }
+DH GEMM(Matrix<Half>& A, Matrix<Half>& B, Matrix<Half>& C, Matrix<Half>& dst) { return gemm_host_h(A, B, &C, dst); }
+DH GEMM(GPU_Matrix<Half>& A, GPU_Matrix<Half>& B, GPU_Matrix<Half>& dst) { return gemm_dev_h(A, B, nullptr, dst); }
+DH GEMM(GPU_Matrix<Half>& A, GPU_Matrix<Half>& B, GPU_Matrix<Half>& C, GPU_Matrix<Half>& dst) { return gemm_dev_h(A, B, &C, dst); }
 
 static DH gemm3(MatrixArray<float>& A, MatrixArray<float>& B, MatrixArray<float>* C, MatrixArray<float>& dst)
 {

@@ -66,6 +66,8 @@ SIGNATURES = {
     "decxb_gemm_f32_act": (_i, [_vp, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i, _vp, _i64, _vp]),
     "decxb_gemm_f32_nt": (_i, [_vp, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
     "decxb_gemm_f32_host": (_i, [_vp, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64]),
+    "decxb_gemm_f16": (_i, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
+    "decxb_gemm_f16_host": (_i, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64]),
     "decxb_gemm_f32_batched": (_i, [_vp, _i, _i, _i64, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp]),
     "decxb_gemm_f32_batched_host": (_i, [_vp, _i, _i, _i64, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64]),
     "decxb_gemm_f32_noalloc": (_i, [_i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, C.c_char_p, _sz]),
@@ -201,6 +203,12 @@ class Context:
     def gemm_host(self, M, N, K, A, lda, B, ldb, D, ldd, Cin=None, ldc=0, mode=GEMM_3XTF32, tile=TILE_AUTO):
         self._chk(self.L.decxb_gemm_f32_host(self.h, mode, tile, M, N, K, _ptr(A), lda, _ptr(B), ldb,
                                              _ptr(Cin), ldc, _ptr(D), ldd))
+
+    def gemm_f16(self, M, N, K, A, lda, B, ldb, D, ldd, Cin=None, ldc=0, stream=None):
+        self._chk(self.L.decxb_gemm_f16(self.h, M, N, K, _ptr(A), lda, _ptr(B), ldb, _ptr(Cin), ldc, _ptr(D), ldd, stream))
+
+    def gemm_f16_host(self, M, N, K, A, lda, B, ldb, D, ldd, Cin=None, ldc=0):
+        self._chk(self.L.decxb_gemm_f16_host(self.h, M, N, K, _ptr(A), lda, _ptr(B), ldb, _ptr(Cin), ldc, _ptr(D), ldd))
 
     def gemm_batched(self, batch, M, N, K, A, lda, sA, B, ldb, sB, D, ldd, sD, Cin=None, ldc=0, sC=0,
                      mode=GEMM_3XTF32, tile=TILE_AUTO, stream=None):

@@ -36,6 +36,9 @@ typedef struct DECX_Handle {
     char* error_string;
 } DH;
 
+/* srcs/classes/classes_util.h:59-62: storage type of IEEE half values. */
+struct alignas(2) Half { unsigned short val; };
+
 /* srcs/core/configs/config.h:62-78.  Must be called before any de::cuda operation;
  * operations return DECX_FAIL_not_init otherwise (srcs/GEMM/CUDA/large_squares/GEMM.h:63-66). */
 void InitCuda();
@@ -175,6 +178,14 @@ DH GEMM(Matrix<float>& A, Matrix<float>& B, Matrix<float>& dst);
 DH GEMM(Matrix<float>& A, Matrix<float>& B, Matrix<float>& C, Matrix<float>& dst);
 DH GEMM(GPU_Matrix<float>& A, GPU_Matrix<float>& B, GPU_Matrix<float>& dst);
 DH GEMM(GPU_Matrix<float>& A, GPU_Matrix<float>& B, GPU_Matrix<float>& C, GPU_Matrix<float>& dst);
+
+/* srcs/GEMM/CUDA/large_squares/GEMM.h:33-49: the same four entry points on half matrices
+ * (pitch = ceil16(width) halves, Matrix.h:25,315).  Accumulation is fp32 here (the reference
+ * accumulates in half). */
+DH GEMM(Matrix<Half>& A, Matrix<Half>& B, Matrix<Half>& dst);
+DH GEMM(Matrix<Half>& A, Matrix<Half>& B, Matrix<Half>& C, Matrix<Half>& dst);
+DH GEMM(GPU_Matrix<Half>& A, GPU_Matrix<Half>& B, GPU_Matrix<Half>& dst);
+DH GEMM(GPU_Matrix<Half>& A, GPU_Matrix<Half>& B, GPU_Matrix<Half>& C, GPU_Matrix<Half>& dst);
 
 /* srcs/GEMM/CUDA/large_squares/GEMM3.h:27-37: dst[i] = A[i]*B[i] (+ C[i]) for every matrix of
  * the arrays, uploads, products and downloads overlapped. */

@@ -176,6 +176,19 @@ DECXB_API int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile,
                                   const float* hC, int64_t ldc,
                                   float* hD, int64_t ldd);
 
+/* fp16 product D = A*B (+C): operands, addend and result are IEEE half (passed as void*), the
+ * accumulation is fp32 on the tensor cores (tcgen05 kind::f16).  Replaces the fp16 overloads of
+ * de::cuda::GEMM (srcs/GEMM/CUDA/large_squares/GEMM.h:33-49, kernels cu_GEMM_fp16_spec /
+ * _ABC_spec, GEMM.cuh:119, :297), which accumulate in half with __hfma2
+ * (srcs/GEMM/CUDA/GEMM_kernel_def.cuh:100-107): results here are at least as close to the
+ * exact product as the reference's.  Leading dimensions in halves. */
+DECXB_API int decxb_gemm_f16(decxb_ctx* ctx, int64_t M, int64_t N, int64_t K,
+                             const void* A, int64_t lda, const void* B, int64_t ldb,
+                             const void* C, int64_t ldc, void* D, int64_t ldd, void* stream);
+DECXB_API int decxb_gemm_f16_host(decxb_ctx* ctx, int64_t M, int64_t N, int64_t K,
+                                  const void* hA, int64_t lda, const void* hB, int64_t ldb,
+                                  const void* hC, int64_t ldc, void* hD, int64_t ldd);
+
 /* Batched product over arrays of equally sized matrices, D[i] = A[i]*B[i] (+C[i]); matrix i of
  * an array starts stride* elements after matrix i-1.  Replaces de::cuda::GEMM3 on MatrixArray
  * (srcs/GEMM/CUDA/large_squares/GEMM3.h:45-114 and, with C, :120-200; its copy/compute

@@ -128,6 +128,28 @@ def gemm_f64(A: np.ndarray, B: np.ndarray, Cin: np.ndarray | None = None) -> np.
     return D
 
 
+def gemm_f16_half_chain(A: np.ndarray, B: np.ndarray, Cin: np.ndarray | None = None) -> np.ndarray:
+    """The reference's fp16 GEMM arithmetic: every output is one chain of HALF-precision fused
+    multiply-adds in ascending k, c = round_half(a*b + c) (__hfma2 in the macro hfma_8x1,
+    srcs/GEMM/CUDA/GEMM_kernel_def.cuh:100-107; accumulators are half2, preloaded from C in the
+    A*B+C kernel).  numpy: the product and sum are formed in float64 (exact for half inputs but for
+    astronomically rare cases) and rounded to half once per step."""
+    A = np.asarray(A, dtype=np.float16); B = np.asarray(B, dtype=np.float16)
+    M, K = A.shape
+    N = B.shape[1]
+    c = np.zeros((M, N), dtype=np.float16) if Cin is None else np.asarray(Cin, dtype=np.float16).copy()
+    A64, B64 = A.astype(np.float64), B.astype(np.float64)
+    for k in range(K):
+        c = (A64[:, k, None] * B64[None, k, :] + c.astype(np.float64)).astype(np.float16)
+    return c
+
+
+def gemm_f16_exact(A: np.ndarray, B: np.ndarray, Cin: np.ndarray | None = None) -> np.ndarray:
+    """Exact product of half inputs in float64 (yardstick for both arithmetic variants)."""
+    D = np.asarray(A, dtype=np.float16).astype(np.float64) @ np.asarray(B, dtype=np.float16).astype(np.float64)
+    return D if Cin is None else D + np.asarray(Cin, dtype=np.float16).astype(np.float64)
+
+
 def conv_geometry(W, H, depth, kW, kH, flag):
     """(out_w, out_h, eq_w, M, Kp) of the im2col convolution."""
     if flag == 1:

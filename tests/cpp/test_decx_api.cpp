@@ -153,6 +153,65 @@ static void test_gemm_random_and_errors()
     CHECK(h.error_type == decx::DECX_SUCCESS && max_err(D2, R) / K <= 1e-6);
 }
 
+/* IEEE half <-> float for the test's own data (round to nearest even; no denormal inputs here) */
+static de::Half f2h(float f)
+{
+    unsigned x; memcpy(&x, &f, 4);
+    const unsigned sign = (x >> 16) & 0x8000u;
+    int e = (int)((x >> 23) & 0xff) - 127 + 15;
+    unsigned m = x & 0x7fffffu;
+    de::Half h;
+    if (e <= 0) { h.val = (unsigned short)sign; return h; }
+    unsigned r = (m >> 13) + ((m & 0x1000u) && ((m & 0x2fffu) != 0) ? 1u : 0u);
+    unsigned v = ((unsigned)e << 10) + r;
+    h.val = (unsigned short)(sign | (v > 0x7bffu ? 0x7c00u : v));
+    return h;
+}
+static float h2f(de::Half h)
+{
+    const unsigned sign = (unsigned)(h.val & 0x8000u) << 16, e = (h.val >> 10) & 0x1f, m = h.val & 0x3ffu;
+    if (e == 0) { float f = (float)m * 5.9604644775390625e-8f; return (h.val & 0x8000u) ? -f : f; }
+    const unsigned x = sign | ((e - 15 + 127) << 23) | (m << 13);
+    float f; memcpy(&f, &x, 4); return f;
+}
+
+static void test_gemm_half()
+{
+    /* the fp16 overloads (GEMM.h:33-49): half in, half out; pitch is ceil16(width) */
+    unsigned s = 99;
+    const int M = 96, K = 80, N = 72;
+    de::Matrix<de::Half>& A = de::CreateMatrixRef<de::Half>(K, M, decx::Page_Default);
+    de::Matrix<de::Half>& B = de::CreateMatrixRef<de::Half>(N, K, decx::Page_Locked);
+    de::Matrix<de::Half>& C = de::CreateMatrixRef<de::Half>(N, M, decx::Page_Default);
+    de::Matrix<de::Half>& D = de::CreateMatrixRef<de::Half>();
+    CHECK(&A.index(1, 0) - &A.index(0, 0) == 80 && &B.index(1, 0) - &B.index(0, 0) == 80);
+    for (int i = 0; i < M; ++i) for (int k = 0; k < K; ++k) A.index(i, k) = f2h(rnd(s));
+    for (int k = 0; k < K; ++k) for (int j = 0; j < N; ++j) B.index(k, j) = f2h(rnd(s));
+    for (int i = 0; i < M; ++i) for (int j = 0; j < N; ++j) C.index(i, j) = f2h(rnd(s));
+    for (int with_c = 0; with_c <= 1; ++with_c) {
+        de::DH h = with_c ? de::cuda::GEMM(A, B, C, D) : de::cuda::GEMM(A, B, D);
+        CHECK(h.error_type == decx::DECX_SUCCESS && D.Width() == (uint)N && D.Height() == (uint)M);
+        double worst = 0;
+        for (int i = 0; i < M; ++i) for (int j = 0; j < N; ++j) {
+            double e = with_c ? (double)h2f(C.index(i, j)) : 0.0;
+            for (int k = 0; k < K; ++k) e += (double)h2f(A.index(i, k)) * (double)h2f(B.index(k, j));
+            worst = fmax(worst, fabs((double)h2f(D.index(i, j)) - e) - (fabs(e) * 4.8828125e-4 + K * 2.4e-7 + 6e-8));
+        }
+        CHECK(worst <= 0.0);
+    }
+    de::GPU_Matrix<de::Half>& dA = de::CreateGPUMatrixRef<de::Half>(K, M);
+    de::GPU_Matrix<de::Half>& dB = de::CreateGPUMatrixRef<de::Half>(N, K);
+    de::GPU_Matrix<de::Half>& dD = de::CreateGPUMatrixRef<de::Half>();
+    dA.Load_from_host(A); dB.Load_from_host(B);
+    de::DH h = de::cuda::GEMM(dA, dB, dD);
+    de::Matrix<de::Half>& D2 = de::CreateMatrixRef<de::Half>(N, M, decx::Page_Default);
+    dD.Load_to_host(D2);
+    de::cuda::GEMM(A, B, D);
+    bool same = h.error_type == decx::DECX_SUCCESS;
+    for (int i = 0; i < M; ++i) for (int j = 0; j < N; ++j) same &= D2.index(i, j).val == D.index(i, j).val;
+    CHECK(same);
+}
+
 static void test_gemm3()
 {
     /* batched product over MatrixArrays (GEMM3.h:45-114), 5 matrices, nothing aligned */
@@ -262,6 +321,7 @@ int main(int argc, char** argv)
         test_gemm_known_answer();
         test_gemm_random_and_errors();
         test_gemm3();
+        test_gemm_half();
         test_conv();
         de::release_all_tmp();
     } else return 2;

@@ -160,6 +160,32 @@ def test_gemm_batched_device_and_host(ctx):
     assert o.norm_err(dD.cpu().numpy(), R, K, 1.0, 1.0) <= TOL_3X
 
 
+@pytest.mark.parametrize("shape", [(128, 128, 64), (256, 512, 256), (100, 72, 50), (300, 129, 77), (1024, 1024, 512)])
+def test_gemm_fp16_against_half_chain_and_exact(ctx, shape):
+    """fp16 GEMM (half in, half out, fp32 accumulation on the tensor cores).  The reference
+    accumulates in half; both are compared with the exact product of the half inputs: the new
+    result must lie within half-precision rounding of it (2^-11 relative plus K * 2^-24 for the
+    fp32 accumulation), and must not be further from it than the reference's half chain is."""
+    M, N, K = shape
+    A = (o.fill_uniform(M * K, 1).reshape(M, K)).astype(np.float16)
+    B = (o.fill_uniform(K * N, 2).reshape(K, N)).astype(np.float16)
+    Cin = (o.fill_uniform(M * N, 3).reshape(M, N)).astype(np.float16)
+    for with_c in (False, True):
+        dD = torch.full((M, N), float("nan"), device=DEV, dtype=torch.float16)
+        ctx.gemm_f16(M, N, K, dev(A), K, dev(B), N, dD, N, Cin=dev(Cin) if with_c else None, ldc=N if with_c else 0)
+        ctx.synchronize()
+        D = dD.cpu().numpy().astype(np.float64)
+        E = o.gemm_f16_exact(A, B, Cin if with_c else None)
+        bound = np.abs(E) * 2.0 ** -11 + K * 2.0 ** -22 + 2.0 ** -24
+        assert np.all(np.abs(D - E) <= bound), float(np.max(np.abs(D - E) - bound))
+        if M * N * K <= 256 * 512 * 256:
+            Rh = o.gemm_f16_half_chain(A, B, Cin if with_c else None).astype(np.float64)
+            assert np.abs(D - E).max() <= np.abs(Rh - E).max() + 1e-12
+    hD = np.empty((M, N), dtype=np.float16)
+    ctx.gemm_f16_host(M, N, K, A, K, B, N, hD, N, Cin=Cin, ldc=N)
+    assert np.array_equal(hD.view(np.uint16), dD.cpu().numpy().view(np.uint16)), "host path must give the device path's bits"
+
+
 def test_gemm_argument_errors(ctx):
     t = torch.zeros(64, device=DEV)
     with pytest.raises(b.DecxbError) as e:
