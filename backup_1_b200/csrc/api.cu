@@ -286,6 +286,48 @@ extern "C" int decxb_gemm_f16_host(decxb_ctx* ctx, int64_t M, int64_t N, int64_t
 }
 
 /* ---- batched GEMM over arrays of equally sized matrices -------------------------------------- */
+/* All matrices of the batch in ONE launch: the operands are split into stacked hi/lo arrays in
+ * which every matrix occupies whole tiles, and the kernel's tile index runs over (matrix, tile). */
+static int gemm_batched_device(decxb_ctx* ctx, int mode, int tile, int64_t batch, int64_t M, int64_t N, int64_t K,
+                               const float* A, int64_t lda, int64_t strideA, const float* B, int64_t ldb, int64_t strideB,
+                               const float* C, int64_t ldc, int64_t strideC, float* D, int64_t ldd, int64_t strideD,
+                               cudaStream_t s)
+{
+    if (mode != DECXB_GEMM_3XTF32 && mode != DECXB_GEMM_1XTF32) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "gemm mode");
+    if (batch < 0 || M <= 0 || N <= 0 || K <= 0) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "gemm dims must be positive");
+    if (batch == 0) return DECXB_OK;
+    if (!A || !B || !D) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null operand");
+    if (lda < K || ldb < N || ldd < N || (C && ldc < N))
+        return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
+    if (batch == 1)
+        return gemm_device(ctx, mode, tile, M, N, K, A, lda, B, ldb, false, C, ldc, D, ldd, s);
+    const bool x3 = mode == DECXB_GEMM_3XTF32;
+    if (tile == DECXB_TILE_AUTO) tile = decxb_pick_tile(ctx, M, N, batch);
+    int tm = 128, tn = 128;
+    decxb_tile_shape(tile, &tm, &tn);
+    const int64_t Kp = decxb_ceil_to(K, 4), m_pad = decxb_ceil_to(M, tm), n_pad = decxb_ceil_to(N, tn);
+    Scratch scratch(ctx, s);
+    float *a_hi = nullptr, *a_lo = nullptr, *b_hi = nullptr, *b_lo = nullptr;
+    int rc;
+    if ((rc = scratch.get((size_t)batch * m_pad * Kp * 4, (void**)&a_hi))) return rc;
+    if ((rc = scratch.get((size_t)batch * n_pad * Kp * 4, (void**)&b_hi))) return rc;
+    if (x3) {
+        if ((rc = scratch.get((size_t)batch * m_pad * Kp * 4, (void**)&a_lo))) return rc;
+        if ((rc = scratch.get((size_t)batch * n_pad * Kp * 4, (void**)&b_lo))) return rc;
+    }
+    if ((rc = decxb_launch_split_rows(ctx, A, M, K, lda, a_hi, a_lo, Kp, m_pad, s, batch, strideA, x3 ? 0 : 1))) return rc;
+    if ((rc = decxb_launch_split_transpose(ctx, B, K, N, ldb, b_hi, b_lo, Kp, x3 ? 0 : 1, s, batch, strideB, n_pad))) return rc;
+    decxb_gemm_args g = {};
+    g.M = M; g.N = N; g.K = K;
+    g.a_hi = a_hi; g.a_lo = a_lo; g.lda = Kp;
+    g.b_hi = b_hi; g.b_lo = b_lo; g.ldb = Kp; g.b_rows = n_pad;
+    g.C = C; g.ldc = ldc; g.D = D; g.ldd = ldd; g.tile = tile;
+    g.nbatch = batch; g.m_pad = m_pad; g.n_pad = n_pad; g.d_batch_stride = strideD; g.c_batch_stride = strideC;
+    rc = decxb_launch_gemm_tn(ctx, g, s);
+    scratch.release();
+    return rc;
+}
+
 extern "C" int decxb_gemm_f32_batched(decxb_ctx* ctx, int mode, int tile, int64_t batch, int64_t M, int64_t N, int64_t K,
                                       const float* A, int64_t lda, int64_t strideA,
                                       const float* B, int64_t ldb, int64_t strideB,
@@ -294,14 +336,8 @@ extern "C" int decxb_gemm_f32_batched(decxb_ctx* ctx, int mode, int tile, int64_
 {
     int rc = decxb_bind(ctx);
     if (rc) return rc;
-    if (batch < 0) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "negative batch");
-    cudaStream_t s = pick_stream(ctx, stream);
-    for (int64_t i = 0; i < batch; ++i) {
-        rc = gemm_device(ctx, mode, tile, M, N, K, A + i * strideA, lda, B + i * strideB, ldb, false,
-                         C ? C + i * strideC : nullptr, ldc, D + i * strideD, ldd, s);
-        if (rc) return rc;
-    }
-    return DECXB_OK;
+    return gemm_batched_device(ctx, mode, tile, batch, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC,
+                               D, ldd, strideD, pick_stream(ctx, stream));
 }
 
 extern "C" int decxb_gemm_f32_batched_host(decxb_ctx* ctx, int mode, int tile, int64_t batch, int64_t M, int64_t N, int64_t K,
@@ -317,42 +353,53 @@ extern "C" int decxb_gemm_f32_batched_host(decxb_ctx* ctx, int mode, int tile, i
     if (!hA || !hB || !hD) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null operand");
     if (lda < K || ldb < N || ldd < N || (hC && ldc < N))
         return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
-    /* A ring of three device slots; matrix i is uploaded while matrix i-1 is multiplied and the
-     * result of matrix i-2 travels back (the reference pipelines the same three phases over two
-     * slots and three streams, GEMM3_macros.h:140-248). */
+    /* A ring of three device slots, each holding a GROUP of matrices (about 32 MiB of operands, so
+     * small matrices still fill the GPU: a group is one batched launch).  Group i is uploaded
+     * while group i-1 is multiplied and the results of group i-2 travel back (the reference
+     * pipelines the same three phases, one matrix at a time, GEMM3_macros.h:140-248). */
     constexpr int SLOTS = 3;
     cudaStream_t s = ctx->stream, up = ctx->copy_stream[0], down = ctx->copy_stream[1];
     Scratch scratch(ctx, s);
     ChunkEvents evs;
     const int64_t Kp = decxb_ceil_to(K, 4), Np = decxb_ceil_to(N, 4);
-    const int nslots = batch < SLOTS ? (int)batch : SLOTS;
+    const int64_t per_matrix = (M * Kp + K * Np + M * Np) * 4;
+    int64_t group = ((int64_t)32 << 20) / per_matrix;
+    if (group < 1) group = 1;
+    if (group > batch) group = batch;
+    const int64_t ngroups = decxb_ceil_div(batch, group);
+    const int nslots = ngroups < SLOTS ? (int)ngroups : SLOTS;
     float *dA[SLOTS], *dB[SLOTS], *dC[SLOTS] = {nullptr, nullptr, nullptr}, *dD[SLOTS];
     for (int k = 0; k < nslots; ++k) {
-        if ((rc = scratch.get((size_t)M * Kp * 4, (void**)&dA[k]))) return rc;
-        if ((rc = scratch.get((size_t)K * Np * 4, (void**)&dB[k]))) return rc;
-        if ((rc = scratch.get((size_t)M * Np * 4, (void**)&dD[k]))) return rc;
-        if (hC && (rc = scratch.get((size_t)M * Np * 4, (void**)&dC[k]))) return rc;
+        if ((rc = scratch.get((size_t)group * M * Kp * 4, (void**)&dA[k]))) return rc;
+        if ((rc = scratch.get((size_t)group * K * Np * 4, (void**)&dB[k]))) return rc;
+        if ((rc = scratch.get((size_t)group * M * Np * 4, (void**)&dD[k]))) return rc;
+        if (hC && (rc = scratch.get((size_t)group * M * Np * 4, (void**)&dC[k]))) return rc;
     }
     if ((rc = fence_copy_streams(ctx, evs))) return rc;
-    std::vector<cudaEvent_t> e_done(batch, nullptr), e_down(batch, nullptr);
-    for (int64_t i = 0; i < batch; ++i) {
-        const int k = (int)(i % nslots);
+    std::vector<cudaEvent_t> e_done(ngroups, nullptr), e_down(ngroups, nullptr);
+    for (int64_t gi = 0; gi < ngroups; ++gi) {
+        const int k = (int)(gi % nslots);
+        const int64_t i0 = gi * group, nb = batch - i0 < group ? batch - i0 : group;
         cudaEvent_t e_up = evs.make();
-        e_done[i] = evs.make(); e_down[i] = evs.make();
-        if (!e_up || !e_done[i] || !e_down[i]) { sync_all_streams(ctx); return decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"); }
-        if (i >= nslots) DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(up, e_done[i - nslots], 0));      /* operands of the slot consumed */
-        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dA[k], Kp * 4, hA + i * strideA, lda * 4, K * 4, M, cudaMemcpyHostToDevice, up));
-        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dB[k], Np * 4, hB + i * strideB, ldb * 4, N * 4, K, cudaMemcpyHostToDevice, up));
-        if (hC) DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dC[k], Np * 4, hC + i * strideC, ldc * 4, N * 4, M, cudaMemcpyHostToDevice, up));
+        e_done[gi] = evs.make(); e_down[gi] = evs.make();
+        if (!e_up || !e_done[gi] || !e_down[gi]) { sync_all_streams(ctx); return decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"); }
+        if (gi >= nslots) DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(up, e_done[gi - nslots], 0));      /* operands of the slot consumed */
+        for (int64_t j = 0; j < nb; ++j) {
+            DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dA[k] + j * M * Kp, Kp * 4, hA + (i0 + j) * strideA, lda * 4, K * 4, M, cudaMemcpyHostToDevice, up));
+            DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dB[k] + j * K * Np, Np * 4, hB + (i0 + j) * strideB, ldb * 4, N * 4, K, cudaMemcpyHostToDevice, up));
+            if (hC) DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dC[k] + j * M * Np, Np * 4, hC + (i0 + j) * strideC, ldc * 4, N * 4, M, cudaMemcpyHostToDevice, up));
+        }
         DECXB_CUDA_TRY(ctx, cudaEventRecord(e_up, up));
         DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(s, e_up, 0));
-        if (i >= nslots) DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(s, e_down[i - nslots], 0));       /* result slot drained */
-        rc = gemm_device(ctx, mode, tile, M, N, K, dA[k], Kp, dB[k], Np, false, dC[k], Np, dD[k], Np, s);
+        if (gi >= nslots) DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(s, e_down[gi - nslots], 0));       /* result slot drained */
+        rc = gemm_batched_device(ctx, mode, tile, nb, M, N, K, dA[k], Kp, M * Kp, dB[k], Np, K * Np,
+                                 dC[k], Np, M * Np, dD[k], Np, M * Np, s);
         if (rc) { sync_all_streams(ctx); return rc; }
-        DECXB_CUDA_TRY(ctx, cudaEventRecord(e_done[i], s));
-        DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(down, e_done[i], 0));
-        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(hD + i * strideD, ldd * 4, dD[k], Np * 4, N * 4, M, cudaMemcpyDeviceToHost, down));
-        DECXB_CUDA_TRY(ctx, cudaEventRecord(e_down[i], down));
+        DECXB_CUDA_TRY(ctx, cudaEventRecord(e_done[gi], s));
+        DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(down, e_done[gi], 0));
+        for (int64_t j = 0; j < nb; ++j)
+            DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(hD + (i0 + j) * strideD, ldd * 4, dD[k] + j * M * Np, Np * 4, N * 4, M, cudaMemcpyDeviceToHost, down));
+        DECXB_CUDA_TRY(ctx, cudaEventRecord(e_down[gi], down));
     }
     if ((rc = sync_all_streams(ctx))) return rc;
     scratch.release();

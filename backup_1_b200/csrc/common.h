@@ -99,10 +99,12 @@ static inline int64_t decxb_ceil_div(int64_t v, int64_t m) { return (v + m - 1) 
 
 /* hi = tf32(a), lo = tf32(a - hi); out pitch `ld_out` (pad columns zeroed).  lo may be NULL. */
 int decxb_launch_split_rows(decxb_ctx* ctx, const float* in, int64_t rows, int64_t cols, int64_t ld_in,
-                            float* hi, float* lo, int64_t ld_out, int64_t rows_out, cudaStream_t s);
+                            float* hi, float* lo, int64_t ld_out, int64_t rows_out, cudaStream_t s,
+                            int64_t nbatch = 1, int64_t in_batch_stride = 0, int raw = 0);
 /* Transposing variant: in[K][ld_in] (K rows, N cols) -> hi/lo[N][ld_out]; `raw` keeps hi = a unrounded. */
 int decxb_launch_split_transpose(decxb_ctx* ctx, const float* in, int64_t K, int64_t N, int64_t ld_in,
-                                 float* hi, float* lo, int64_t ld_out, int raw, cudaStream_t s);
+                                 float* hi, float* lo, int64_t ld_out, int raw, cudaStream_t s,
+                                 int64_t nbatch = 1, int64_t in_batch_stride = 0, int64_t out_batch_rows = 0);
 
 /* The tensor-core GEMM on K-contiguous operands.  a_hi/a_lo: [M][lda], b_hi/b_lo: [N][ldb]
  * (lo pointers NULL for plain TF32).  C optional addend, D output. */
@@ -115,7 +117,13 @@ struct decxb_gemm_args {
     float* D; int64_t ldd;
     int tile;
     const float* bias; int act;      /* fused epilogue (NULL / DECXB_ACT_NONE = off) */
+    /* batched: nbatch > 1 stacked matrices; A holds m_pad rows per matrix, B n_pad rows per matrix
+     * (both multiples of the tile chosen by `tile`, which must then be explicit) */
+    int64_t nbatch, m_pad, n_pad, d_batch_stride, c_batch_stride;
 };
+/* Tile shape (rows, cols) of a decxb_gemm_tile value; the AUTO choice for a batched problem. */
+void decxb_tile_shape(int tile, int* tm, int* tn);
+int decxb_pick_tile(decxb_ctx* ctx, int64_t M, int64_t N, int64_t nbatch);
 int decxb_launch_gemm_tn(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s);
 
 /* fp16 GEMM on K-contiguous operands: A [M][lda], Bt [N][ldbt] (halves), optional fp16 addend,

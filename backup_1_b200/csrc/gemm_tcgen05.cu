@@ -256,6 +256,10 @@ struct GemmParams {
     int kw, off_x, off_y;       /* filter width, source offset of tap (0,0)                      */
     int cblocks;                /* 32-channel blocks per tap                                     */
     int64_t dst_img_stride;     /* floats between destination images                             */
+    /* batched GEMM: the operand arrays stack `nbatch` matrices, each padded to whole tiles
+     * (tiles_m_per tiles of rows in A, b_batch_rows rows in B); results lie d_batch_stride apart */
+    int tiles_m_per;            /* 0 = not batched                                                */
+    int64_t b_batch_rows, d_batch_stride, c_batch_stride;
     /* fused epilogue: D = act(acc (+C) (+bias[col])) */
     const float* bias;          /* per output column (filter), or NULL                            */
     int act;                    /* DECXB_ACT_*                                                    */
@@ -385,7 +389,8 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
             for (int t = cluster_id; t < num_tiles && alive; t += num_clusters) {
                 int tm, tn; tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
                 const int row_a = tm * C::UMMA_M + (int)cta_rank * BM_CTA;
-                const int row_b = tn * C::UMMA_N + (int)cta_rank * BN;
+                int row_b = tn * C::UMMA_N + (int)cta_rank * BN;
+                if (!CONV && p.tiles_m_per) row_b += (tm / p.tiles_m_per) * (int)p.b_batch_rows;   /* matrix of the batch */
                 /* convolution: this CTA's patch of output pixels */
                 int img = 0, px0 = 0, py0 = 0;
                 if (CONV) {
@@ -474,8 +479,9 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
     } else {
         /* ------------------------------------------------------------ epilogue -------- */
         const int q = warp & 3;                   /* TMEM lane quarter this warp may read */
-        const bool d_vec = ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) && (p.ldd % 4 == 0);
-        const bool c_vec = p.C && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && (p.ldc % 4 == 0);
+        const bool d_vec = ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) && (p.ldd % 4 == 0) && (p.d_batch_stride % 4 == 0) &&
+                           (p.dst_img_stride % 4 == 0);
+        const bool c_vec = p.C && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && (p.ldc % 4 == 0) && (p.c_batch_stride % 4 == 0);
         int it = 0;
         bool alive = true;
         for (int t = cluster_id; t < num_tiles && alive; t += num_clusters, ++it) {
@@ -484,11 +490,12 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
             const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
             if (!wait_bounded(tfull_bar(acc), acc_phase, p, 400 + acc, t)) { alive = false; break; }
             tc_fence_after();
-            int64_t row = (int64_t)tm * C::UMMA_M + (int64_t)cta_rank * BM_CTA + q * 32 + lane;
+            const int bidx = (!CONV && p.tiles_m_per) ? tm / p.tiles_m_per : 0;
+            int64_t row = (int64_t)(tm - bidx * p.tiles_m_per) * C::UMMA_M + (int64_t)cta_rank * BM_CTA + q * 32 + lane;
             bool row_ok = row < p.M;
             const int64_t col0 = (int64_t)tn * C::UMMA_N;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * C::UMMA_N);
-            float* __restrict__ drow = p.D + row * p.ldd;
+            float* __restrict__ drow = p.D + bidx * p.d_batch_stride + row * p.ldd;
             if (CONV) {
                 /* tile row i is pixel (px0 + i % bx, py0 + i / bx) of image img */
                 const int per_img = p.tiles_x * p.tiles_y;
@@ -500,7 +507,7 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
                 row_ok = (x < p.eq_w) && (y < p.out_h);
                 drow = p.D + (int64_t)img * p.dst_img_stride + ((int64_t)y * p.eq_w + x) * p.ldd;
             }
-            const float* __restrict__ crow = (p.C && !CONV) ? p.C + row * p.ldc : nullptr;
+            const float* __restrict__ crow = (p.C && !CONV) ? p.C + bidx * p.c_batch_stride + row * p.ldc : nullptr;
 #pragma unroll 1
             for (int c = 0; c < C::UMMA_N; c += 32) {
                 if (col0 + c >= p.N) break;           /* warp-uniform */
@@ -752,11 +759,13 @@ int launch_cfg(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s)
     using C = Cfg<CTAS, BN, NSPLIT>;
     CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
     int rc;
-    if ((rc = make_map(ctx, &ma_hi, a.a_hi, a.M, a.K, a.lda, BM_CTA))) return rc;
-    if ((rc = make_map(ctx, &mb_hi, a.b_hi, a.b_rows, a.K, a.ldb, BN))) return rc;
+    const int64_t a_rows = a.nbatch > 1 ? a.m_pad * a.nbatch : a.M;
+    const int64_t b_rows = a.nbatch > 1 ? a.n_pad * a.nbatch : a.b_rows;
+    if ((rc = make_map(ctx, &ma_hi, a.a_hi, a_rows, a.K, a.lda, BM_CTA))) return rc;
+    if ((rc = make_map(ctx, &mb_hi, a.b_hi, b_rows, a.K, a.ldb, BN))) return rc;
     if (NSPLIT == 3) {
-        if ((rc = make_map(ctx, &ma_lo, a.a_lo, a.M, a.K, a.lda, BM_CTA))) return rc;
-        if ((rc = make_map(ctx, &mb_lo, a.b_lo, a.b_rows, a.K, a.ldb, BN))) return rc;
+        if ((rc = make_map(ctx, &ma_lo, a.a_lo, a_rows, a.K, a.lda, BM_CTA))) return rc;
+        if ((rc = make_map(ctx, &mb_lo, a.b_lo, b_rows, a.K, a.ldb, BN))) return rc;
     } else { ma_lo = ma_hi; mb_lo = mb_hi; }
 
     GemmParams p = {};
@@ -765,6 +774,14 @@ int launch_cfg(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s)
     p.bias = a.bias; p.act = a.act;
     p.tiles_m = (int)decxb_ceil_div(a.M, C::UMMA_M);
     p.tiles_n = (int)decxb_ceil_div(a.N, C::UMMA_N);
+    if (a.nbatch > 1) {
+        /* stacked operands: every matrix occupies whole tiles (a.m_pad rows of A, a.n_pad rows of B) */
+        if (a.m_pad % C::UMMA_M || a.n_pad % C::UMMA_N) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "batched operands not padded to the tile");
+        p.tiles_m_per = (int)(a.m_pad / C::UMMA_M);
+        if ((int64_t)p.tiles_m_per * a.nbatch > 0x7fffffffLL) return decxb_fail(ctx, DECXB_ERR_TOO_LARGE, "batched tiles");
+        p.tiles_m = p.tiles_m_per * (int)a.nbatch;
+        p.b_batch_rows = a.n_pad; p.d_batch_stride = a.d_batch_stride; p.c_batch_stride = a.c_batch_stride;
+    }
     p.num_kb = (int)decxb_ceil_div(a.K, BK);
     p.wait_limit_ns = ctx->wait_limit_ns;
     p.status = ctx->d_status;
@@ -807,27 +824,41 @@ int decxb_launch_gemm_f16_tn(decxb_ctx* ctx, const decxb_gemm_f16_args& a, cudaS
 
 void* decxb_tensor_map_encoder() { return reinterpret_cast<void*>(get_encode_fn()); }
 
+void decxb_tile_shape(int tile, int* tm, int* tn)
+{
+    switch (tile) {
+    case DECXB_TILE_2CTA_256x256: *tm = 256; *tn = 256; break;
+    case DECXB_TILE_1CTA_128x256: *tm = 128; *tn = 256; break;
+    case DECXB_TILE_1CTA_128x64:  *tm = 128; *tn = 64; break;
+    default: *tm = 128; *tn = 128; break;
+    }
+}
+
+/* cost = waves x accumulator area per SM x relative cost per unit of area; the relative costs
+ * were measured on B200 at M=8192 N=4096 K=2048 and at 1024^3 (bigger tiles move fewer
+ * shared-memory bytes per flop; small problems need more tiles than SMs) */
+int decxb_pick_tile(decxb_ctx* ctx, int64_t M, int64_t N, int64_t nbatch)
+{
+    struct Cand { int tile, tm, tn, sms_per_tile; double area, rel; };
+    const Cand cands[4] = {{DECXB_TILE_2CTA_256x256, 256, 256, 2, 32768, 1.00}, {DECXB_TILE_1CTA_128x256, 128, 256, 1, 32768, 1.18},
+                           {DECXB_TILE_1CTA_128x128, 128, 128, 1, 16384, 1.24}, {DECXB_TILE_1CTA_128x64, 128, 64, 1, 8192, 2.20}};
+    double best = -1; int tile = DECXB_TILE_1CTA_128x128;
+    for (const Cand& c : cands) {
+        const int64_t tiles = decxb_ceil_div(M, c.tm) * decxb_ceil_div(N, c.tn) * (nbatch > 1 ? nbatch : 1);
+        const int64_t slots = ctx->sm_count / c.sms_per_tile > 0 ? ctx->sm_count / c.sms_per_tile : 1;
+        const double cost = (double)decxb_ceil_div(tiles, slots) * c.area * c.rel;
+        if (best < 0 || cost < best * 0.999) { best = cost; tile = c.tile; }
+    }
+    return tile;
+}
+
 int decxb_launch_gemm_tn(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s)
 {
     if (a.M <= 0 || a.N <= 0 || a.K <= 0) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "gemm dims must be positive");
     if (a.M > 0x7fffffffLL || a.N > 0x7fffffffLL || a.K > 0x7fffffffLL) return decxb_fail(ctx, DECXB_ERR_TOO_LARGE, "gemm dims");
     const bool x3 = a.a_lo != nullptr;
     int tile = a.tile;
-    if (tile == DECXB_TILE_AUTO) {
-        /* cost = waves x accumulator area per SM x relative cost per unit of area; the relative
-         * costs were measured on B200 at M=8192 N=4096 K=2048 and at 1024^3 (bigger tiles move
-         * fewer shared-memory bytes per flop; small problems need more tiles than SMs) */
-        struct Cand { int tile, tm, tn, sms_per_tile; double area, rel; };
-        const Cand cands[4] = {{DECXB_TILE_2CTA_256x256, 256, 256, 2, 32768, 1.00}, {DECXB_TILE_1CTA_128x256, 128, 256, 1, 32768, 1.18},
-                               {DECXB_TILE_1CTA_128x128, 128, 128, 1, 16384, 1.24}, {DECXB_TILE_1CTA_128x64, 128, 64, 1, 8192, 2.20}};
-        double best = -1;
-        for (const Cand& c : cands) {
-            const int64_t tiles = decxb_ceil_div(a.M, c.tm) * decxb_ceil_div(a.N, c.tn);
-            const int64_t slots = ctx->sm_count / c.sms_per_tile > 0 ? ctx->sm_count / c.sms_per_tile : 1;
-            const double cost = (double)decxb_ceil_div(tiles, slots) * c.area * c.rel;
-            if (best < 0 || cost < best * 0.999) { best = cost; tile = c.tile; }
-        }
-    }
+    if (tile == DECXB_TILE_AUTO) tile = decxb_pick_tile(ctx, a.M, a.N, a.nbatch);
     switch (tile) {
     case DECXB_TILE_1CTA_128x128: return x3 ? launch_cfg<1, 128, 3>(ctx, a, s) : launch_cfg<1, 128, 1>(ctx, a, s);
     case DECXB_TILE_2CTA_256x256: return x3 ? launch_cfg<2, 128, 3>(ctx, a, s) : launch_cfg<2, 128, 1>(ctx, a, s);

@@ -79,16 +79,19 @@ __device__ __forceinline__ void split1(float a, float& hi, float& lo)
 __global__ void __launch_bounds__(256)
 decxb_split_rows_kernel(const float* __restrict__ in, int64_t rows, int64_t cols, int64_t ld_in,
                         float* __restrict__ hi, float* __restrict__ lo, int64_t ld_out, int64_t rows_out,
-                        int in_vec_ok)
+                        int in_vec_ok, int64_t nbatch, int64_t in_batch_stride, int raw)
 {
+    /* nbatch matrices: matrix b reads rows [0, rows) at in + b*in_batch_stride and writes rows
+     * [b*rows_out, (b+1)*rows_out) of the stacked output (rows beyond `rows` are zero) */
     const int64_t q_per_row = ld_out >> 2;
-    const int64_t total = rows_out * q_per_row;
+    const int64_t total = nbatch * rows_out * q_per_row;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t r = i / q_per_row, c = (i - r * q_per_row) << 2;
+        const int64_t r_all = i / q_per_row, c = (i - r_all * q_per_row) << 2;
+        const int64_t b = nbatch > 1 ? r_all / rows_out : 0, r = r_all - b * rows_out;
         float v[4] = {0.f, 0.f, 0.f, 0.f};
         if (r < rows) {
-            const float* p = in + r * ld_in + c;
+            const float* p = in + b * in_batch_stride + r * ld_in + c;
             if (in_vec_ok && c + 3 < cols) {
                 const float4 t = __ldg(reinterpret_cast<const float4*>(p));
                 v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
@@ -98,24 +101,28 @@ decxb_split_rows_kernel(const float* __restrict__ in, int64_t rows, int64_t cols
             }
         }
         float4 h, l;
-        split1(v[0], h.x, l.x); split1(v[1], h.y, l.y); split1(v[2], h.z, l.z); split1(v[3], h.w, l.w);
-        *reinterpret_cast<float4*>(hi + r * ld_out + c) = h;
-        if (lo) *reinterpret_cast<float4*>(lo + r * ld_out + c) = l;
+        if (raw) { h = make_float4(v[0], v[1], v[2], v[3]); l = h; }
+        else { split1(v[0], h.x, l.x); split1(v[1], h.y, l.y); split1(v[2], h.z, l.z); split1(v[3], h.w, l.w); }
+        *reinterpret_cast<float4*>(hi + r_all * ld_out + c) = h;
+        if (lo && !raw) *reinterpret_cast<float4*>(lo + r_all * ld_out + c) = l;
     }
 }
 
 int decxb_launch_split_rows(decxb_ctx* ctx, const float* in, int64_t rows, int64_t cols, int64_t ld_in,
-                            float* hi, float* lo, int64_t ld_out, int64_t rows_out, cudaStream_t s)
+                            float* hi, float* lo, int64_t ld_out, int64_t rows_out, cudaStream_t s,
+                            int64_t nbatch, int64_t in_batch_stride, int raw)
 {
     if (ld_out % 4 || ld_out < cols || rows_out < rows) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "split_rows pitch");
-    const int64_t total = rows_out * (ld_out / 4);
+    if (nbatch < 1) nbatch = 1;
+    const int64_t total = nbatch * rows_out * (ld_out / 4);
     if (total == 0) return DECXB_OK;
-    const int vec_ok = ((uintptr_t)in % 16 == 0) && (ld_in % 4 == 0);
+    const int vec_ok = ((uintptr_t)in % 16 == 0) && (ld_in % 4 == 0) && (in_batch_stride % 4 == 0);
     int64_t blocks = (total + 255) / 256;
     if (blocks > (int64_t)ctx->sm_count * 32) blocks = (int64_t)ctx->sm_count * 32;
     {
         decxb_launch_scope scope(ctx, s, DECXB_K_SPLIT);
-        decxb_split_rows_kernel<<<(int)blocks, 256, 0, s>>>(in, rows, cols, ld_in, hi, lo, ld_out, rows_out, vec_ok);
+        decxb_split_rows_kernel<<<(int)blocks, 256, 0, s>>>(in, rows, cols, ld_in, hi, lo, ld_out, rows_out, vec_ok,
+                                                            nbatch, in_batch_stride, raw);
     }
     DECXB_CUDA_TRY(ctx, cudaGetLastError());
     return DECXB_OK;
@@ -126,13 +133,16 @@ int decxb_launch_split_rows(decxb_ctx* ctx, const float* in, int64_t rows, int64
 __global__ void __launch_bounds__(256)
 decxb_split_transpose_kernel(const float* __restrict__ in, int64_t K, int64_t N, int64_t ld_in,
                              float* __restrict__ hi, float* __restrict__ lo, int64_t ld_out, int raw,
-                             int64_t tiles_n)
+                             int64_t tiles_n, int64_t nbatch, int64_t in_batch_stride, int64_t out_batch_rows)
 {
     __shared__ float tile[64][65];
     const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;   /* 64 x 4 */
     const int64_t tiles_k = (ld_out + 63) / 64;
     const int64_t n_tiles = tiles_k * tiles_n;
-    for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+    const float* const in0 = in; float* const hi0 = hi; float* const lo0 = lo;
+    for (int64_t tt = blockIdx.x; tt < n_tiles * nbatch; tt += gridDim.x) {
+        const int64_t bb = tt / n_tiles, t = tt - bb * n_tiles;
+        in = in0 + bb * in_batch_stride; hi = hi0 + bb * out_batch_rows * ld_out; lo = lo0 ? lo0 + bb * out_batch_rows * ld_out : nullptr;
         const int64_t k0 = (t / tiles_n) * 64, n0 = (t % tiles_n) * 64;
 #pragma unroll 4
         for (int j = ty; j < 64; j += 4) {
@@ -165,13 +175,16 @@ decxb_split_transpose_kernel(const float* __restrict__ in, int64_t K, int64_t N,
 __global__ void __launch_bounds__(256)
 decxb_split_transpose_vec_kernel(const float* __restrict__ in, int64_t K, int64_t N, int64_t ld_in,
                                  float* __restrict__ hi, float* __restrict__ lo, int64_t ld_out, int raw,
-                                 int64_t tiles_n)
+                                 int64_t tiles_n, int64_t nbatch, int64_t in_batch_stride, int64_t out_batch_rows)
 {
     __shared__ float tile[64][65];
     const int tid = threadIdx.x;
     const int64_t tiles_k = (ld_out + 63) / 64;
     const int64_t n_tiles = tiles_k * tiles_n;
-    for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+    const float* const in0 = in; float* const hi0 = hi; float* const lo0 = lo;
+    for (int64_t tt = blockIdx.x; tt < n_tiles * nbatch; tt += gridDim.x) {
+        const int64_t bb = tt / n_tiles, t = tt - bb * n_tiles;
+        in = in0 + bb * in_batch_stride; hi = hi0 + bb * out_batch_rows * ld_out; lo = lo0 ? lo0 + bb * out_batch_rows * ld_out : nullptr;
         const int64_t k0 = (t / tiles_n) * 64, n0 = (t % tiles_n) * 64;
         /* load: 64 k-rows x 16 float4 along n */
 #pragma unroll
@@ -210,22 +223,27 @@ decxb_split_transpose_vec_kernel(const float* __restrict__ in, int64_t K, int64_
 }
 
 int decxb_launch_split_transpose(decxb_ctx* ctx, const float* in, int64_t K, int64_t N, int64_t ld_in,
-                                 float* hi, float* lo, int64_t ld_out, int raw, cudaStream_t s)
+                                 float* hi, float* lo, int64_t ld_out, int raw, cudaStream_t s,
+                                 int64_t nbatch, int64_t in_batch_stride, int64_t out_batch_rows)
 {
     if (ld_out % 4 || ld_out < K) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "split_transpose pitch");
+    if (nbatch < 1) nbatch = 1;
     const int64_t tiles_n = (N + 63) / 64, tiles_k = (ld_out + 63) / 64;
-    int64_t blocks = tiles_n * tiles_k;
+    int64_t blocks = tiles_n * tiles_k * nbatch;
     if (blocks == 0) return DECXB_OK;
     if (blocks > (int64_t)ctx->sm_count * 16) blocks = (int64_t)ctx->sm_count * 16;
-    if (((uintptr_t)in % 16 == 0) && (ld_in % 4 == 0) && ((uintptr_t)hi % 16 == 0) && (raw || (uintptr_t)lo % 16 == 0)) {
+    if (((uintptr_t)in % 16 == 0) && (ld_in % 4 == 0) && (in_batch_stride % 4 == 0) && ((uintptr_t)hi % 16 == 0) &&
+        (raw || (uintptr_t)lo % 16 == 0)) {
         decxb_launch_scope scope(ctx, s, DECXB_K_SPLIT);
-        decxb_split_transpose_vec_kernel<<<(int)blocks, 256, 0, s>>>(in, K, N, ld_in, hi, lo, ld_out, raw, tiles_n);
+        decxb_split_transpose_vec_kernel<<<(int)blocks, 256, 0, s>>>(in, K, N, ld_in, hi, lo, ld_out, raw, tiles_n,
+                                                                     nbatch, in_batch_stride, out_batch_rows);
         DECXB_CUDA_TRY(ctx, cudaGetLastError());
         return DECXB_OK;
     }
     {
         decxb_launch_scope scope(ctx, s, DECXB_K_SPLIT);
-        decxb_split_transpose_kernel<<<(int)blocks, 256, 0, s>>>(in, K, N, ld_in, hi, lo, ld_out, raw, tiles_n);
+        decxb_split_transpose_kernel<<<(int)blocks, 256, 0, s>>>(in, K, N, ld_in, hi, lo, ld_out, raw, tiles_n,
+                                                                 nbatch, in_batch_stride, out_batch_rows);
     }
     DECXB_CUDA_TRY(ctx, cudaGetLastError());
     return DECXB_OK;

@@ -186,6 +186,33 @@ def test_gemm_fp16_against_half_chain_and_exact(ctx, shape):
     assert np.array_equal(hD.view(np.uint16), dD.cpu().numpy().view(np.uint16)), "host path must give the device path's bits"
 
 
+@pytest.mark.parametrize("mode", [b.GEMM_3XTF32, b.GEMM_1XTF32])
+@pytest.mark.parametrize("tile", [b.TILE_AUTO, b.TILE_2CTA_256x256, b.TILE_1CTA_128x64])
+def test_gemm_batched_single_launch_many_small(ctx, mode, tile):
+    """40 small ragged matrices in one launch (tile index runs over matrix and tile), pitched and
+    strided arrays, addend; every matrix against the oracle."""
+    nb, M, N, K = 40, 70, 90, 52
+    lda, ldb, ldd = 56, 96, 92
+    sA, sB, sD = M * lda + 8, K * ldb + 16, M * ldd + (4 if tile else 3)     # an odd stride forces scalar stores
+    A = np.zeros((nb, sA), dtype=np.float32); B = np.zeros((nb, sB), dtype=np.float32)
+    Cin = o.fill_uniform(nb * M * N, 3).reshape(nb, M, N)
+    for i in range(nb):
+        A[i, :M * lda] = o.fill_uniform_2d(M, K, lda, 1, first_index=i * 100003).reshape(-1)
+        B[i, :K * ldb] = o.fill_uniform_2d(K, N, ldb, 2, first_index=i * 100019).reshape(-1)
+    dD = torch.full((nb, sD), 7.0, device=DEV)
+    before = ctx.launches()
+    ctx.gemm_batched(nb, M, N, K, dev(A), lda, sA, dev(B), ldb, sB, dD, ldd, sD, Cin=dev(Cin), ldc=N, sC=M * N, mode=mode, tile=tile)
+    ctx.synchronize()
+    assert ctx.launches() - before == 3, "split, transposing split and ONE GEMM launch"
+    D = dD.cpu().numpy()
+    tol = TOL_3X if mode == b.GEMM_3XTF32 else TOL_1X
+    for i in range(nb):
+        Ai = A[i, :M * lda].reshape(M, lda)[:, :K]; Bi = B[i, :K * ldb].reshape(K, ldb)[:, :N]
+        Di = D[i, :M * ldd].reshape(M, ldd)
+        assert o.norm_err(Di[:, :N], o.gemm_fmaf(Ai, Bi, Cin[i]), K, 1.0, 1.0) <= tol, i
+        assert np.all(Di[:, N:] == 7.0) and np.all(D[i, M * ldd:] == 7.0)
+
+
 def test_gemm_argument_errors(ctx):
     t = torch.zeros(64, device=DEV)
     with pytest.raises(b.DecxbError) as e:
