@@ -11,6 +11,7 @@ from .lib import (  # noqa: F401
     DecxbError,
     GEMM_1XTF32,
     GEMM_3XTF32,
+    GEMM_3XTF32_STRICT,
     ACT_NONE,
     ACT_RELU,
     ACT_SIGMOID,

@@ -4,6 +4,7 @@
  */
 #include "common.h"
 
+#include <stdlib.h>
 #include <vector>
 
 namespace {
@@ -83,12 +84,27 @@ int gemm_device(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_
                 const float* C, int64_t ldc, float* D, int64_t ldd, cudaStream_t s,
                 const float* bias = nullptr, int act = DECXB_ACT_NONE)
 {
-    if (mode != DECXB_GEMM_3XTF32 && mode != DECXB_GEMM_1XTF32) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "gemm mode");
+    if (mode != DECXB_GEMM_3XTF32 && mode != DECXB_GEMM_1XTF32 && mode != DECXB_GEMM_3XTF32_STRICT)
+        return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "gemm mode");
     if (act < DECXB_ACT_NONE || act > DECXB_ACT_TANH) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "activation");
     if (M <= 0 || N <= 0 || K <= 0) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "gemm dims must be positive");
     if (!A || !B || !D) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null operand");
     if (lda < K || ldb < (b_is_nt ? K : N) || ldd < N || (C && ldc < N))
         return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
+    if (mode == DECXB_GEMM_3XTF32_STRICT) {
+        /* K in chunks of 128: D = A[:, k0:k1] * B[k0:k1, :] + (first chunk ? C : D); the epilogue's
+         * fp32 add of the previous partial result is an IEEE round-to-nearest add */
+        constexpr int64_t KC = 128;     /* measured on the all-positive 2048^3 case: 128 -> 3.3e-7, 256 -> 6.5e-7, 512 -> 1.2e-6 */
+        for (int64_t k0 = 0; k0 < K; k0 += KC) {
+            const int64_t kc = K - k0 < KC ? K - k0 : KC;
+            const bool last = k0 + kc >= K;
+            const float* Bk = b_is_nt ? B + k0 : B + k0 * ldb;
+            int rc = gemm_device(ctx, DECXB_GEMM_3XTF32, tile, M, N, kc, A + k0, lda, Bk, ldb, b_is_nt,
+                                 k0 == 0 ? C : D, k0 == 0 ? ldc : ldd, D, ldd, s, last ? bias : nullptr, last ? act : DECXB_ACT_NONE);
+            if (rc) return rc;
+        }
+        return DECXB_OK;
+    }
     Scratch scratch(ctx, s);
     const bool x3 = mode == DECXB_GEMM_3XTF32;
     PreparedB pb;
@@ -172,6 +188,24 @@ extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M
     if (!hA || !hB || !hD) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null operand");
     if (lda < K || ldb < N || ldd < N || (hC && ldc < N))
         return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
+    if (mode == DECXB_GEMM_3XTF32_STRICT) {
+        /* no pipelining over row-blocks in the chunked mode: stage, multiply, copy back */
+        cudaStream_t s0 = ctx->stream;
+        Scratch sc(ctx, s0);
+        const int64_t Kq = decxb_ceil_to(K, 4), Nq = decxb_ceil_to(N, 4);
+        float *dA, *dB, *dC = nullptr, *dD;
+        if ((rc = sc.get((size_t)M * Kq * 4, (void**)&dA)) || (rc = sc.get((size_t)K * Nq * 4, (void**)&dB)) ||
+            (rc = sc.get((size_t)M * Nq * 4, (void**)&dD)) || (hC && (rc = sc.get((size_t)M * Nq * 4, (void**)&dC)))) return rc;
+        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dA, Kq * 4, hA, lda * 4, K * 4, M, cudaMemcpyHostToDevice, s0));
+        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dB, Nq * 4, hB, ldb * 4, N * 4, K, cudaMemcpyHostToDevice, s0));
+        if (hC) DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dC, Nq * 4, hC, ldc * 4, N * 4, M, cudaMemcpyHostToDevice, s0));
+        rc = gemm_device(ctx, mode, tile, M, N, K, dA, Kq, dB, Nq, false, dC, Nq, dD, Nq, s0);
+        if (rc) { cudaStreamSynchronize(s0); return rc; }
+        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(hD, ldd * 4, dD, Nq * 4, N * 4, M, cudaMemcpyDeviceToHost, s0));
+        DECXB_CUDA_TRY(ctx, cudaStreamSynchronize(s0));
+        sc.release();
+        return decxb_check_dev_status(ctx);
+    }
     if (mode != DECXB_GEMM_3XTF32 && mode != DECXB_GEMM_1XTF32) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "gemm mode");
     /* Three streams: uploads, compute, downloads.  B goes up first and is prepared once; A
      * (and C) go up in row-blocks, each multiplied as soon as it has landed while the next one

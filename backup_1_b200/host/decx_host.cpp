@@ -17,7 +17,7 @@
 namespace decx {
 
 /* decx::cuP of the reference (srcs/core/configs/config.h:50): whether InitCuda ran. */
-struct cudaProp { bool is_init = false; decxb_ctx* ctx = nullptr; bool plain_tf32 = false; bool explicit_pack = false; };
+struct cudaProp { bool is_init = false; decxb_ctx* ctx = nullptr; bool plain_tf32 = false; bool strict = false; bool explicit_pack = false; };
 static cudaProp cuP;
 
 static inline uint ceil_to(uint v, uint m) { return (v + m - 1) / m * m; }
@@ -381,9 +381,14 @@ void release_all_tmp()
 namespace cuda {
 
 void SetGemmPlainTF32(bool on) { decx::cuP.plain_tf32 = on; }
+void SetGemmStrictAccumulation(bool on) { decx::cuP.strict = on; }
 void SetConvExplicitPack(bool on) { decx::cuP.explicit_pack = on; }
 
-static int gemm_mode() { return decx::cuP.plain_tf32 ? DECXB_GEMM_1XTF32 : DECXB_GEMM_3XTF32; }
+static int gemm_mode()
+{
+    return decx::cuP.plain_tf32 ? DECXB_GEMM_1XTF32 : decx::cuP.strict ? DECXB_GEMM_3XTF32_STRICT : DECXB_GEMM_3XTF32;
+}
+static int conv_gemm_mode() { return decx::cuP.plain_tf32 ? DECXB_GEMM_1XTF32 : DECXB_GEMM_3XTF32; }
 static int conv_algo() { return decx::cuP.explicit_pack ? DECXB_CONV_EXPLICIT : DECXB_CONV_IMPLICIT; }
 
 static DH gemm_host(Matrix<float>& A, Matrix<float>& B, Matrix<float>* C, Matrix<float>& dst)
@@ -484,7 +489,7 @@ static DH gemm3(MatrixArray<float>& A, MatrixArray<float>& B, MatrixArray<float>
         decx::MDim_Not_Matching(&handle); return handle;
     }
     _dst->re_construct(_B->width, _A->height, (uint)_A->ArrayNumber, decx::Page_Locked);
-    int rc = decxb_gemm_f32_batched_host(decx::cuP.ctx, gemm_mode(), DECXB_TILE_AUTO, (int64_t)_A->ArrayNumber,
+    int rc = decxb_gemm_f32_batched_host(decx::cuP.ctx, conv_gemm_mode(), DECXB_TILE_AUTO, (int64_t)_A->ArrayNumber,
                                          _A->height, _B->width, _A->width,
                                          _A->MatArr.get(), _A->pitch, (int64_t)_A->_plane,
                                          _B->MatArr.get(), _B->pitch, (int64_t)_B->_plane,
@@ -509,7 +514,7 @@ DH Conv2_MK_im2col(Tensor<float>& src, TensorArray<float>& kernel, Tensor<float>
     int rc = decxb_conv_geometry(_src->width, _src->height, _src->depth, _kernel->width, _kernel->height, _kernel->tensor_num, flag, &g);
     if (rc) { decx::from_status(&handle, rc); return handle; }
     _dst->re_construct((uint)g.out_w, (uint)g.out_h, _kernel->tensor_num, decx::Page_Locked);   /* conv2_mk_im2col.h:173-178 */
-    rc = decxb_conv2_im2col_f32_host(decx::cuP.ctx, gemm_mode(), conv_algo(), flag,
+    rc = decxb_conv2_im2col_f32_host(decx::cuP.ctx, conv_gemm_mode(), conv_algo(), flag,
                                      _src->Tens.get(), _src->width, _src->height, _src->depth,
                                      _kernel->TensArr.get(), _kernel->width, _kernel->height, _kernel->tensor_num,
                                      _dst->Tens.get(), 1, 0, 0);
@@ -520,7 +525,7 @@ DH Conv2_MK_im2col(Tensor<float>& src, TensorArray<float>& kernel, Tensor<float>
 static DH conv_dev(const float* src, uint W, uint H, uint depth, int64_t batch, decx::_GPU_TensorArray* k, float* dst, int flag)
 {
     DH handle;
-    int rc = decxb_conv2_im2col_f32(decx::cuP.ctx, gemm_mode(), conv_algo(), flag, src, W, H, depth,
+    int rc = decxb_conv2_im2col_f32(decx::cuP.ctx, conv_gemm_mode(), conv_algo(), flag, src, W, H, depth,
                                     k->TensArr.get(), k->width, k->height, k->tensor_num, dst, batch, 0, 0, nullptr);
     if (rc == DECXB_OK) rc = decxb_synchronize(decx::cuP.ctx);
     decx::from_status(&handle, rc);

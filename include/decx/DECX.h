@@ -204,6 +204,7 @@ DH Conv2_MK_im2col(GPU_TensorArray<float>& src, GPU_TensorArray<float>& kernel, 
  * plain TF32 instead of the default 3xTF32, explicit pack + GEMM instead of the default
  * implicit convolution. */
 void SetGemmPlainTF32(bool on);
+void SetGemmStrictAccumulation(bool on);   /* K accumulated in chunks added in IEEE fp32 (same-sign data) */
 void SetConvExplicitPack(bool on);
 }  // namespace cuda
 }  // namespace de

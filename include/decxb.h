@@ -55,7 +55,14 @@ typedef enum decxb_status {
  * chain (srcs/GEMM/CUDA/large_squares/GEMM.cuh:53-94).  Plain TF32 is opt-in. */
 typedef enum decxb_gemm_mode {
     DECXB_GEMM_3XTF32 = 0,
-    DECXB_GEMM_1XTF32 = 1
+    DECXB_GEMM_1XTF32 = 1,
+    /* 3xTF32 with the K dimension accumulated in chunks of 128: every chunk starts a fresh
+     * tensor-core accumulator and the chunk results are added in IEEE fp32 (round to nearest) on
+     * the CUDA cores.  The tensor core's accumulator rounds toward zero, which biases long sums
+     * of same-sign terms (the reference test program's all-positive matrices reach 2.9e-6 of
+     * K max|a| max|b| at K = 2048); chunking brings such inputs to 3.3e-7, at the price
+     * of re-reading and re-writing D once per chunk. */
+    DECXB_GEMM_3XTF32_STRICT = 2
 } decxb_gemm_mode;
 
 /* Tile configuration of the GEMM kernel (0 = choose from the shape). */

@@ -113,6 +113,29 @@ def test_gemm_known_answer_of_reference_test_program(ctx):
     assert abs(float(D[0, 0]) - expect) / expect <= 2e-5
 
 
+def test_gemm_strict_mode_meets_the_bar_on_same_sign_data(ctx):
+    """The chunked 3xTF32 mode on the reference test program's all-positive matrices (2048^3):
+    under 1e-6 of K max|a| max|b| where the plain tensor-core accumulation reaches 2.9e-6; and
+    on +-1 data it stays within the bar, with the addend."""
+    n = 2048
+    v = (0.1 * np.arange(n, dtype=np.float32)).astype(np.float32)
+    A = np.tile(v[None, :], (n, 1)); B = np.tile(v[:, None], (1, n))
+    expect = float(np.sum(v.astype(np.float64) ** 2))
+    scale = n * float(v.max()) ** 2
+    e_strict = abs(float(run_gemm(ctx, A, B, mode=b.GEMM_3XTF32_STRICT)[7, 9]) - expect) / scale
+    e_plain = abs(float(run_gemm(ctx, A, B)[7, 9]) - expect) / scale
+    assert e_strict <= TOL_3X < e_plain
+    M, N, K = 300, 200, 1300
+    A = o.fill_uniform(M * K, 1).reshape(M, K); B = o.fill_uniform(K * N, 2).reshape(K, N)
+    Cin = o.fill_uniform(M * N, 3).reshape(M, N)
+    R = o.gemm_fmaf(A, B, Cin)
+    assert o.norm_err(run_gemm(ctx, A, B, Cin, mode=b.GEMM_3XTF32_STRICT), R, K, 1.0, 1.0) <= TOL_3X
+    assert o.norm_err(run_gemm(ctx, A, B, Cin, mode=b.GEMM_3XTF32_STRICT, nt=True), R, K, 1.0, 1.0) <= TOL_3X
+    D = np.empty((M, N), dtype=np.float32)
+    ctx.gemm_host(M, N, K, A, K, B, N, D, N, Cin=Cin, ldc=N, mode=b.GEMM_3XTF32_STRICT)
+    assert o.norm_err(D, R, K, 1.0, 1.0) <= TOL_3X
+
+
 def test_gemm_pitched_operands(ctx):
     """Leading dimensions larger than the row length (DECX pitch = ceil8(width))."""
     M, N, K = 130, 100, 70
