@@ -67,7 +67,7 @@ class ClockSampler:
         self.proc = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(gpu_index)],
+                                          "-lms", "50", "-i", str(gpu_index)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -162,10 +162,10 @@ def run_reference(args, wl, name):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
-    ap.add_argument("--mode", default="3xtf32", choices=["3xtf32", "1xtf32"])
+    ap.add_argument("--mode", default="3xtf32", choices=["3xtf32", "1xtf32", "strict", "f16"])
     ap.add_argument("--tile", type=int, default=0)
     ap.add_argument("--algo", default="implicit", choices=["explicit", "implicit"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -202,7 +202,9 @@ def main():
     dev = torch.device(f"cuda:{local}")
     ctx = b.Context(local)
     ctx.set_pack_variant(args.pack_variant)
-    mode = b.GEMM_3XTF32 if args.mode == "3xtf32" else b.GEMM_1XTF32
+    mode = {"3xtf32": b.GEMM_3XTF32, "1xtf32": b.GEMM_1XTF32, "strict": b.GEMM_3XTF32_STRICT, "f16": b.GEMM_1XTF32}[args.mode]
+    if args.mode == "f16" and wl["kind"] != "gemm":
+        raise SystemExit("--mode f16 applies to the GEMM workloads")
     algo = b.CONV_EXPLICIT if args.algo == "explicit" else b.CONV_IMPLICIT
     ts = torch.cuda.Stream(device=dev)
     st = ts.cuda_stream
@@ -225,13 +227,24 @@ def main():
         def step():
             ctx.gemm(M_rank, N, K, dA, K, dB, N, dD, N, mode=mode, tile=args.tile, stream=st)
 
-        hA = torch.empty((M_rank, K), pin_memory=True); hB = torch.empty((K, N), pin_memory=True)
-        hD = torch.empty((M_rank, N), pin_memory=True)
+        if args.mode == "f16":          # the fp16 overloads: half operands and result, fp32 accumulation
+            dA, dB, dD = dA.half(), dB.half(), dD.half()
+            touched = ((M_rank * K + 2 * K * N) + M_rank * N) * 2
+
+            def step():  # noqa: F811
+                ctx.gemm_f16(M_rank, N, K, dA, K, dB, N, dD, N, stream=st)
+
+        hA = torch.empty((M_rank, K), pin_memory=True, dtype=dA.dtype); hB = torch.empty((K, N), pin_memory=True, dtype=dA.dtype)
+        hD = torch.empty((M_rank, N), pin_memory=True, dtype=dA.dtype)
         hA.copy_(dA); hB.copy_(dB)
-        h2d, d2h = (M_rank * K + K * N) * 4, M_rank * N * 4
+        esz = dA.element_size()
+        h2d, d2h = (M_rank * K + K * N) * esz, M_rank * N * esz
 
         def step_host():
-            ctx.gemm_host(M_rank, N, K, hA.data_ptr(), K, hB.data_ptr(), N, hD.data_ptr(), N, mode=mode, tile=args.tile)
+            if args.mode == "f16":
+                ctx.gemm_f16_host(M_rank, N, K, hA.data_ptr(), K, hB.data_ptr(), N, hD.data_ptr(), N)
+            else:
+                ctx.gemm_host(M_rank, N, K, hA.data_ptr(), K, hB.data_ptr(), N, hD.data_ptr(), N, mode=mode, tile=args.tile)
     else:
         W, H, C, kW, kH, F, batch = (wl[k] for k in ("W", "H", "C", "kW", "kH", "F", "batch"))
         if wl["scaling"] == "strong":
@@ -320,11 +333,12 @@ def main():
         launches_per_step = prof["gemm"]["launches"] / args.steps
         ach = flops_rank / launches_per_step / (avg_ms * 1e-3) / 1e12
         tf32 = peaks["bf16_tflops"] / 2.0
-        peak = tf32 / 3.0 if args.mode == "3xtf32" else tf32
+        peak = {"3xtf32": tf32 / 3.0, "strict": tf32 / 3.0, "1xtf32": tf32, "f16": peaks["bf16_tflops"]}[args.mode]
         roofline = {"bound": "tensor", "kernel": "decxb_gemm_tf32_kernel", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
                     "frac": ach / peak, "traffic": NCU_TRAFFIC_BYTES.get((args.workload, args.mode, "gemm")) if args.tile == 0 else None,
-                    "peak_basis": f"{peaks['basis']} bf16 dense burst {peaks['bf16_tflops']} TFLOP/s / 2 (TF32)"
-                                  + (" / 3 (3xTF32)" if args.mode == "3xtf32" else ""),
+                    "peak_basis": f"{peaks['basis']} bf16 dense burst {peaks['bf16_tflops']} TFLOP/s"
+                                  + {"3xtf32": " / 2 (TF32) / 3 (3xTF32)", "strict": " / 2 (TF32) / 3 (3xTF32)", "1xtf32": " / 2 (TF32)",
+                                     "f16": " (fp16 runs at the bf16 rate)"}[args.mode],
                     "avg_launch_ms": avg_ms, "time_shares": shares}
     else:
         # HBM-bound kernel: algorithmic bytes = what it must read plus what it must write
@@ -410,8 +424,8 @@ def main():
         line = {
             "metric": "fp32_gemm_conv_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
-            "scaling": wl["scaling"], "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core split, fp32 accumulate)"
-            if args.mode == "3xtf32" else "tf32", "data": "synthetic (seeded uniform [-1,1), generated on device)",
+            "scaling": wl["scaling"], "vs_baseline": None, "dtype": {"3xtf32": "f32 (3xTF32 tensor-core split, fp32 accumulate)", "strict": "f32 (3xTF32, K chunks added in IEEE fp32)",
+                      "1xtf32": "tf32", "f16": "f16 (fp32 accumulate)"}[args.mode], "data": "synthetic (seeded uniform [-1,1), generated on device)",
             "config": {"workload": args.workload, "desc": wl["desc"], "mode": args.mode, "tile": args.tile,
                        "algo": args.algo if wl["kind"] == "conv" else None,
                        "l2": (f"each step touches {touched / 1e6:.0f} MB (operands, split/column scratch, result) "

@@ -91,3 +91,27 @@ def test_reference_cpu_gemm_runs_and_matches(tmp_path):
     A = o.fill_uniform(256 * 192, 1).reshape(256, 192)
     B = o.fill_uniform(192 * 128, 2).reshape(192, 128)
     assert np.array_equal(np.fromfile(f, dtype=np.float32).reshape(256, 128), o.gemm_fmaf(A, B))
+
+
+def test_activation_restatement_known_values():
+    """ReLU / sigmoid / tanh as the reference's operators define them (nn/operators/ReLU.h:48-75,
+    sigmoid.h:45-46, tanh.h:41-42), bias added first."""
+    x = np.array([[-2.0, -0.0, 0.0, 0.5, 3.0]], dtype=np.float32)
+    assert np.array_equal(o.bias_activation(x, None, 1), np.array([[0, 0, 0, 0.5, 3.0]], dtype=np.float32))
+    s = o.bias_activation(x, None, 2)
+    assert np.allclose(s, 1.0 / (1.0 + np.exp(-x.astype(np.float64))), atol=1e-7) and s[0, 2] == 0.5
+    t = o.bias_activation(x, None, 3)
+    assert np.allclose(t, np.tanh(x.astype(np.float64)), atol=2e-7) and t[0, 2] == 0.0
+    b = np.array([1, 1, 1, 1, -5], dtype=np.float32)
+    assert np.array_equal(o.bias_activation(x, b, 1), np.array([[0, 1, 1, 1.5, 0]], dtype=np.float32))
+
+
+def test_half_chain_restatement():
+    """The reference's fp16 GEMM accumulates in half: integer-valued inputs small enough to stay
+    exact must reproduce the exact product; random inputs must show half-precision error."""
+    A = np.arange(12, dtype=np.float16).reshape(3, 4) - 5
+    B = (np.arange(20, dtype=np.float16).reshape(4, 5) % 7) - 3
+    assert np.array_equal(o.gemm_f16_half_chain(A, B).astype(np.float64), o.gemm_f16_exact(A, B))
+    A = o.fill_uniform(32 * 256, 1).reshape(32, 256); B = o.fill_uniform(256 * 16, 2).reshape(256, 16)
+    err = np.abs(o.gemm_f16_half_chain(A, B).astype(np.float64) - o.gemm_f16_exact(A, B)).max()
+    assert 1e-4 < err < 0.2
