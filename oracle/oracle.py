@@ -326,10 +326,9 @@ def ref_cpu_gemm(M: int, N: int, K: int, A="seed:1", B="seed:2", reps: int = 3, 
                                   if a * b < tx * ty and M % a == 0 and (M // a) % 32 == 0 and (N // 16) // b >= 1]
     err = ""
     for tx, ty in attempts:
-        cpus = sorted(os.sched_getaffinity(0))[: max(tx * ty, 1)]
         cmd = [str(HERE / "_ref" / "decx_ref_cpu"), "gemm", str(M), str(N), str(K), f"{tx}x{ty}", str(reps), A, B, out]
-        r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout,
-                           preexec_fn=lambda: os.sched_setaffinity(0, cpus))
+        env = dict(os.environ, DECX_REF_CPUS=str(max(tx * ty, 1)))
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
         if r.returncode == 0:
             break
         err = f"decx_ref_cpu failed rc={r.returncode}: {r.stderr.strip()}"

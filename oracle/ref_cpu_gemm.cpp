@@ -38,6 +38,30 @@
 #include <algorithm>
 #include <string>
 
+/* The reference's global pool is built during static initialisation with one worker per CPU
+ * of the affinity mask, into arrays of 16.  This object is defined before the reference
+ * headers are included, so it is constructed first: it narrows the mask to at most 16 CPUs
+ * (or DECX_REF_CPUS of them), whatever launched the program. */
+#include <sched.h>
+#include <unistd.h>
+static int g_pool_cpus = 0;
+struct AffinityGuard {
+    AffinityGuard()
+    {
+        cpu_set_t have, want;
+        CPU_ZERO(&want);
+        if (sched_getaffinity(0, sizeof have, &have) != 0) return;
+        int limit = 16;
+        if (const char* e = getenv("DECX_REF_CPUS")) { int v = atoi(e); if (v >= 1 && v <= 16) limit = v; }
+        int n = 0;
+        for (int c = 0; c < CPU_SETSIZE && n < limit; ++c)
+            if (CPU_ISSET(c, &have)) { CPU_SET(c, &want); ++n; }
+        if (n > 0) sched_setaffinity(0, sizeof want, &want);
+        g_pool_cpus = n;
+    }
+};
+static AffinityGuard g_affinity_guard;
+
 struct decx_shim_m256 {
     union { __m256 v; float m256_f32[8]; };
     decx_shim_m256() {}
@@ -97,6 +121,12 @@ int main(int argc, char** argv)
     if (sscanf(argv[5], "%dx%d", &tx, &ty) != 2) return 2;
     const int reps = atoi(argv[6]);
     caller_t fn = pick(tx, ty);
+    /* more tasks than workers makes the reference's queue picker index queues that were never
+     * constructed (thread_pool.h:72-99 returns a queue LENGTH as an index) */
+    if (g_pool_cpus > 0 && tx * ty > g_pool_cpus) {
+        fprintf(stderr, "thread split %dx%d needs %d CPUs, %d available\n", tx, ty, tx * ty, g_pool_cpus);
+        return 7;
+    }
     /* Preconditions of the reference entry (sgemm_callers.h:231,307,1120,1231-1248;
      * aligned loads sgemm_calc_kernel.h:207-211): */
     if (!fn || K % 8 || N % 8 || K < 64 || (M / tx) % 32 || (M % tx) || (N / 16) / ty < 1) {
