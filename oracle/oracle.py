@@ -318,10 +318,11 @@ def ref_cpu_gemm(M: int, N: int, K: int, A="seed:1", B="seed:2", reps: int = 3, 
     """Run the reference's CPU GEMM in a child process limited to <=16 CPUs.
     A/B are 'seed:<n>' or file names of raw float32 data."""
     tx, ty = split or ref_cpu_threads(M, N)
-    # The reference's thread pool has start-up races of its own (its mutexes are never taken,
-    # srcs/core/memory_management/MemoryPool_D.h:24; workers start while queues are still being
-    # constructed, thread_pool.h:126-137) and occasionally aborts inside glibc.  Such a run is
-    # repeated, then retried with fewer workers.
+    # The reference's pool starts hardware_concurrency() workers into arrays of 16 slots
+    # (thread_pool.h:18, :144-150, :246) and aborted inside glibc on hosts with more than 16 CPUs
+    # online; the driver program now caps the count it reports (see ref_cpu_gemm.cpp).  The
+    # repeat-then-degrade loop below stays as a guard: the pool also starts its workers while
+    # the queues are still being constructed (thread_pool.h:126-137).
     attempts = [(tx, ty)] * 3 + [(a, b) for a, b in ((4, 2), (2, 2), (1, 1))
                                   if a * b < tx * ty and M % a == 0 and (M // a) % 32 == 0 and (N // 16) // b >= 1]
     err = ""

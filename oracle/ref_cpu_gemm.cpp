@@ -19,7 +19,7 @@
  *
  * The reference's global thread pool starts hardware_concurrency() workers
  * at static-initialisation time into arrays of 16 slots (thread_pool.h:18,
- * 141-150, 246): run this program with at most 16 CPUs in its affinity mask.
+ * 141-150, 246); this program caps that count itself (see get_nprocs below).
  *
  * Usage: decx_ref_cpu gemm M N K TXxTY reps A B Cout
  *   A, B: "seed:<n>" (seeded uniform [-1,1), same generator as the oracle) or a
@@ -38,25 +38,42 @@
 #include <algorithm>
 #include <string>
 
-/* The reference's global pool is built during static initialisation with one worker per CPU
- * of the affinity mask, into arrays of 16.  This object is defined before the reference
- * headers are included, so it is constructed first: it narrows the mask to at most 16 CPUs
- * (or DECX_REF_CPUS of them), whatever launched the program. */
+/* The reference's global pool is built during static initialisation with
+ * std::thread::hardware_concurrency() workers placed into arrays of 16 slots
+ * (thread_pool.h:18, :144-150, :246).  With glibc >= 2.35 that count is the number of CPUs the
+ * machine has online, not the size of the affinity mask, so on a host with more than 16 CPUs
+ * the pool overruns its arrays whatever `taskset` says (seen as an abort inside
+ * pthread_mutex_lock on 24-CPU hosts).  Two measures, both taken before the pool exists:
+ *   - get_nprocs(), which the C++ runtime asks for that count, is defined here and answers
+ *     with the CPUs this process may use, at most 16 (or DECX_REF_CPUS);
+ *   - the affinity mask is narrowed to the same CPUs, so the workers do not migrate.
+ * The guard object is defined before the reference headers are included, so it is constructed
+ * first. */
 #include <sched.h>
 #include <unistd.h>
 static int g_pool_cpus = 0;
+static int usable_cpus(cpu_set_t* want)
+{
+    cpu_set_t have;
+    if (want) CPU_ZERO(want);
+    if (sched_getaffinity(0, sizeof have, &have) != 0) return 1;
+    int limit = 16;
+    if (const char* e = getenv("DECX_REF_CPUS")) { int v = atoi(e); if (v >= 1 && v <= 16) limit = v; }
+    int n = 0;
+    for (int c = 0; c < CPU_SETSIZE && n < limit; ++c)
+        if (CPU_ISSET(c, &have)) { if (want) CPU_SET(c, want); ++n; }
+    return n > 0 ? n : 1;
+}
+extern "C" int get_nprocs(void)
+{
+    return g_pool_cpus > 0 ? g_pool_cpus : usable_cpus(nullptr);
+}
 struct AffinityGuard {
     AffinityGuard()
     {
-        cpu_set_t have, want;
-        CPU_ZERO(&want);
-        if (sched_getaffinity(0, sizeof have, &have) != 0) return;
-        int limit = 16;
-        if (const char* e = getenv("DECX_REF_CPUS")) { int v = atoi(e); if (v >= 1 && v <= 16) limit = v; }
-        int n = 0;
-        for (int c = 0; c < CPU_SETSIZE && n < limit; ++c)
-            if (CPU_ISSET(c, &have)) { CPU_SET(c, &want); ++n; }
-        if (n > 0) sched_setaffinity(0, sizeof want, &want);
+        cpu_set_t want;
+        int n = usable_cpus(&want);
+        if (CPU_COUNT(&want) > 0) sched_setaffinity(0, sizeof want, &want);
         g_pool_cpus = n;
     }
 };
