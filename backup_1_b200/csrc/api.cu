@@ -59,10 +59,11 @@ int prepare_b(decxb_ctx* ctx, Scratch& scratch, bool x3, int64_t N, int64_t K,
 int gemm_prepared(decxb_ctx* ctx, Scratch& scratch, bool x3, int tile, int64_t M, int64_t N, int64_t K,
                   const float* A, int64_t lda, const PreparedB& pb,
                   const float* C, int64_t ldc, float* D, int64_t ldd, cudaStream_t s,
-                  const float* bias = nullptr, int act = DECXB_ACT_NONE)
+                  const float* bias = nullptr, int act = DECXB_ACT_NONE, bool chunked = false)
 {
     const int64_t Kp = decxb_ceil_to(K, 4);
     decxb_gemm_args g = {};
+    g.chunked = chunked ? 1 : 0;
     g.M = M; g.N = N; g.K = K; g.C = C; g.ldc = ldc; g.D = D; g.ldd = ldd; g.tile = tile; g.b_rows = N;
     g.b_hi = pb.hi; g.b_lo = pb.lo; g.ldb = pb.ld;
     g.bias = bias; g.act = act;
@@ -91,25 +92,13 @@ int gemm_device(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_
     if (!A || !B || !D) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null operand");
     if (lda < K || ldb < (b_is_nt ? K : N) || ldd < N || (C && ldc < N))
         return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
-    if (mode == DECXB_GEMM_3XTF32_STRICT) {
-        /* K in chunks of 128: D = A[:, k0:k1] * B[k0:k1, :] + (first chunk ? C : D); the epilogue's
-         * fp32 add of the previous partial result is an IEEE round-to-nearest add */
-        constexpr int64_t KC = 128;     /* measured on the all-positive 2048^3 case: 128 -> 3.3e-7, 256 -> 6.5e-7, 512 -> 1.2e-6 */
-        for (int64_t k0 = 0; k0 < K; k0 += KC) {
-            const int64_t kc = K - k0 < KC ? K - k0 : KC;
-            const bool last = k0 + kc >= K;
-            const float* Bk = b_is_nt ? B + k0 : B + k0 * ldb;
-            int rc = gemm_device(ctx, DECXB_GEMM_3XTF32, tile, M, N, kc, A + k0, lda, Bk, ldb, b_is_nt,
-                                 k0 == 0 ? C : D, k0 == 0 ? ldc : ldd, D, ldd, s, last ? bias : nullptr, last ? act : DECXB_ACT_NONE);
-            if (rc) return rc;
-        }
-        return DECXB_OK;
-    }
     Scratch scratch(ctx, s);
-    const bool x3 = mode == DECXB_GEMM_3XTF32;
+    /* the strict mode is the 3xTF32 product with K accumulated in chunks (see gemm_tcgen05.cu) */
+    const bool strict = mode == DECXB_GEMM_3XTF32_STRICT;
+    const bool x3 = mode == DECXB_GEMM_3XTF32 || strict;
     PreparedB pb;
     int rc = prepare_b(ctx, scratch, x3, N, K, B, ldb, b_is_nt, s, &pb);
-    if (rc == DECXB_OK) rc = gemm_prepared(ctx, scratch, x3, tile, M, N, K, A, lda, pb, C, ldc, D, ldd, s, bias, act);
+    if (rc == DECXB_OK) rc = gemm_prepared(ctx, scratch, x3, tile, M, N, K, A, lda, pb, C, ldc, D, ldd, s, bias, act, strict);
     scratch.release();
     return rc;
 }
@@ -188,25 +177,8 @@ extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M
     if (!hA || !hB || !hD) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null operand");
     if (lda < K || ldb < N || ldd < N || (hC && ldc < N))
         return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
-    if (mode == DECXB_GEMM_3XTF32_STRICT) {
-        /* no pipelining over row-blocks in the chunked mode: stage, multiply, copy back */
-        cudaStream_t s0 = ctx->stream;
-        Scratch sc(ctx, s0);
-        const int64_t Kq = decxb_ceil_to(K, 4), Nq = decxb_ceil_to(N, 4);
-        float *dA, *dB, *dC = nullptr, *dD;
-        if ((rc = sc.get((size_t)M * Kq * 4, (void**)&dA)) || (rc = sc.get((size_t)K * Nq * 4, (void**)&dB)) ||
-            (rc = sc.get((size_t)M * Nq * 4, (void**)&dD)) || (hC && (rc = sc.get((size_t)M * Nq * 4, (void**)&dC)))) return rc;
-        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dA, Kq * 4, hA, lda * 4, K * 4, M, cudaMemcpyHostToDevice, s0));
-        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dB, Nq * 4, hB, ldb * 4, N * 4, K, cudaMemcpyHostToDevice, s0));
-        if (hC) DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dC, Nq * 4, hC, ldc * 4, N * 4, M, cudaMemcpyHostToDevice, s0));
-        rc = gemm_device(ctx, mode, tile, M, N, K, dA, Kq, dB, Nq, false, dC, Nq, dD, Nq, s0);
-        if (rc) { cudaStreamSynchronize(s0); return rc; }
-        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(hD, ldd * 4, dD, Nq * 4, N * 4, M, cudaMemcpyDeviceToHost, s0));
-        DECXB_CUDA_TRY(ctx, cudaStreamSynchronize(s0));
-        sc.release();
-        return decxb_check_dev_status(ctx);
-    }
-    if (mode != DECXB_GEMM_3XTF32 && mode != DECXB_GEMM_1XTF32) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "gemm mode");
+    if (mode != DECXB_GEMM_3XTF32 && mode != DECXB_GEMM_1XTF32 && mode != DECXB_GEMM_3XTF32_STRICT)
+        return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "gemm mode");
     /* Three streams: uploads, compute, downloads.  B goes up first and is prepared once; A
      * (and C) go up in row-blocks, each multiplied as soon as it has landed while the next one
      * is in flight and the previous result block is on its way back.  (The reference does the
@@ -214,7 +186,8 @@ extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M
     cudaStream_t s = ctx->stream, up = ctx->copy_stream[0], down = ctx->copy_stream[1];
     Scratch scratch(ctx, s);
     ChunkEvents evs;
-    const bool x3 = mode == DECXB_GEMM_3XTF32;
+    const bool strict = mode == DECXB_GEMM_3XTF32_STRICT;
+    const bool x3 = mode == DECXB_GEMM_3XTF32 || strict;
     const int64_t Kp = decxb_ceil_to(K, 4), Np = decxb_ceil_to(N, 4);
     float *dA, *dB, *dC = nullptr, *dD;
     if ((rc = scratch.get((size_t)M * Kp * 4, (void**)&dA))) return rc;
@@ -242,7 +215,7 @@ extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M
         DECXB_CUDA_TRY(ctx, cudaEventRecord(e_up, up));
         DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(s, e_up, 0));
         rc = gemm_prepared(ctx, scratch, x3, tile, nr, N, K, dA + r0 * Kp, Kp, pb, dC ? dC + r0 * Np : nullptr, Np,
-                           dD + r0 * Np, Np, s);
+                           dD + r0 * Np, Np, s, nullptr, DECXB_ACT_NONE, strict);
         if (rc) { sync_all_streams(ctx); return rc; }
         DECXB_CUDA_TRY(ctx, cudaEventRecord(e_done, s));
         DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(down, e_done, 0));
@@ -327,7 +300,8 @@ static int gemm_batched_device(decxb_ctx* ctx, int mode, int tile, int64_t batch
                                const float* C, int64_t ldc, int64_t strideC, float* D, int64_t ldd, int64_t strideD,
                                cudaStream_t s)
 {
-    if (mode != DECXB_GEMM_3XTF32 && mode != DECXB_GEMM_1XTF32) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "gemm mode");
+    if (mode != DECXB_GEMM_3XTF32 && mode != DECXB_GEMM_1XTF32 && mode != DECXB_GEMM_3XTF32_STRICT)
+        return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "gemm mode");
     if (batch < 0 || M <= 0 || N <= 0 || K <= 0) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "gemm dims must be positive");
     if (batch == 0) return DECXB_OK;
     if (!A || !B || !D) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null operand");
@@ -335,7 +309,8 @@ static int gemm_batched_device(decxb_ctx* ctx, int mode, int tile, int64_t batch
         return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
     if (batch == 1)
         return gemm_device(ctx, mode, tile, M, N, K, A, lda, B, ldb, false, C, ldc, D, ldd, s);
-    const bool x3 = mode == DECXB_GEMM_3XTF32;
+    const bool strict = mode == DECXB_GEMM_3XTF32_STRICT;
+    const bool x3 = mode == DECXB_GEMM_3XTF32 || strict;
     if (tile == DECXB_TILE_AUTO) tile = decxb_pick_tile(ctx, M, N, batch);
     int tm = 128, tn = 128;
     decxb_tile_shape(tile, &tm, &tn);
@@ -357,6 +332,7 @@ static int gemm_batched_device(decxb_ctx* ctx, int mode, int tile, int64_t batch
     g.b_hi = b_hi; g.b_lo = b_lo; g.ldb = Kp; g.b_rows = n_pad;
     g.C = C; g.ldc = ldc; g.D = D; g.ldd = ldd; g.tile = tile;
     g.nbatch = batch; g.m_pad = m_pad; g.n_pad = n_pad; g.d_batch_stride = strideD; g.c_batch_stride = strideC;
+    g.chunked = strict ? 1 : 0;
     rc = decxb_launch_gemm_tn(ctx, g, s);
     scratch.release();
     return rc;
@@ -477,7 +453,8 @@ int conv_device(decxb_ctx* ctx, int mode, int algo, int flag,
                 float* dst, int64_t batch, int64_t src_stride, int64_t dst_stride, cudaStream_t s,
                 const float* bias = nullptr, int act = DECXB_ACT_NONE)
 {
-    if (mode != DECXB_GEMM_3XTF32 && mode != DECXB_GEMM_1XTF32) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "gemm mode");
+    if (mode != DECXB_GEMM_3XTF32 && mode != DECXB_GEMM_1XTF32 && mode != DECXB_GEMM_3XTF32_STRICT)
+        return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "gemm mode");
     if (act < DECXB_ACT_NONE || act > DECXB_ACT_TANH) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "activation");
     if (algo != DECXB_CONV_EXPLICIT && algo != DECXB_CONV_IMPLICIT) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "conv algo");
     if (!src || !filters || !dst) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null tensor");
@@ -488,7 +465,8 @@ int conv_device(decxb_ctx* ctx, int mode, int algo, int flag,
     const int64_t dp = decxb_ceil_to(depth, 4), wp = decxb_ceil_to(W, 4);
     if (src_stride == 0) src_stride = H * wp * dp;
     if (dst_stride == 0) dst_stride = g.M * g.Np;
-    const bool x3 = mode == DECXB_GEMM_3XTF32;
+    const bool strict = mode == DECXB_GEMM_3XTF32_STRICT;
+    const bool x3 = mode == DECXB_GEMM_3XTF32 || strict;
     Scratch scratch(ctx, s);
     if (algo == DECXB_CONV_IMPLICIT) {
         /* The column matrix is never written: the GEMM's A tiles are TMA boxes of the (split)
@@ -523,6 +501,7 @@ int conv_device(decxb_ctx* ctx, int mode, int algo, int flag,
         a.out_h = g.out_h; a.eq_w = g.eq_w; a.Np = g.Np;
         a.dst = dst; a.dst_img_stride = dst_stride;
         a.bias = bias; a.act = act;
+        a.chunked = strict ? 1 : 0;
         rc = decxb_launch_conv_implicit(ctx, a, s);
         scratch.release();
         return rc;
@@ -578,6 +557,7 @@ int conv_device(decxb_ctx* ctx, int mode, int algo, int flag,
             a.D = dst + (b0 + j) * dst_stride; a.ldd = g.Np;
             a.tile = DECXB_TILE_AUTO;
             a.bias = bias; a.act = act;
+            a.chunked = strict ? 1 : 0;
             if ((rc = decxb_launch_gemm_tn(ctx, a, s))) return rc;
         }
     }

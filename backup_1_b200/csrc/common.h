@@ -117,6 +117,7 @@ struct decxb_gemm_args {
     float* D; int64_t ldd;
     int tile;
     const float* bias; int act;      /* fused epilogue (NULL / DECXB_ACT_NONE = off) */
+    int chunked;                     /* 1 = accumulate K in chunks of 128 added in IEEE fp32 (3xTF32 only) */
     /* batched: nbatch > 1 stacked matrices; A holds m_pad rows per matrix, B n_pad rows per matrix
      * (both multiples of the tile chosen by `tile`, which must then be explicit) */
     int64_t nbatch, m_pad, n_pad, d_batch_stride, c_batch_stride;
@@ -152,6 +153,7 @@ struct decxb_conv_gemm_args {
     int64_t out_h, eq_w, Np;
     float* dst; int64_t dst_img_stride;
     const float* bias; int act;
+    int chunked;                      /* as decxb_gemm_args::chunked */
 };
 int decxb_launch_conv_implicit(decxb_ctx* ctx, const decxb_conv_gemm_args& a, cudaStream_t s);
 

@@ -34,7 +34,13 @@ namespace {
 constexpr int BM_CTA = 128;        /* rows of A (and of the accumulator) per CTA          */
 constexpr int BK = 32;             /* floats per k-block = one 128-byte swizzle row        */
 constexpr int UMMA_K = 8;          /* k per tcgen05.mma kind::tf32                          */
-constexpr int NUM_THREADS = 192;   /* 6 warps                                                */
+constexpr int NUM_THREADS = 192;   /* 6 warps: producer, MMA issuer, 4 epilogue warps        */
+constexpr int NUM_THREADS_CHUNKED = 384;   /* chunked accumulation: warp group 0 = producer, MMA issuer
+                                              and two idle warps; warp groups 1, 2 = 8 epilogue warps */
+constexpr int KCHUNK = 4;          /* k-blocks per chunk of the chunked accumulation: 128 values of K.
+                                      Largest error seen on the all-positive 2048^3 case, relative to
+                                      K max|a| max|b|: 64 -> 1.9e-7, 128 -> 3.3e-7, 256 -> 6.5e-7,
+                                      512 -> 1.2e-6, whole K -> 2.9e-6 */
 constexpr int SMEM_LIMIT = 232448; /* 227 KiB opt-in maximum per CTA                        */
 
 /* ---------------------------------------------------------------- PTX wrappers ------ */
@@ -299,6 +305,41 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, cons
     return true;
 }
 
+/* Writes 32 consecutive result columns of one row, first column `col_first`:
+ * (+C) (+bias[col]) activation, with 128-bit stores when `vec` says the rows allow them. */
+__device__ __forceinline__ void store32_f32(const float* v, int64_t col_first, const GemmParams& p,
+                                            float* __restrict__ drow, const float* __restrict__ crow, bool vec)
+{
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+        const int64_t col = col_first + j;
+        if (col + 3 < p.N && vec) {
+            float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            if (crow) {
+                const float4 ci = __ldg(reinterpret_cast<const float4*>(crow + col));
+                o.x += ci.x; o.y += ci.y; o.z += ci.z; o.w += ci.w;
+            }
+            if (p.bias) {
+                o.x += __ldg(p.bias + col); o.y += __ldg(p.bias + col + 1);
+                o.z += __ldg(p.bias + col + 2); o.w += __ldg(p.bias + col + 3);
+            }
+            if (p.act) {
+                o.x = apply_act(o.x, p.act); o.y = apply_act(o.y, p.act);
+                o.z = apply_act(o.z, p.act); o.w = apply_act(o.w, p.act);
+            }
+            *reinterpret_cast<float4*>(drow + col) = o;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (col + e < p.N) {
+                    float x = v[j + e] + (crow ? __ldg(crow + col + e) : 0.0f);
+                    if (p.bias) x += __ldg(p.bias + col + e);
+                    drow[col + e] = p.act ? apply_act(x, p.act) : x;
+                }
+        }
+    }
+}
+
 /* Tile order: groups of 8 tile-rows, column by column inside a group, so that the CTAs
  * running at the same time share A row-panels and B column-panels in L2. */
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn)
@@ -319,6 +360,12 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
  * NSPLIT : 3 = 3xTF32 (hi and lo parts of both operands), 1 = plain TF32,
  *          16 = fp16 operands and fp16 result with fp32 accumulation (kind::f16); a k-block is
  *          then 64 halves, still one 128-byte row, and a k-step 16 halves, still 32 bytes
+ * KCH    : 0 = the tensor core accumulates over all of K.  > 0 = chunked accumulation: the
+ *          tensor core accumulates KCH k-blocks (KCH * 32 values of K) at a time into one of the
+ *          two TMEM buffers, and eight epilogue warps add each finished chunk to a running sum
+ *          held in registers with IEEE round-to-nearest fp32 adds, while the tensor core works
+ *          on the next chunk in the other buffer.  (The tensor core's own accumulator rounds
+ *          toward zero, which biases long sums of same-sign products; short chunks bound it.)
  * ------------------------------------------------------------------------------------ */
 template <int CTAS, int BN, int NSPLIT>
 struct Cfg {
@@ -339,8 +386,8 @@ struct Cfg {
     static_assert(TMEM_COLS_RAW <= 512, "two accumulators must fit in TMEM");
 };
 
-template <int CTAS, int BN, int NSPLIT, bool CONV>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+template <int CTAS, int BN, int NSPLIT, bool CONV, int KCH>
+__global__ void __launch_bounds__(KCH ? NUM_THREADS_CHUNKED : NUM_THREADS, 1)
 decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                        const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
                        const GemmParams p)
@@ -367,7 +414,7 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4 * CTAS); }
+        for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), (KCH ? 8 : 4) * CTAS); }
         fence_barrier_init();
     }
     if (warp == 1) {
@@ -381,6 +428,14 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
+    /* Chunked accumulation with 128 running sums per thread: the epilogue warp groups take
+     * registers that warp group 0 gives up (168 per thread at launch for 384 threads;
+     * 128 * 56 + 256 * 224 = 64512 = 384 * 168).  The host refuses to launch the variant if the
+     * kernel was not compiled to 168 registers, so the request can always be met. */
+    constexpr bool REALLOC = KCH > 0 && C::UMMA_N / 2 > 64;
+
+    if (KCH ? warp < 4 : warp < 2) {
+    if constexpr (REALLOC) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (warp == 0) {
         /* ------------------------------------------------------------ TMA producer ---- */
         if (lane == 0) {
@@ -440,61 +495,64 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
         if (is_leader && lane == 0) {
             constexpr uint32_t idesc = NSPLIT == 16 ? make_idesc_f16(C::UMMA_M, C::UMMA_N) : make_idesc(C::UMMA_M, C::UMMA_N);
             int stage = 0; uint32_t phase = 0;
-            int it = 0;
+            int unit = 0;              /* accumulation units so far: tiles, or (tile, chunk) pairs */
             bool alive = true;
-            for (int t = cluster_id; t < num_tiles && alive; t += num_clusters, ++it) {
-                const int acc = it & 1;
-                const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-                if (!wait_bounded(tempty_bar(acc), acc_phase ^ 1u, p, 200 + acc, t)) { alive = false; break; }
-                tc_fence_after();
-                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * C::UMMA_N);
-                for (int kb = 0; kb < p.num_kb; ++kb) {
-                    if (!wait_bounded(full_bar(stage), phase, p, 300 + stage, t)) { alive = false; break; }
+            const int per_unit = KCH ? KCH : p.num_kb;
+            for (int t = cluster_id; t < num_tiles && alive; t += num_clusters) {
+                for (int kb0 = 0; kb0 < p.num_kb && alive; kb0 += per_unit, ++unit) {
+                    const int acc = unit & 1;
+                    const uint32_t acc_phase = (uint32_t)(unit >> 1) & 1u;
+                    if (!wait_bounded(tempty_bar(acc), acc_phase ^ 1u, p, 200 + acc, t)) { alive = false; break; }
                     tc_fence_after();
-                    const uint64_t da_hi = make_smem_desc(stage_a(stage, 0));
-                    const uint64_t db_hi = make_smem_desc(stage_b(stage, 0));
-                    const uint64_t da_lo = make_smem_desc(stage_a(stage, C::PARTS - 1));
-                    const uint64_t db_lo = make_smem_desc(stage_b(stage, C::PARTS - 1));
+                    const uint32_t tmem_d = tmem_base + (uint32_t)(acc * C::UMMA_N);
+                    const int kb1 = min(kb0 + per_unit, p.num_kb);
+                    for (int kb = kb0; kb < kb1; ++kb) {
+                        if (!wait_bounded(full_bar(stage), phase, p, 300 + stage, t)) { alive = false; break; }
+                        tc_fence_after();
+                        const uint64_t da_hi = make_smem_desc(stage_a(stage, 0));
+                        const uint64_t db_hi = make_smem_desc(stage_b(stage, 0));
+                        const uint64_t da_lo = make_smem_desc(stage_a(stage, C::PARTS - 1));
+                        const uint64_t db_lo = make_smem_desc(stage_b(stage, C::PARTS - 1));
 #pragma unroll
-                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                        /* advance 8 floats = 32 bytes inside the 128-byte swizzled row */
-                        const uint64_t koff = (uint64_t)((kk * UMMA_K * 4) >> 4);
-                        const uint32_t first = (kb | kk) != 0 ? 1u : 0u;
-                        if (NSPLIT == 3) {
-                            umma_tf32<CTAS>(tmem_d, da_lo + koff, db_hi + koff, idesc, first);
-                            umma_tf32<CTAS>(tmem_d, da_hi + koff, db_lo + koff, idesc, 1u);
-                            umma_tf32<CTAS>(tmem_d, da_hi + koff, db_hi + koff, idesc, 1u);
-                        } else if (NSPLIT == 16) {
-                            umma_f16<CTAS>(tmem_d, da_hi + koff, db_hi + koff, idesc, first);
-                        } else {
-                            umma_tf32<CTAS>(tmem_d, da_hi + koff, db_hi + koff, idesc, first);
+                        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                            /* advance 8 floats = 32 bytes inside the 128-byte swizzled row */
+                            const uint64_t koff = (uint64_t)((kk * UMMA_K * 4) >> 4);
+                            const uint32_t first = ((kb - kb0) | kk) != 0 ? 1u : 0u;
+                            if (NSPLIT == 3) {
+                                umma_tf32<CTAS>(tmem_d, da_lo + koff, db_hi + koff, idesc, first);
+                                umma_tf32<CTAS>(tmem_d, da_hi + koff, db_lo + koff, idesc, 1u);
+                                umma_tf32<CTAS>(tmem_d, da_hi + koff, db_hi + koff, idesc, 1u);
+                            } else if (NSPLIT == 16) {
+                                umma_f16<CTAS>(tmem_d, da_hi + koff, db_hi + koff, idesc, first);
+                            } else {
+                                umma_tf32<CTAS>(tmem_d, da_hi + koff, db_hi + koff, idesc, first);
+                            }
                         }
+                        umma_commit<CTAS>(empty_bar(stage));     /* stage reusable once these MMAs have read it */
+                        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                     }
-                    umma_commit<CTAS>(empty_bar(stage));     /* stage reusable once these MMAs have read it */
-                    if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                    if (alive) umma_commit<CTAS>(tfull_bar(acc)); /* accumulator (chunk) complete */
                 }
-                if (alive) umma_commit<CTAS>(tfull_bar(acc)); /* accumulator complete */
             }
         }
+    }
     } else {
         /* ------------------------------------------------------------ epilogue -------- */
+        if constexpr (REALLOC) asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         const int q = warp & 3;                   /* TMEM lane quarter this warp may read */
         const bool d_vec = ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) && (p.ldd % 4 == 0) && (p.d_batch_stride % 4 == 0) &&
                            (p.dst_img_stride % 4 == 0);
         const bool c_vec = p.C && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && (p.ldc % 4 == 0) && (p.c_batch_stride % 4 == 0);
-        int it = 0;
+        int unit = 0;                             /* same count as the MMA issuer's */
         bool alive = true;
-        for (int t = cluster_id; t < num_tiles && alive; t += num_clusters, ++it) {
+        const int eh = KCH ? (warp - 4) >> 2 : 0; /* chunked: column half this warp sums */
+        for (int t = cluster_id; t < num_tiles && alive; t += num_clusters) {
             int tm, tn; tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
-            const int acc = it & 1;
-            const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-            if (!wait_bounded(tfull_bar(acc), acc_phase, p, 400 + acc, t)) { alive = false; break; }
-            tc_fence_after();
             const int bidx = (!CONV && p.tiles_m_per) ? tm / p.tiles_m_per : 0;
             int64_t row = (int64_t)(tm - bidx * p.tiles_m_per) * C::UMMA_M + (int64_t)cta_rank * BM_CTA + q * 32 + lane;
             bool row_ok = row < p.M;
             const int64_t col0 = (int64_t)tn * C::UMMA_N;
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * C::UMMA_N);
+            const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16);
             float* __restrict__ drow = p.D + bidx * p.d_batch_stride + row * p.ldd;
             if (CONV) {
                 /* tile row i is pixel (px0 + i % bx, py0 + i / bx) of image img */
@@ -508,6 +566,54 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
                 drow = p.D + (int64_t)img * p.dst_img_stride + ((int64_t)y * p.eq_w + x) * p.ldd;
             }
             const float* __restrict__ crow = (p.C && !CONV) ? p.C + bidx * p.c_batch_stride + row * p.ldc : nullptr;
+            const bool vec = d_vec && (!crow || c_vec);
+            if constexpr (KCH > 0) {
+                /* chunked accumulation: this warp owns NCW columns of its 32 rows */
+                constexpr int NCW = C::UMMA_N / 2;
+                static_assert(NCW % 32 == 0, "column half must be whole 32-column groups");
+                constexpr int DRAIN = NCW < 64 ? NCW : 64;   /* columns fetched per round */
+                float sum[NCW];
+#pragma unroll
+                for (int c = 0; c < NCW; ++c) sum[c] = 0.0f;
+                for (int kb0 = 0; kb0 < p.num_kb; kb0 += KCH, ++unit) {
+                    const int acc = unit & 1;
+                    const uint32_t acc_phase = (uint32_t)(unit >> 1) & 1u;
+                    if (!wait_bounded(tfull_bar(acc), acc_phase, p, 400 + acc, t)) { alive = false; break; }
+                    tc_fence_after();
+                    const uint32_t taddr = tlane + (uint32_t)(acc * C::UMMA_N + eh * NCW);
+#pragma unroll
+                    for (int c = 0; c < NCW; c += DRAIN) {
+                        /* the loads of one round are in flight together; one wait per round */
+                        float v[DRAIN];
+#pragma unroll
+                        for (int g = 0; g < DRAIN; g += 32) tmem_ld_32x32(taddr + (uint32_t)(c + g), v + g);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < DRAIN; ++j) sum[c + j] = __fadd_rn(sum[c + j], v[j]);
+                    }
+                    /* chunk taken: hand the buffer back to the MMA issuer (in the leader CTA) */
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (CTAS == 1) mbar_arrive_cluster(tempty_bar(acc));
+                        else           mbar_arrive_cluster(mapa(tempty_bar(acc), 0));
+                    }
+                }
+                if (!alive) break;
+                if (row_ok) {
+#pragma unroll
+                    for (int c = 0; c < NCW; c += 32) {
+                        if (col0 + eh * NCW + c < p.N) store32_f32(sum + c, col0 + eh * NCW + c, p, drow, crow, vec);
+                        asm volatile("" ::: "memory");   /* keep the next group's loads behind these stores */
+                    }
+                }
+            } else {
+            const int acc = unit & 1;
+            const uint32_t acc_phase = (uint32_t)(unit >> 1) & 1u;
+            ++unit;
+            if (!wait_bounded(tfull_bar(acc), acc_phase, p, 400 + acc, t)) { alive = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = tlane + (uint32_t)(acc * C::UMMA_N);
 #pragma unroll 1
             for (int c = 0; c < C::UMMA_N; c += 32) {
                 if (col0 + c >= p.N) break;           /* warp-uniform */
@@ -543,34 +649,7 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
                         }
                     }
                 } else if (row_ok) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        const int64_t col = col0 + c + j;
-                        if (col + 3 < p.N && d_vec && (!crow || c_vec)) {
-                            float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                            if (crow) {
-                                const float4 ci = __ldg(reinterpret_cast<const float4*>(crow + col));
-                                o.x += ci.x; o.y += ci.y; o.z += ci.z; o.w += ci.w;
-                            }
-                            if (p.bias) {
-                                o.x += __ldg(p.bias + col); o.y += __ldg(p.bias + col + 1);
-                                o.z += __ldg(p.bias + col + 2); o.w += __ldg(p.bias + col + 3);
-                            }
-                            if (p.act) {
-                                o.x = apply_act(o.x, p.act); o.y = apply_act(o.y, p.act);
-                                o.z = apply_act(o.z, p.act); o.w = apply_act(o.w, p.act);
-                            }
-                            *reinterpret_cast<float4*>(drow + col) = o;
-                        } else {
-#pragma unroll
-                            for (int e = 0; e < 4; ++e)
-                                if (col + e < p.N) {
-                                    float x = v[j + e] + (crow ? __ldg(crow + col + e) : 0.0f);
-                                    if (p.bias) x += __ldg(p.bias + col + e);
-                                    drow[col + e] = p.act ? apply_act(x, p.act) : x;
-                                }
-                        }
-                    }
+                    store32_f32(v, col0 + c, p, drow, crow, vec);
                 }
             }
             /* accumulator drained: hand it back to the MMA issuer (in the leader CTA) */
@@ -580,6 +659,7 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
                 if (CTAS == 1) mbar_arrive_cluster(tempty_bar(acc));
                 else           mbar_arrive_cluster(mapa(tempty_bar(acc), 0));
             }
+            }   /* whole-K accumulation */
         }
     }
 
@@ -677,12 +757,12 @@ int make_map_conv(decxb_ctx* ctx, CUtensorMap* map, const float* base, int64_t d
     return DECXB_OK;
 }
 
-template <int CTAS, int BN, int NSPLIT, bool CONV>
+template <int CTAS, int BN, int NSPLIT, bool CONV, int KCH = 0>
 int launch_kernel(decxb_ctx* ctx, const CUtensorMap& ma_hi, const CUtensorMap& ma_lo, const CUtensorMap& mb_hi,
                   const CUtensorMap& mb_lo, const GemmParams& p, cudaStream_t s)
 {
     using C = Cfg<CTAS, BN, NSPLIT>;
-    auto kernel = decxb_gemm_tf32_kernel<CTAS, BN, NSPLIT, CONV>;
+    auto kernel = decxb_gemm_tf32_kernel<CTAS, BN, NSPLIT, CONV, KCH>;
     static std::once_flag once[16];
     static cudaError_t attr_err[16];
     const int dev = ctx->device & 15;
@@ -691,13 +771,24 @@ int launch_kernel(decxb_ctx* ctx, const CUtensorMap& ma_hi, const CUtensorMap& m
     });
     if (attr_err[dev] != cudaSuccess)
         return decxb_fail(ctx, DECXB_ERR_CUDA, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(attr_err[dev]));
+    if (KCH > 0 && C::UMMA_N / 2 > 64) {
+        /* the kernel moves registers between its warp groups and counts on 168 per thread at launch */
+        static int regs[16];
+        if (regs[dev] == 0) {
+            cudaFuncAttributes fa;
+            DECXB_CUDA_TRY(ctx, cudaFuncGetAttributes(&fa, kernel));
+            regs[dev] = fa.numRegs;
+        }
+        if (regs[dev] != 168)
+            return decxb_fail(ctx, DECXB_ERR_CUDA, "chunked GEMM kernel compiled to " + std::to_string(regs[dev]) + " registers, 168 expected");
+    }
     const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
     int64_t clusters = ctx->sm_count / CTAS;
     if (clusters > tiles) clusters = tiles;
     if (clusters < 1) clusters = 1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(clusters * CTAS), 1, 1);
-    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.blockDim = dim3(KCH ? NUM_THREADS_CHUNKED : NUM_THREADS, 1, 1);
     cfg.dynamicSmemBytes = C::SMEM_BYTES;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
@@ -711,7 +802,7 @@ int launch_kernel(decxb_ctx* ctx, const CUtensorMap& ma_hi, const CUtensorMap& m
     return DECXB_OK;
 }
 
-template <int CTAS, int BN, int NSPLIT>
+template <int CTAS, int BN, int NSPLIT, int KCH = 0>
 int launch_conv_cfg(decxb_ctx* ctx, const decxb_conv_gemm_args& a, cudaStream_t s)
 {
     using C = Cfg<CTAS, BN, NSPLIT>;
@@ -750,10 +841,10 @@ int launch_conv_cfg(decxb_ctx* ctx, const decxb_conv_gemm_args& a, cudaStream_t 
     p.num_kb = (int)(a.kW * a.kH * cblocks);
     p.wait_limit_ns = ctx->wait_limit_ns;
     p.status = ctx->d_status;
-    return launch_kernel<CTAS, BN, NSPLIT, true>(ctx, ma_hi, ma_lo, mb_hi, mb_lo, p, s);
+    return launch_kernel<CTAS, BN, NSPLIT, true, KCH>(ctx, ma_hi, ma_lo, mb_hi, mb_lo, p, s);
 }
 
-template <int CTAS, int BN, int NSPLIT>
+template <int CTAS, int BN, int NSPLIT, int KCH = 0>
 int launch_cfg(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s)
 {
     using C = Cfg<CTAS, BN, NSPLIT>;
@@ -785,7 +876,7 @@ int launch_cfg(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s)
     p.num_kb = (int)decxb_ceil_div(a.K, BK);
     p.wait_limit_ns = ctx->wait_limit_ns;
     p.status = ctx->d_status;
-    return launch_kernel<CTAS, BN, NSPLIT, false>(ctx, ma_hi, ma_lo, mb_hi, mb_lo, p, s);
+    return launch_kernel<CTAS, BN, NSPLIT, false, KCH>(ctx, ma_hi, ma_lo, mb_hi, mb_lo, p, s);
 }
 
 
@@ -859,6 +950,16 @@ int decxb_launch_gemm_tn(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t 
     const bool x3 = a.a_lo != nullptr;
     int tile = a.tile;
     if (tile == DECXB_TILE_AUTO) tile = decxb_pick_tile(ctx, a.M, a.N, a.nbatch);
+    if (a.chunked) {
+        if (!x3) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "chunked accumulation needs the 3xTF32 operands");
+        switch (tile) {
+        case DECXB_TILE_1CTA_128x128: return launch_cfg<1, 128, 3, KCHUNK>(ctx, a, s);
+        case DECXB_TILE_2CTA_256x256: return launch_cfg<2, 128, 3, KCHUNK>(ctx, a, s);
+        case DECXB_TILE_1CTA_128x256: return launch_cfg<1, 256, 3, KCHUNK>(ctx, a, s);
+        case DECXB_TILE_1CTA_128x64:  return launch_cfg<1, 64, 3, KCHUNK>(ctx, a, s);
+        default: return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "unknown gemm tile");
+        }
+    }
     switch (tile) {
     case DECXB_TILE_1CTA_128x128: return x3 ? launch_cfg<1, 128, 3>(ctx, a, s) : launch_cfg<1, 128, 1>(ctx, a, s);
     case DECXB_TILE_2CTA_256x256: return x3 ? launch_cfg<2, 128, 3>(ctx, a, s) : launch_cfg<2, 128, 1>(ctx, a, s);
@@ -871,6 +972,12 @@ int decxb_launch_gemm_tn(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t 
 int decxb_launch_conv_implicit(decxb_ctx* ctx, const decxb_conv_gemm_args& a, cudaStream_t s)
 {
     const bool x3 = a.src_lo != nullptr;
+    if (a.chunked) {
+        if (!x3) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "chunked accumulation needs the 3xTF32 operands");
+        if (a.Np <= 64)  return launch_conv_cfg<1, 64, 3, KCHUNK>(ctx, a, s);
+        if (a.Np <= 128) return launch_conv_cfg<1, 128, 3, KCHUNK>(ctx, a, s);
+        return launch_conv_cfg<2, 128, 3, KCHUNK>(ctx, a, s);
+    }
     if (a.Np <= 64)  return x3 ? launch_conv_cfg<1, 64, 3>(ctx, a, s)  : launch_conv_cfg<1, 64, 1>(ctx, a, s);
     if (a.Np <= 128) return x3 ? launch_conv_cfg<1, 128, 3>(ctx, a, s) : launch_conv_cfg<1, 128, 1>(ctx, a, s);
     return x3 ? launch_conv_cfg<2, 128, 3>(ctx, a, s) : launch_conv_cfg<2, 128, 1>(ctx, a, s);

@@ -57,11 +57,12 @@ typedef enum decxb_gemm_mode {
     DECXB_GEMM_3XTF32 = 0,
     DECXB_GEMM_1XTF32 = 1,
     /* 3xTF32 with the K dimension accumulated in chunks of 128: every chunk starts a fresh
-     * tensor-core accumulator and the chunk results are added in IEEE fp32 (round to nearest) on
-     * the CUDA cores.  The tensor core's accumulator rounds toward zero, which biases long sums
-     * of same-sign terms (the reference test program's all-positive matrices reach 2.9e-6 of
-     * K max|a| max|b| at K = 2048); chunking brings such inputs to 3.3e-7, at the price
-     * of re-reading and re-writing D once per chunk. */
+     * tensor-core accumulator, and the epilogue warps add the finished chunks to a running sum in
+     * registers with IEEE fp32 adds (round to nearest) while the tensor core works on the next
+     * chunk, all inside the one kernel.  The tensor core's accumulator rounds toward zero, which
+     * biases long sums of same-sign terms (the reference test program's all-positive matrices
+     * reach 2.9e-6 of K max|a| max|b| at K = 2048); chunking brings such inputs to 3.3e-7.
+     * Accepted by every fp32 GEMM and convolution entry point. */
     DECXB_GEMM_3XTF32_STRICT = 2
 } decxb_gemm_mode;
 

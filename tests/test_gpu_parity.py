@@ -136,6 +136,58 @@ def test_gemm_strict_mode_meets_the_bar_on_same_sign_data(ctx):
     assert o.norm_err(D, R, K, 1.0, 1.0) <= TOL_3X
 
 
+@pytest.mark.parametrize("tile", TILES)
+@pytest.mark.parametrize("shape", [(128, 128, 32), (128, 128, 128), (256, 256, 160), (257, 129, 33), (300, 520, 777),
+                                   (1024, 1024, 1024), (100, 70, 50), (512, 300, 1300)])
+def test_gemm_strict_mode_every_tile_and_ragged_k(ctx, shape, tile):
+    """Chunked accumulation in every tile configuration: K below one chunk (32, 33, 50), exactly
+    one chunk (128), a ragged last chunk (160, 777, 1300) and whole chunks (1024); with an addend."""
+    M, N, K = shape
+    A = o.fill_uniform(M * K, 1).reshape(M, K)
+    B = o.fill_uniform(K * N, 2).reshape(K, N)
+    Cin = o.fill_uniform(M * N, 3).reshape(M, N)
+    D = run_gemm(ctx, A, B, mode=b.GEMM_3XTF32_STRICT, tile=tile)
+    assert not np.isnan(D).any()
+    assert o.norm_err(D, o.gemm_fmaf(A, B), K, 1.0, 1.0) <= TOL_3X
+    Dc = run_gemm(ctx, A, B, Cin, mode=b.GEMM_3XTF32_STRICT, tile=tile)
+    assert o.norm_err(Dc, o.gemm_fmaf(A, B, Cin), K, 1.0, 1.0) <= TOL_3X
+
+
+@pytest.mark.parametrize("tile", TILES)
+def test_gemm_strict_mode_same_sign_data_every_tile(ctx, tile):
+    """All-positive operands (the worst case for the tensor core's round-toward-zero accumulator)
+    at 1024 x 512 x 2048 in every tile configuration: within 1e-6 of K max|a| max|b|."""
+    M, N, K = 1024, 512, 2048
+    v = (0.1 * np.arange(K, dtype=np.float32)).astype(np.float32)
+    A = np.tile(v[None, :], (M, 1)); B = np.tile(v[:, None], (1, N))
+    expect = float(np.sum(v.astype(np.float64) ** 2))
+    D = run_gemm(ctx, A, B, mode=b.GEMM_3XTF32_STRICT, tile=tile)
+    assert np.all(D == D[0, 0]), "every element must be the same number"
+    assert abs(float(D[0, 0]) - expect) / (K * float(v.max()) ** 2) <= TOL_3X
+
+
+def test_strict_mode_batched_and_convolution(ctx):
+    """The chunked mode through the batched GEMM (one launch) and both convolution algorithms."""
+    nb, M, N, K = 5, 130, 90, 300
+    A = o.fill_uniform(nb * M * K, 1).reshape(nb, M, K)
+    B = o.fill_uniform(nb * K * N, 2).reshape(nb, K, N)
+    R = np.stack([o.gemm_fmaf(A[i], B[i]) for i in range(nb)])
+    dD = torch.full((nb, M, N), float("nan"), device=DEV)
+    ctx.gemm_batched(nb, M, N, K, dev(A), K, M * K, dev(B), N, K * N, dD, N, M * N, mode=b.GEMM_3XTF32_STRICT)
+    ctx.synchronize()
+    assert o.norm_err(dD.cpu().numpy(), R, K, 1.0, 1.0) <= TOL_3X
+    for W, H, C, kW, kH, Nf, flag in [(40, 30, 20, 3, 3, 24, 0), (66, 34, 64, 3, 3, 200, 1), (30, 30, 40, 5, 5, 100, 1)]:
+        src = o.make_tensor(W, H, C, 4)
+        flt = o.make_filters(kW, kH, C, Nf, 5)
+        Rc = o.conv2_im2col(src, W, C, flt, kW, flag)
+        Kc = kW * kH * o.ceil4(C)
+        for algo in ALGOS:
+            Dv = run_conv(ctx, src, W, C, flt, kW, flag, mode=b.GEMM_3XTF32_STRICT, algo=algo)
+            assert not np.isnan(Dv).any()
+            assert o.norm_err(Dv, Rc, Kc, 1.0, 1.0) <= TOL_3X
+            assert np.all(Dv[..., Nf:] == 0)
+
+
 def test_gemm_pitched_operands(ctx):
     """Leading dimensions larger than the row length (DECX pitch = ceil8(width))."""
     M, N, K = 130, 100, 70
