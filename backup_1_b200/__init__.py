@@ -12,6 +12,7 @@ from .lib import (  # noqa: F401
     GEMM_1XTF32,
     GEMM_3XTF32,
     GEMM_3XTF32_STRICT,
+    GEMM_DEFAULT,
     ACT_NONE,
     ACT_RELU,
     ACT_SIGMOID,

@@ -17,7 +17,7 @@
 namespace decx {
 
 /* decx::cuP of the reference (srcs/core/configs/config.h:50): whether InitCuda ran. */
-struct cudaProp { bool is_init = false; decxb_ctx* ctx = nullptr; bool plain_tf32 = false; bool strict = false; bool explicit_pack = false; };
+struct cudaProp { bool is_init = false; decxb_ctx* ctx = nullptr; bool plain_tf32 = false; bool strict = true; bool explicit_pack = false; };
 static cudaProp cuP;
 
 static inline uint ceil_to(uint v, uint m) { return (v + m - 1) / m * m; }
@@ -388,7 +388,7 @@ static int gemm_mode()
 {
     return decx::cuP.plain_tf32 ? DECXB_GEMM_1XTF32 : decx::cuP.strict ? DECXB_GEMM_3XTF32_STRICT : DECXB_GEMM_3XTF32;
 }
-static int conv_gemm_mode() { return decx::cuP.plain_tf32 ? DECXB_GEMM_1XTF32 : DECXB_GEMM_3XTF32; }
+static int conv_gemm_mode() { return gemm_mode(); }
 static int conv_algo() { return decx::cuP.explicit_pack ? DECXB_CONV_EXPLICIT : DECXB_CONV_IMPLICIT; }
 
 static DH gemm_host(Matrix<float>& A, Matrix<float>& B, Matrix<float>* C, Matrix<float>& dst)

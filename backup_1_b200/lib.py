@@ -5,6 +5,7 @@ import ctypes as C
 from pathlib import Path
 
 GEMM_3XTF32, GEMM_1XTF32, GEMM_3XTF32_STRICT = 0, 1, 2
+GEMM_DEFAULT = GEMM_3XTF32_STRICT   # what the DECX-facing host layer uses unless told otherwise
 TILE_AUTO, TILE_1CTA_128x128, TILE_2CTA_256x256, TILE_1CTA_128x256, TILE_1CTA_128x64 = 0, 1, 2, 3, 4
 CONV_NO_COMPENSATE, CONV_ZERO_COMPENSATE = 0, 1
 CONV_EXPLICIT, CONV_IMPLICIT = 0, 1
@@ -187,20 +188,20 @@ class Context:
         self._chk(self.L.decxb_fill_uniform_f32(self.h, _ptr(dst), rows, cols, pitch, seed, first_index, stream))
 
     # -- GEMM ---------------------------------------------------------------------------
-    def gemm(self, M, N, K, A, lda, B, ldb, D, ldd, Cin=None, ldc=0, mode=GEMM_3XTF32, tile=TILE_AUTO, stream=None):
+    def gemm(self, M, N, K, A, lda, B, ldb, D, ldd, Cin=None, ldc=0, mode=GEMM_DEFAULT, tile=TILE_AUTO, stream=None):
         self._chk(self.L.decxb_gemm_f32(self.h, mode, tile, M, N, K, _ptr(A), lda, _ptr(B), ldb,
                                         _ptr(Cin), ldc, _ptr(D), ldd, stream))
 
     def gemm_act(self, M, N, K, A, lda, B, ldb, D, ldd, Cin=None, ldc=0, bias=None, act=ACT_NONE,
-                 mode=GEMM_3XTF32, tile=TILE_AUTO, stream=None):
+                 mode=GEMM_DEFAULT, tile=TILE_AUTO, stream=None):
         self._chk(self.L.decxb_gemm_f32_act(self.h, mode, tile, M, N, K, _ptr(A), lda, _ptr(B), ldb, _ptr(Cin), ldc,
                                             _ptr(bias), act, _ptr(D), ldd, stream))
 
-    def gemm_nt(self, M, N, K, A, lda, Bt, ldbt, D, ldd, Cin=None, ldc=0, mode=GEMM_3XTF32, tile=TILE_AUTO, stream=None):
+    def gemm_nt(self, M, N, K, A, lda, Bt, ldbt, D, ldd, Cin=None, ldc=0, mode=GEMM_DEFAULT, tile=TILE_AUTO, stream=None):
         self._chk(self.L.decxb_gemm_f32_nt(self.h, mode, tile, M, N, K, _ptr(A), lda, _ptr(Bt), ldbt,
                                            _ptr(Cin), ldc, _ptr(D), ldd, stream))
 
-    def gemm_host(self, M, N, K, A, lda, B, ldb, D, ldd, Cin=None, ldc=0, mode=GEMM_3XTF32, tile=TILE_AUTO):
+    def gemm_host(self, M, N, K, A, lda, B, ldb, D, ldd, Cin=None, ldc=0, mode=GEMM_DEFAULT, tile=TILE_AUTO):
         self._chk(self.L.decxb_gemm_f32_host(self.h, mode, tile, M, N, K, _ptr(A), lda, _ptr(B), ldb,
                                              _ptr(Cin), ldc, _ptr(D), ldd))
 
@@ -211,12 +212,12 @@ class Context:
         self._chk(self.L.decxb_gemm_f16_host(self.h, M, N, K, _ptr(A), lda, _ptr(B), ldb, _ptr(Cin), ldc, _ptr(D), ldd))
 
     def gemm_batched(self, batch, M, N, K, A, lda, sA, B, ldb, sB, D, ldd, sD, Cin=None, ldc=0, sC=0,
-                     mode=GEMM_3XTF32, tile=TILE_AUTO, stream=None):
+                     mode=GEMM_DEFAULT, tile=TILE_AUTO, stream=None):
         self._chk(self.L.decxb_gemm_f32_batched(self.h, mode, tile, batch, M, N, K, _ptr(A), lda, sA, _ptr(B), ldb, sB,
                                                 _ptr(Cin), ldc, sC, _ptr(D), ldd, sD, stream))
 
     def gemm_batched_host(self, batch, M, N, K, A, lda, sA, B, ldb, sB, D, ldd, sD, Cin=None, ldc=0, sC=0,
-                          mode=GEMM_3XTF32, tile=TILE_AUTO):
+                          mode=GEMM_DEFAULT, tile=TILE_AUTO):
         self._chk(self.L.decxb_gemm_f32_batched_host(self.h, mode, tile, batch, M, N, K, _ptr(A), lda, sA, _ptr(B), ldb, sB,
                                                      _ptr(Cin), ldc, sC, _ptr(D), ldd, sD))
 
@@ -229,18 +230,18 @@ class Context:
                                                batch, src_stride, i2c_stride, stream))
 
     def conv2_im2col(self, src, W, H, depth, filters, kW, kH, N, dst, flag=CONV_ZERO_COMPENSATE, batch=1,
-                     src_stride=0, dst_stride=0, mode=GEMM_3XTF32, algo=CONV_EXPLICIT, stream=None):
+                     src_stride=0, dst_stride=0, mode=GEMM_DEFAULT, algo=CONV_EXPLICIT, stream=None):
         self._chk(self.L.decxb_conv2_im2col_f32(self.h, mode, algo, flag, _ptr(src), W, H, depth, _ptr(filters),
                                                 kW, kH, N, _ptr(dst), batch, src_stride, dst_stride, stream))
 
     def conv2_im2col_act(self, src, W, H, depth, filters, kW, kH, N, dst, bias=None, act=ACT_NONE,
-                         flag=CONV_ZERO_COMPENSATE, batch=1, src_stride=0, dst_stride=0, mode=GEMM_3XTF32,
+                         flag=CONV_ZERO_COMPENSATE, batch=1, src_stride=0, dst_stride=0, mode=GEMM_DEFAULT,
                          algo=CONV_IMPLICIT, stream=None):
         self._chk(self.L.decxb_conv2_im2col_f32_act(self.h, mode, algo, flag, _ptr(src), W, H, depth, _ptr(filters),
                                                     kW, kH, N, _ptr(bias), act, _ptr(dst), batch, src_stride,
                                                     dst_stride, stream))
 
     def conv2_im2col_host(self, src, W, H, depth, filters, kW, kH, N, dst, flag=CONV_ZERO_COMPENSATE, batch=1,
-                          src_stride=0, dst_stride=0, mode=GEMM_3XTF32, algo=CONV_EXPLICIT):
+                          src_stride=0, dst_stride=0, mode=GEMM_DEFAULT, algo=CONV_EXPLICIT):
         self._chk(self.L.decxb_conv2_im2col_f32_host(self.h, mode, algo, flag, _ptr(src), W, H, depth, _ptr(filters),
                                                      kW, kH, N, _ptr(dst), batch, src_stride, dst_stride))

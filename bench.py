@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the fp32 GEMM / im2col-convolution hot path on B200.
 
-    python bench.py --gpus N --steps K --warmup W [--workload NAME] [--mode 3xtf32|1xtf32]
+    python bench.py --gpus N --steps K --warmup W [--workload NAME] [--mode strict|3xtf32|1xtf32|f16]
     python bench.py --impl reference ...     # the reference's CPU GEMM on the host cores
 
 One "step" is one pass of the hot path over one batch of synthetic input.  Default workload:
@@ -43,7 +43,8 @@ WORKLOADS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel, from the ncu
 # captures summarised under profiles/ (gemm_tf32_kernel_cfg2.md, im2col_pack_kernel_cfg3.md)
-NCU_TRAFFIC_BYTES = {("cfg2", "3xtf32", "gemm"): 727.8e6, ("cfg3", "3xtf32", "pack"): 70.7e6}
+NCU_TRAFFIC_BYTES = {("cfg2", "3xtf32", "gemm"): 727.8e6, ("cfg2", "strict", "gemm"): 732.1e6, ("cfg3", "3xtf32", "pack"): 70.7e6,
+                     ("cfg3", "strict", "pack"): 70.7e6}
 
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
@@ -165,7 +166,9 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
-    ap.add_argument("--mode", default="3xtf32", choices=["3xtf32", "1xtf32", "strict", "f16"])
+    ap.add_argument("--mode", default="strict", choices=["strict", "3xtf32", "1xtf32", "f16"],
+                    help="strict = 3xTF32 with chunked IEEE accumulation (the default of the DECX-facing layer); "
+                         "3xtf32 = tensor core accumulates over all of K; 1xtf32 = plain TF32; f16 = the fp16 overloads")
     ap.add_argument("--tile", type=int, default=0)
     ap.add_argument("--algo", default="implicit", choices=["explicit", "implicit"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -222,7 +225,7 @@ def main():
         ctx.fill_uniform(dA, M_rank, K, K, 1, first_index=row0 * K)
         ctx.fill_uniform(dB, K, N, N, 2)
         flops_rank = 2.0 * M_rank * N * K
-        touched = (M_rank * K + K * N) * 4 * (3 if args.mode == "3xtf32" else 2) + M_rank * N * 4
+        touched = (M_rank * K + K * N) * 4 * (3 if args.mode in ("3xtf32", "strict") else 2) + M_rank * N * 4
 
         def step():
             ctx.gemm(M_rank, N, K, dA, K, dB, N, dD, N, mode=mode, tile=args.tile, stream=st)
@@ -265,7 +268,7 @@ def main():
         dF[:, :, :kW, :] = tmpF
         dO = torch.empty((nb, g.out_h, g.eq_w, g.Np), device=dev)
         flops_rank = 2.0 * nb * (H * W) * (kW * kH * C) * F
-        touched = dS.numel() * 4 + nb * g.M * g.Kp * 4 * (3 if args.mode == "3xtf32" else 1) + dO.numel() * 4
+        touched = dS.numel() * 4 + nb * g.M * g.Kp * 4 * (3 if args.mode in ("3xtf32", "strict") else 1) + dO.numel() * 4
 
         def step():
             ctx.conv2_im2col(dS, W, H, C, dF, kW, kH, F, dO, flag=1, batch=nb, mode=mode, algo=algo, stream=st)
@@ -346,7 +349,7 @@ def main():
         avg_ms = k["ms"] / k["launches"]
         per_step = k["launches"] / args.steps
         if dom == "pack":
-            packs = 2 if args.mode == "3xtf32" else 1                    # hi and lo parts are packed separately
+            packs = 2 if args.mode in ("3xtf32", "strict") else 1                    # hi and lo parts are packed separately
             alg = packs * (H * wp * dp + g.M * g.Kp) * 4 * nb / per_step   # read tensor, write column matrix
             kname = "decxb_im2col_pack_tma_kernel"
         elif wl["kind"] == "conv":

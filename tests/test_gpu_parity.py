@@ -22,7 +22,7 @@ def dev(a: np.ndarray) -> torch.Tensor:
     return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
 
 
-def run_gemm(ctx, A, B, Cin=None, mode=b.GEMM_3XTF32, tile=b.TILE_AUTO, nt=False):
+def run_gemm(ctx, A, B, Cin=None, mode=b.GEMM_DEFAULT, tile=b.TILE_AUTO, nt=False):
     M, K = A.shape
     N = B.shape[1]
     dA = dev(A)
@@ -49,13 +49,14 @@ def test_seeded_fill_is_bit_identical_to_oracle(ctx):
         assert np.array_equal(t.cpu().numpy().view(np.uint32), ref.view(np.uint32))
 
 
+@pytest.mark.parametrize("mode", [b.GEMM_DEFAULT, b.GEMM_3XTF32])
 @pytest.mark.parametrize("tile", TILES)
 @pytest.mark.parametrize("shape", GEMM_SHAPES)
-def test_gemm_3xtf32_matches_fma_chain(ctx, shape, tile):
+def test_gemm_3xtf32_matches_fma_chain(ctx, shape, tile, mode):
     M, N, K = shape
     A = o.fill_uniform(M * K, 1).reshape(M, K)
     B = o.fill_uniform(K * N, 2).reshape(K, N)
-    D = run_gemm(ctx, A, B, tile=tile)
+    D = run_gemm(ctx, A, B, tile=tile, mode=mode)
     R = o.gemm_fmaf(A, B)
     err = o.norm_err(D, R, K, 1.0, 1.0)
     assert err <= TOL_3X, f"{shape} tile {tile}: {err:.3e}"
@@ -103,14 +104,18 @@ def test_gemm_known_answer_of_reference_test_program(ctx):
     v = (0.1 * np.arange(n, dtype=np.float32)).astype(np.float32)
     A = np.tile(v[None, :], (n, 1))
     B = np.tile(v[:, None], (1, n))
-    D = run_gemm(ctx, A, B)
     expect = float(np.sum(v.astype(np.float64) ** 2))
+    D = run_gemm(ctx, A, B)
     assert np.all(D == D[0, 0]), "every element must be the same number"
     # All terms are positive and grow with k: the worst case for the tensor core's fp32
-    # accumulator, which rounds every add toward zero.  The bias stays below 1e-5 of
-    # K max|a| max|b| (seeded +-1 data of the benchmark configs sits near 1e-7).
-    assert abs(float(D[0, 0]) - expect) / (n * float(v.max()) ** 2) <= 1e-5
-    assert abs(float(D[0, 0]) - expect) / expect <= 2e-5
+    # accumulator, which rounds every add toward zero.  The default mode (K in chunks of 128
+    # added in IEEE fp32) stays within the 1e-6 bar; whole-K tensor-core accumulation is the
+    # opt-in faster mode and stays below 1e-5 here (seeded +-1 data sits near 1e-7 in both).
+    assert abs(float(D[0, 0]) - expect) / (n * float(v.max()) ** 2) <= TOL_3X
+    Df = run_gemm(ctx, A, B, mode=b.GEMM_3XTF32)
+    assert np.all(Df == Df[0, 0])
+    assert abs(float(Df[0, 0]) - expect) / (n * float(v.max()) ** 2) <= 1e-5
+    assert abs(float(Df[0, 0]) - expect) / expect <= 2e-5
 
 
 def test_gemm_strict_mode_meets_the_bar_on_same_sign_data(ctx):
@@ -123,7 +128,7 @@ def test_gemm_strict_mode_meets_the_bar_on_same_sign_data(ctx):
     expect = float(np.sum(v.astype(np.float64) ** 2))
     scale = n * float(v.max()) ** 2
     e_strict = abs(float(run_gemm(ctx, A, B, mode=b.GEMM_3XTF32_STRICT)[7, 9]) - expect) / scale
-    e_plain = abs(float(run_gemm(ctx, A, B)[7, 9]) - expect) / scale
+    e_plain = abs(float(run_gemm(ctx, A, B, mode=b.GEMM_3XTF32)[7, 9]) - expect) / scale
     assert e_strict <= TOL_3X < e_plain
     M, N, K = 300, 200, 1300
     A = o.fill_uniform(M * K, 1).reshape(M, K); B = o.fill_uniform(K * N, 2).reshape(K, N)
@@ -436,7 +441,7 @@ CONV_CASES = [(12, 20, 6, 5, 3, 5, 1), (22, 19, 6, 3, 5, 5, 0), (9, 7, 3, 3, 3, 
               (17, 33, 8, 7, 5, 4, 0), (28, 28, 64, 3, 3, 64, 1), (56, 56, 64, 3, 3, 130, 1)]
 
 
-def run_conv(ctx, src, W, depth, flt, kW, flag, mode=b.GEMM_3XTF32, algo=b.CONV_EXPLICIT, host=False):
+def run_conv(ctx, src, W, depth, flt, kW, flag, mode=b.GEMM_DEFAULT, algo=b.CONV_EXPLICIT, host=False):
     H = src.shape[-3]
     N, kH = flt.shape[0], flt.shape[1]
     nb = src.shape[0] if src.ndim == 4 else 1
