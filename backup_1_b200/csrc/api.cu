@@ -179,44 +179,87 @@ extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M
         return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
     if (mode != DECXB_GEMM_3XTF32 && mode != DECXB_GEMM_1XTF32 && mode != DECXB_GEMM_3XTF32_STRICT)
         return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "gemm mode");
-    /* Three streams: uploads, compute, downloads.  B goes up first and is prepared once; A
-     * (and C) go up in row-blocks, each multiplied as soon as it has landed while the next one
-     * is in flight and the previous result block is on its way back.  (The reference does the
-     * three phases one after the other on one stream, GEMM.h:106-123.) */
+    /* Three streams: uploads, compute, downloads.  (The reference does the three phases one
+     * after the other on one stream, GEMM.h:106-123.)
+     * Phase 1: the first row-block of A (about K rows, so that its result takes as long to
+     * download as B takes to upload) goes up, then B in column blocks; every column block is
+     * prepared and multiplied with that row-block as soon as it has landed, and its piece of
+     * the result starts its way back while the next column block is still in flight.
+     * Phase 2: the remaining row-blocks of A (and C) go up, each multiplied with the whole
+     * prepared B as it lands while the previous result block downloads. */
     cudaStream_t s = ctx->stream, up = ctx->copy_stream[0], down = ctx->copy_stream[1];
     Scratch scratch(ctx, s);
     ChunkEvents evs;
     const bool strict = mode == DECXB_GEMM_3XTF32_STRICT;
     const bool x3 = mode == DECXB_GEMM_3XTF32 || strict;
     const int64_t Kp = decxb_ceil_to(K, 4), Np = decxb_ceil_to(N, 4);
-    float *dA, *dB, *dC = nullptr, *dD;
+    float *dA, *dB, *dC = nullptr, *dD, *b_hi = nullptr, *b_lo = nullptr;
     if ((rc = scratch.get((size_t)M * Kp * 4, (void**)&dA))) return rc;
     if ((rc = scratch.get((size_t)K * Np * 4, (void**)&dB))) return rc;
     if ((rc = scratch.get((size_t)M * Np * 4, (void**)&dD))) return rc;
     if (hC && (rc = scratch.get((size_t)M * Np * 4, (void**)&dC))) return rc;
+    if ((rc = scratch.get((size_t)N * Kp * 4, (void**)&b_hi))) return rc;
+    if (x3 && (rc = scratch.get((size_t)N * Kp * 4, (void**)&b_lo))) return rc;
     if ((rc = fence_copy_streams(ctx, evs))) return rc;
-    /* row-blocks of about 1/8 of M, multiples of 256 rows, at least 512 */
+    /* later row-blocks: about 1/8 of M, multiples of 256 rows, at least 512 */
     int64_t rows = decxb_ceil_to(decxb_ceil_div(M, 8), 256);
     if (rows < 512) rows = 512;
     if (rows > M) rows = M;
-    cudaEvent_t eb = evs.make();
-    if (!eb) return decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate");
-    DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dB, Np * 4, hB, ldb * 4, N * 4, K, cudaMemcpyHostToDevice, up));
-    DECXB_CUDA_TRY(ctx, cudaEventRecord(eb, up));
-    DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(s, eb, 0));
-    PreparedB pb;
-    if ((rc = prepare_b(ctx, scratch, x3, N, K, dB, Np, false, s, &pb))) { sync_all_streams(ctx); return rc; }
-    for (int64_t r0 = 0; r0 < M; r0 += rows) {
+    /* first row-block: about K rows; column blocks of B: about 1/8 of N, at least 1024 columns */
+    int64_t rows0 = decxb_ceil_to(K, 256);
+    if (rows0 < rows) rows0 = rows;
+    if (rows0 > M) rows0 = M;
+    int64_t ncol = decxb_ceil_to(decxb_ceil_div(N, 8), 256);
+    if (ncol < 1024) ncol = 1024;
+    if (N < 2048 || ncol > N) ncol = N;
+
+    auto fail = [&](int code) { sync_all_streams(ctx); return code; };
+    cudaEvent_t e_a0 = evs.make();
+    if (!e_a0) return decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate");
+    DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dA, Kp * 4, hA, lda * 4, K * 4, rows0, cudaMemcpyHostToDevice, up));
+    if (hC) DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dC, Np * 4, hC, ldc * 4, N * 4, rows0, cudaMemcpyHostToDevice, up));
+    DECXB_CUDA_TRY(ctx, cudaEventRecord(e_a0, up));
+    DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(s, e_a0, 0));
+    const float *a0_hi = dA, *a0_lo = nullptr;
+    if (x3) {
+        float *hi = nullptr, *lo = nullptr;
+        if ((rc = scratch.get((size_t)rows0 * Kp * 4, (void**)&hi)) || (rc = scratch.get((size_t)rows0 * Kp * 4, (void**)&lo))) return fail(rc);
+        if ((rc = decxb_launch_split_rows(ctx, dA, rows0, K, Kp, hi, lo, Kp, rows0, s))) return fail(rc);
+        a0_hi = hi; a0_lo = lo;
+    }
+    for (int64_t c0 = 0; c0 < N; c0 += ncol) {
+        const int64_t nc = N - c0 < ncol ? N - c0 : ncol;
+        cudaEvent_t e_up = evs.make(), e_done = evs.make();
+        if (!e_up || !e_done) return fail(decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"));
+        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dB + c0, Np * 4, hB + c0, ldb * 4, nc * 4, K, cudaMemcpyHostToDevice, up));
+        DECXB_CUDA_TRY(ctx, cudaEventRecord(e_up, up));
+        DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(s, e_up, 0));
+        /* columns c0.. of B are rows c0.. of the prepared (K-contiguous) operand */
+        if ((rc = decxb_launch_split_transpose(ctx, dB + c0, K, nc, Np, b_hi + c0 * Kp, x3 ? b_lo + c0 * Kp : nullptr, Kp,
+                                               x3 ? 0 : 1, s))) return fail(rc);
+        decxb_gemm_args g = {};
+        g.M = rows0; g.N = nc; g.K = K;
+        g.a_hi = a0_hi; g.a_lo = a0_lo; g.lda = Kp;
+        g.b_hi = b_hi + c0 * Kp; g.b_lo = x3 ? b_lo + c0 * Kp : nullptr; g.ldb = Kp; g.b_rows = nc;
+        g.C = dC ? dC + c0 : nullptr; g.ldc = Np; g.D = dD + c0; g.ldd = Np;
+        g.tile = tile; g.chunked = strict ? 1 : 0;
+        if ((rc = decxb_launch_gemm_tn(ctx, g, s))) return fail(rc);
+        DECXB_CUDA_TRY(ctx, cudaEventRecord(e_done, s));
+        DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(down, e_done, 0));
+        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(hD + c0, ldd * 4, dD + c0, Np * 4, nc * 4, rows0, cudaMemcpyDeviceToHost, down));
+    }
+    PreparedB pb = {b_hi, b_lo, Kp};
+    for (int64_t r0 = rows0; r0 < M; r0 += rows) {
         const int64_t nr = M - r0 < rows ? M - r0 : rows;
         cudaEvent_t e_up = evs.make(), e_done = evs.make();
-        if (!e_up || !e_done) { sync_all_streams(ctx); return decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"); }
+        if (!e_up || !e_done) return fail(decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"));
         DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dA + r0 * Kp, Kp * 4, hA + r0 * lda, lda * 4, K * 4, nr, cudaMemcpyHostToDevice, up));
         if (hC) DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dC + r0 * Np, Np * 4, hC + r0 * ldc, ldc * 4, N * 4, nr, cudaMemcpyHostToDevice, up));
         DECXB_CUDA_TRY(ctx, cudaEventRecord(e_up, up));
         DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(s, e_up, 0));
         rc = gemm_prepared(ctx, scratch, x3, tile, nr, N, K, dA + r0 * Kp, Kp, pb, dC ? dC + r0 * Np : nullptr, Np,
                            dD + r0 * Np, Np, s, nullptr, DECXB_ACT_NONE, strict);
-        if (rc) { sync_all_streams(ctx); return rc; }
+        if (rc) return fail(rc);
         DECXB_CUDA_TRY(ctx, cudaEventRecord(e_done, s));
         DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(down, e_done, 0));
         DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(hD + r0 * ldd, ldd * 4, dD + r0 * Np, Np * 4, N * 4, nr, cudaMemcpyDeviceToHost, down));

@@ -220,6 +220,29 @@ def test_gemm_host_resident(ctx):
     assert o.norm_err(D, o.gemm_fmaf(A, B, Cin), K, 1.0, 1.0) <= TOL_3X
 
 
+@pytest.mark.parametrize("mode", [b.GEMM_DEFAULT, b.GEMM_3XTF32, b.GEMM_1XTF32])
+@pytest.mark.parametrize("shape", [(3000, 2500, 700), (1100, 4100, 300), (600, 2048, 2100)])
+def test_gemm_host_resident_two_phase_pipeline(ctx, shape, mode):
+    """Host-resident GEMM large enough for both phases of the staging pipeline: a first row-block
+    multiplied with B column block by column block (ragged last block), then further row-blocks
+    with the whole B; pitched host operands, with an addend.  The bits must equal the
+    device-resident entry's."""
+    M, N, K = shape
+    lda, ldb, ldn = K + 8, N + 16, N + 24
+    A = np.zeros((M, lda), dtype=np.float32); A[:, :K] = o.fill_uniform(M * K, 1).reshape(M, K)
+    B = np.zeros((K, ldb), dtype=np.float32); B[:, :N] = o.fill_uniform(K * N, 2).reshape(K, N)
+    Cin = np.zeros((M, ldn), dtype=np.float32); Cin[:, :N] = o.fill_uniform(M * N, 3).reshape(M, N)
+    D = np.full((M, ldn), np.nan, dtype=np.float32)
+    ctx.gemm_host(M, N, K, A, lda, B, ldb, D, ldn, Cin=Cin, ldc=ldn, mode=mode)
+    assert np.isnan(D[:, N:]).all() and not np.isnan(D[:, :N]).any()
+    Dd = run_gemm(ctx, A[:, :K], B[:, :N], Cin[:, :N], mode=mode)
+    assert np.array_equal(D[:, :N], Dd)
+    if mode != b.GEMM_1XTF32:
+        rows = np.r_[0:64, M // 2:M // 2 + 32, M - 40:M]
+        R = o.gemm_fmaf(np.ascontiguousarray(A[rows, :K]), np.ascontiguousarray(B[:, :N]), np.ascontiguousarray(Cin[rows, :N]))
+        assert o.norm_err(D[rows, :N], R, K, 1.0, 1.0) <= TOL_3X
+
+
 def test_gemm_batched_device_and_host(ctx):
     """Batched product over arrays of matrices (de::cuda::GEMM3): 7 matrices through the
     three-slot upload/compute/download ring, with and without addend."""
