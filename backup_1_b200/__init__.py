@@ -29,4 +29,5 @@ from .lib import (  # noqa: F401
     conv_geometry,
     library_path,
     load_library,
+    shard_range,
 )

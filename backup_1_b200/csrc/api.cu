@@ -214,12 +214,21 @@ extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M
     if (N < 2048 || ncol > N) ncol = N;
 
     auto fail = [&](int code) { sync_all_streams(ctx); return code; };
+    /* a failed call inside the pipeline drains the three streams before the scratch goes back */
+#define PIPE_TRY(expr)                                                                              \
+    do {                                                                                           \
+        cudaError_t _e = (expr);                                                                   \
+        if (_e != cudaSuccess) {                                                                   \
+            decxb_set_error(ctx, std::string(#expr) + ": " + cudaGetErrorString(_e));             \
+            return fail(DECXB_ERR_CUDA);                                                           \
+        }                                                                                          \
+    } while (0)
     cudaEvent_t e_a0 = evs.make();
     if (!e_a0) return decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate");
-    DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dA, Kp * 4, hA, lda * 4, K * 4, rows0, cudaMemcpyHostToDevice, up));
-    if (hC) DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dC, Np * 4, hC, ldc * 4, N * 4, rows0, cudaMemcpyHostToDevice, up));
-    DECXB_CUDA_TRY(ctx, cudaEventRecord(e_a0, up));
-    DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(s, e_a0, 0));
+    PIPE_TRY(cudaMemcpy2DAsync(dA, Kp * 4, hA, lda * 4, K * 4, rows0, cudaMemcpyHostToDevice, up));
+    if (hC) PIPE_TRY(cudaMemcpy2DAsync(dC, Np * 4, hC, ldc * 4, N * 4, rows0, cudaMemcpyHostToDevice, up));
+    PIPE_TRY(cudaEventRecord(e_a0, up));
+    PIPE_TRY(cudaStreamWaitEvent(s, e_a0, 0));
     const float *a0_hi = dA, *a0_lo = nullptr;
     if (x3) {
         float *hi = nullptr, *lo = nullptr;
@@ -231,9 +240,9 @@ extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M
         const int64_t nc = N - c0 < ncol ? N - c0 : ncol;
         cudaEvent_t e_up = evs.make(), e_done = evs.make();
         if (!e_up || !e_done) return fail(decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"));
-        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dB + c0, Np * 4, hB + c0, ldb * 4, nc * 4, K, cudaMemcpyHostToDevice, up));
-        DECXB_CUDA_TRY(ctx, cudaEventRecord(e_up, up));
-        DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(s, e_up, 0));
+        PIPE_TRY(cudaMemcpy2DAsync(dB + c0, Np * 4, hB + c0, ldb * 4, nc * 4, K, cudaMemcpyHostToDevice, up));
+        PIPE_TRY(cudaEventRecord(e_up, up));
+        PIPE_TRY(cudaStreamWaitEvent(s, e_up, 0));
         /* columns c0.. of B are rows c0.. of the prepared (K-contiguous) operand */
         if ((rc = decxb_launch_split_transpose(ctx, dB + c0, K, nc, Np, b_hi + c0 * Kp, x3 ? b_lo + c0 * Kp : nullptr, Kp,
                                                x3 ? 0 : 1, s))) return fail(rc);
@@ -244,29 +253,30 @@ extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M
         g.C = dC ? dC + c0 : nullptr; g.ldc = Np; g.D = dD + c0; g.ldd = Np;
         g.tile = tile; g.chunked = strict ? 1 : 0;
         if ((rc = decxb_launch_gemm_tn(ctx, g, s))) return fail(rc);
-        DECXB_CUDA_TRY(ctx, cudaEventRecord(e_done, s));
-        DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(down, e_done, 0));
-        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(hD + c0, ldd * 4, dD + c0, Np * 4, nc * 4, rows0, cudaMemcpyDeviceToHost, down));
+        PIPE_TRY(cudaEventRecord(e_done, s));
+        PIPE_TRY(cudaStreamWaitEvent(down, e_done, 0));
+        PIPE_TRY(cudaMemcpy2DAsync(hD + c0, ldd * 4, dD + c0, Np * 4, nc * 4, rows0, cudaMemcpyDeviceToHost, down));
     }
     PreparedB pb = {b_hi, b_lo, Kp};
     for (int64_t r0 = rows0; r0 < M; r0 += rows) {
         const int64_t nr = M - r0 < rows ? M - r0 : rows;
         cudaEvent_t e_up = evs.make(), e_done = evs.make();
         if (!e_up || !e_done) return fail(decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"));
-        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dA + r0 * Kp, Kp * 4, hA + r0 * lda, lda * 4, K * 4, nr, cudaMemcpyHostToDevice, up));
-        if (hC) DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dC + r0 * Np, Np * 4, hC + r0 * ldc, ldc * 4, N * 4, nr, cudaMemcpyHostToDevice, up));
-        DECXB_CUDA_TRY(ctx, cudaEventRecord(e_up, up));
-        DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(s, e_up, 0));
+        PIPE_TRY(cudaMemcpy2DAsync(dA + r0 * Kp, Kp * 4, hA + r0 * lda, lda * 4, K * 4, nr, cudaMemcpyHostToDevice, up));
+        if (hC) PIPE_TRY(cudaMemcpy2DAsync(dC + r0 * Np, Np * 4, hC + r0 * ldc, ldc * 4, N * 4, nr, cudaMemcpyHostToDevice, up));
+        PIPE_TRY(cudaEventRecord(e_up, up));
+        PIPE_TRY(cudaStreamWaitEvent(s, e_up, 0));
         rc = gemm_prepared(ctx, scratch, x3, tile, nr, N, K, dA + r0 * Kp, Kp, pb, dC ? dC + r0 * Np : nullptr, Np,
                            dD + r0 * Np, Np, s, nullptr, DECXB_ACT_NONE, strict);
         if (rc) return fail(rc);
-        DECXB_CUDA_TRY(ctx, cudaEventRecord(e_done, s));
-        DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(down, e_done, 0));
-        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(hD + r0 * ldd, ldd * 4, dD + r0 * Np, Np * 4, N * 4, nr, cudaMemcpyDeviceToHost, down));
+        PIPE_TRY(cudaEventRecord(e_done, s));
+        PIPE_TRY(cudaStreamWaitEvent(down, e_done, 0));
+        PIPE_TRY(cudaMemcpy2DAsync(hD + r0 * ldd, ldd * 4, dD + r0 * Np, Np * 4, N * 4, nr, cudaMemcpyDeviceToHost, down));
     }
     if ((rc = sync_all_streams(ctx))) return rc;
     scratch.release();
     return decxb_check_dev_status(ctx);
+#undef PIPE_TRY
 }
 
 /* ---- fp16 GEMM ------------------------------------------------------------------------------- */
@@ -684,4 +694,48 @@ extern "C" int decxb_conv2_im2col_f32_host(decxb_ctx* ctx, int mode, int algo, i
     if ((rc = sync_all_streams(ctx))) return rc;
     scratch.release();
     return decxb_check_dev_status(ctx);
+}
+
+/* ---- sharding over ranks ----------------------------------------------------------------------- */
+extern "C" int decxb_shard_range(int64_t total, int world, int rank, int64_t* first, int64_t* last)
+{
+    if (total < 0 || world <= 0 || rank < 0 || rank >= world) return DECXB_ERR_BAD_PARAM;
+    const int64_t base = total / world, extra = total % world;
+    const int64_t f = rank * base + (rank < extra ? rank : extra);
+    if (first) *first = f;
+    if (last) *last = f + base + (rank < extra ? 1 : 0);
+    return DECXB_OK;
+}
+
+extern "C" int decxb_gemm_f32_rowshard(decxb_ctx* ctx, int mode, int tile, int world, int rank,
+                                       int64_t M, int64_t N, int64_t K,
+                                       const float* A_rows, int64_t lda, const float* B, int64_t ldb,
+                                       const float* C_rows, int64_t ldc, float* D_rows, int64_t ldd,
+                                       void* stream, int64_t* first, int64_t* last)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    int64_t f = 0, l = 0;
+    if (decxb_shard_range(M, world, rank, &f, &l)) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "bad world/rank");
+    if (first) *first = f;
+    if (last) *last = l;
+    if (l == f) return DECXB_OK;                 /* more ranks than rows: nothing to do here */
+    return gemm_device(ctx, mode, tile, l - f, N, K, A_rows, lda, B, ldb, false, C_rows, ldc, D_rows, ldd, pick_stream(ctx, stream));
+}
+
+extern "C" int decxb_conv2_im2col_f32_batchshard(decxb_ctx* ctx, int mode, int algo, int flag, int world, int rank,
+                                                 const float* src, int64_t W, int64_t H, int64_t depth,
+                                                 const float* filters, int64_t kW, int64_t kH, int64_t N,
+                                                 float* dst, int64_t batch, int64_t src_stride, int64_t dst_stride,
+                                                 void* stream, int64_t* first, int64_t* last)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    int64_t f = 0, l = 0;
+    if (decxb_shard_range(batch, world, rank, &f, &l)) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "bad world/rank");
+    if (first) *first = f;
+    if (last) *last = l;
+    if (l == f) return DECXB_OK;
+    return conv_device(ctx, mode, algo, flag, src, W, H, depth, filters, kW, kH, N, dst, l - f, src_stride, dst_stride,
+                       pick_stream(ctx, stream));
 }

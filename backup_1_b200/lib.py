@@ -78,6 +78,11 @@ SIGNATURES = {
     "decxb_conv2_im2col_f32": (_i, [_vp, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp]),
     "decxb_conv2_im2col_f32_act": (_i, [_vp, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i, _vp, _i64, _i64, _i64, _vp]),
     "decxb_conv2_im2col_f32_host": (_i, [_vp, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64]),
+    "decxb_shard_range": (_i, [_i64, _i, _i, C.POINTER(_i64), C.POINTER(_i64)]),
+    "decxb_gemm_f32_rowshard": (_i, [_vp, _i, _i, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp,
+                                     C.POINTER(_i64), C.POINTER(_i64)]),
+    "decxb_conv2_im2col_f32_batchshard": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp,
+                                               _i64, _i64, _i64, _vp, C.POINTER(_i64), C.POINTER(_i64)]),
     "decxb_kernel_launch_count": (_u64, [_vp]),
     "decxb_selftest_bounded_wait": (_i, [_vp, _i]),
     "decxb_profile_enable": (_i, [_vp, _i]),
@@ -100,6 +105,15 @@ def load_library() -> C.CDLL:
             fn.restype, fn.argtypes = res, args
         _lib = L
     return _lib
+
+
+def shard_range(total: int, world: int, rank: int) -> tuple[int, int]:
+    """Units [first, last) of `total` that `rank` of `world` owns (the library's partition rule)."""
+    f, l = C.c_int64(0), C.c_int64(0)
+    rc = load_library().decxb_shard_range(total, world, rank, C.byref(f), C.byref(l))
+    if rc:
+        raise DecxbError(rc, "bad world/rank")
+    return f.value, l.value
 
 
 def conv_geometry(W, H, depth, kW, kH, N, flag) -> ConvGeom:
@@ -233,6 +247,24 @@ class Context:
                      src_stride=0, dst_stride=0, mode=GEMM_DEFAULT, algo=CONV_EXPLICIT, stream=None):
         self._chk(self.L.decxb_conv2_im2col_f32(self.h, mode, algo, flag, _ptr(src), W, H, depth, _ptr(filters),
                                                 kW, kH, N, _ptr(dst), batch, src_stride, dst_stride, stream))
+
+    def gemm_rowshard(self, world, rank, M, N, K, A_rows, lda, B, ldb, D_rows, ldd, C_rows=None, ldc=0,
+                      mode=GEMM_DEFAULT, tile=TILE_AUTO, stream=None):
+        """This rank's rows of D = A B (+C); returns the row range [first, last) it computed."""
+        f, l = C.c_int64(0), C.c_int64(0)
+        self._chk(self.L.decxb_gemm_f32_rowshard(self.h, mode, tile, world, rank, M, N, K, _ptr(A_rows), lda, _ptr(B), ldb,
+                                                 _ptr(C_rows), ldc, _ptr(D_rows), ldd, stream, C.byref(f), C.byref(l)))
+        return f.value, l.value
+
+    def conv2_im2col_batchshard(self, world, rank, src, W, H, depth, filters, kW, kH, N, dst, batch,
+                                flag=CONV_ZERO_COMPENSATE, src_stride=0, dst_stride=0, mode=GEMM_DEFAULT,
+                                algo=CONV_IMPLICIT, stream=None):
+        """This rank's images of the batch; src/dst point at its first image.  Returns [first, last)."""
+        f, l = C.c_int64(0), C.c_int64(0)
+        self._chk(self.L.decxb_conv2_im2col_f32_batchshard(self.h, mode, algo, flag, world, rank, _ptr(src), W, H, depth,
+                                                           _ptr(filters), kW, kH, N, _ptr(dst), batch, src_stride,
+                                                           dst_stride, stream, C.byref(f), C.byref(l)))
+        return f.value, l.value
 
     def conv2_im2col_act(self, src, W, H, depth, filters, kW, kH, N, dst, bias=None, act=ACT_NONE,
                          flag=CONV_ZERO_COMPENSATE, batch=1, src_stride=0, dst_stride=0, mode=GEMM_DEFAULT,

@@ -312,6 +312,31 @@ typedef struct decxb_profile {
 DECXB_API int decxb_profile_enable(decxb_ctx* ctx, int on);
 DECXB_API int decxb_profile_read(decxb_ctx* ctx, decxb_profile* out);
 
+/* ---- sharding over ranks (one process per GPU) ---------------------------------------
+ * The reference is single-GPU ("supports only single GPU", DECX_cpu/DECX_CPU.cpp:9); these
+ * entries have no counterpart there.  The path shards into independent units: GEMM by rows of A
+ * and C (B replicated), the convolution by images (filters replicated).  No data crosses
+ * ranks to compute; gathering the result blocks is the caller's collective (the benchmark
+ * uses torch.distributed all-gather over NCCL).
+ *
+ * decxb_shard_range: units [first, last) of `total` owned by `rank` of `world`; contiguous
+ * blocks, the first total % world ranks own one unit more.
+ * decxb_gemm_f32_rowshard: this rank's rows of D = A * B (+C).  A_rows / C_rows / D_rows point
+ * at the rank's own row block (row `first` of the whole matrix), B is the whole matrix.
+ * decxb_conv2_im2col_f32_batchshard: this rank's images; src / dst point at image `first`.
+ * Both report the block they computed through first / last (either may be NULL). */
+DECXB_API int decxb_shard_range(int64_t total, int world, int rank, int64_t* first, int64_t* last);
+DECXB_API int decxb_gemm_f32_rowshard(decxb_ctx* ctx, int mode, int tile, int world, int rank,
+                                      int64_t M, int64_t N, int64_t K,
+                                      const float* A_rows, int64_t lda, const float* B, int64_t ldb,
+                                      const float* C_rows, int64_t ldc, float* D_rows, int64_t ldd,
+                                      void* stream, int64_t* first, int64_t* last);
+DECXB_API int decxb_conv2_im2col_f32_batchshard(decxb_ctx* ctx, int mode, int algo, int flag, int world, int rank,
+                                                const float* src, int64_t W, int64_t H, int64_t depth,
+                                                const float* filters, int64_t kW, int64_t kH, int64_t N,
+                                                float* dst, int64_t batch, int64_t src_stride, int64_t dst_stride,
+                                                void* stream, int64_t* first, int64_t* last);
+
 /* Number of kernels this library has launched on the context since it was created. */
 DECXB_API uint64_t decxb_kernel_launch_count(decxb_ctx* ctx);
 /* Failure-detection self-test: launches one tiny kernel whose only thread waits, with the

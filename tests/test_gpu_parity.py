@@ -587,6 +587,38 @@ def test_conv_config3_full_size(ctx, algo):
     assert o.norm_err(D[rows], R, P.shape[1], 1.0, 1.0) <= TOL_3X
 
 
+def test_rank_shards_assemble_the_unsharded_result(ctx):
+    """decxb_gemm_f32_rowshard / decxb_conv2_im2col_f32_batchshard: the shards of 3 ranks (run one
+    after the other on this GPU, each on its own block) assemble, bit for bit, the result of the
+    unsharded call; a rank beyond the number of units has nothing to do."""
+    M, N, K, world = 1000, 264, 200, 3
+    A = o.fill_uniform(M * K, 1).reshape(M, K); B = o.fill_uniform(K * N, 2).reshape(K, N)
+    Cin = o.fill_uniform(M * N, 3).reshape(M, N)
+    dA, dB, dC = dev(A), dev(B), dev(Cin)
+    dD = torch.full((M, N), float("nan"), device=DEV)
+    spans = []
+    for r in range(world):
+        f, l = b.shard_range(M, world, r)
+        got = ctx.gemm_rowshard(world, r, M, N, K, dA[f:], K, dB, N, dD[f:], N, C_rows=dC[f:], ldc=N)
+        assert got == (f, l)
+        spans.append(got)
+    ctx.synchronize()
+    assert spans[0][0] == 0 and spans[-1][1] == M
+    assert np.array_equal(dD.cpu().numpy(), run_gemm(ctx, A, B, Cin))
+    assert ctx.gemm_rowshard(8, 7, 5, N, K, dA, K, dB, N, dD, N) == (5, 5)
+    W, H, Cc, kW, F, nb = 20, 12, 8, 3, 16, 5
+    src = np.stack([o.make_tensor(W, H, Cc, 40 + i) for i in range(nb)])
+    flt = o.make_filters(kW, kW, Cc, F, 5)
+    full = run_conv(ctx, src, W, Cc, flt, kW, 1, algo=b.CONV_IMPLICIT)
+    dS, dF = dev(src), dev(flt)
+    out = torch.full(full.shape, float("nan"), device=DEV)
+    for r in range(2):
+        f, l = b.shard_range(nb, 2, r)
+        assert ctx.conv2_im2col_batchshard(2, r, dS[f:], W, H, Cc, dF, kW, kW, F, out[f:], nb) == (f, l)
+    ctx.synchronize()
+    assert np.array_equal(out.cpu().numpy(), full)
+
+
 def test_bounded_wait_expires_and_context_survives(ctx):
     """Failure detection without a fault: a wait on a barrier nothing signals gives up after
     its limit, the host reads DECXB_ERR_TIMEOUT, and the next GEMM on the same context is fine."""

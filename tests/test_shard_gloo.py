@@ -25,6 +25,22 @@ def test_block_range_partitions_exactly():
     assert shard.conv_batch_shard(256, 8, 7) == (224, 256)
 
 
+def test_library_partition_rule_equals_the_python_one():
+    """The C-ABI rule (decxb_shard_range, what a non-Python host binds) and shard.block_range
+    must be the same function."""
+    import backup_1_b200 as b
+    for total in (0, 1, 5, 7, 255, 256, 257, 8192, 32768, 10 ** 12 + 7):
+        for world in (1, 2, 3, 4, 5, 8, 16):
+            for rank in range(world):
+                assert b.shard_range(total, world, rank) == shard.block_range(total, world, rank)
+    for bad in ((10, 0, 0), (10, 2, 2), (10, 2, -1), (-1, 2, 0)):
+        try:
+            b.shard_range(*bad)
+        except b.DecxbError:
+            continue
+        raise AssertionError(f"{bad} accepted")
+
+
 def _worker(rank, world, port, q):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
