@@ -13,9 +13,10 @@
  *  - tcgen05.mma kind::tf32, accumulators in tensor memory (TMEM), fp32.  3xTF32 issues
  *    a_lo*b_hi, a_hi*b_lo, a_hi*b_hi into the same accumulator for every k-step of 8.
  *  - Warp-specialised, persistent: warp 0 = TMA producer, warp 1 = MMA issuer (and TMEM
- *    owner), warps 2..5 = epilogue (tcgen05.ld -> registers -> 128-bit global stores).  The
- *    accumulator is double-buffered in TMEM so the epilogue of tile i overlaps the main loop
- *    of tile i+1.
+ *    owner), warps 2..5 = epilogue (tcgen05.ld -> registers -> a swizzled 32 x 32 box in shared
+ *    memory -> one TMA store per box; 128-bit stores from the threads for layouts the copy
+ *    engine cannot describe).  The accumulator is double-buffered in TMEM so the epilogue of
+ *    tile i overlaps the main loop of tile i+1.
  *  - CTAS = 2 pairs two CTAs (one thread-block cluster) on a 256 x (2*BN) tile with
  *    cta_group::2: each CTA loads its own 128 rows of A and its own half of B, the leader
  *    CTA issues the MMAs for both, completion is signalled to both CTAs with one commit.
@@ -37,10 +38,11 @@ constexpr int UMMA_K = 8;          /* k per tcgen05.mma kind::tf32              
 constexpr int NUM_THREADS = 192;   /* 6 warps: producer, MMA issuer, 4 epilogue warps        */
 constexpr int NUM_THREADS_CHUNKED = 384;   /* chunked accumulation: warp group 0 = producer, MMA issuer
                                               and two idle warps; warp groups 1, 2 = 8 epilogue warps */
-constexpr int KCHUNK = 4;          /* k-blocks per chunk of the chunked accumulation: 128 values of K.
+constexpr int KCHUNK = 4;          /* k-blocks per chunk of the chunked accumulation: 128 values of K
+                                      (256 for the first two chunks of a tile, see chunk_blocks).
                                       Largest error seen on the all-positive 2048^3 case, relative to
-                                      K max|a| max|b|: 64 -> 1.9e-7, 128 -> 3.3e-7, 256 -> 6.5e-7,
-                                      512 -> 1.2e-6, whole K -> 2.9e-6 */
+                                      K max|a| max|b|, with uniform chunks of 64 -> 1.9e-7,
+                                      128 -> 3.3e-7, 256 -> 6.5e-7, 512 -> 1.2e-6, whole K -> 2.9e-6 */
 constexpr int SMEM_LIMIT = 232448; /* 227 KiB opt-in maximum per CTA                        */
 
 /* ---------------------------------------------------------------- PTX wrappers ------ */
@@ -129,6 +131,26 @@ __device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap
     asm volatile(
         "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
         :: "r"(dst), "l"(map), "r"(bar_cluster_addr), "r"(c), "r"(x), "r"(y), "r"(n) : "memory");
+}
+
+/* Tiled TMA store of a 32 x 32 fp32 box from this CTA's shared memory (bulk async-group). */
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 :: "l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+/* every bulk store of this thread has finished READING shared memory (the staging buffer may be rewritten) */
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+/* every bulk store of this thread is complete */
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+/* generic-proxy writes to shared memory become visible to the async proxy (TMA) */
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+/* Brings a tensor map into the copy engine's descriptor cache ahead of its first use. */
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map)
+{
+    asm volatile("prefetch.tensormap [%0];" :: "l"(map) : "memory");
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -269,6 +291,7 @@ struct GemmParams {
     /* fused epilogue: D = act(acc (+C) (+bias[col])) */
     const float* bias;          /* per output column (filter), or NULL                            */
     int act;                    /* DECXB_ACT_*                                                    */
+    int tma_store;              /* 1 = results leave through shared memory and TMA stores (map_d)   */
 };
 
 /* Activations with the reference's formulas (srcs/nn/operators/ReLU.h:48-75 keeps x when its
@@ -340,6 +363,65 @@ __device__ __forceinline__ void store32_f32(const float* v, int64_t col_first, c
     }
 }
 
+/* The same 32 columns for the 32 rows of a warp at once, through the warp's 4 KiB staging box
+ * and one TMA store: lane r writes its row into the box (16-byte pieces XOR-swizzled by the row,
+ * the 128-byte swizzle the tensor map describes, so the four-way minimum of bank conflicts),
+ * lane 0 hands the box to the copy engine, which writes 32 full 128-byte row segments and
+ * clips what lies beyond M or N.  Against per-thread stores (32 rows per instruction, 16 bytes
+ * each) this takes the result traffic off the load/store path that the tensor core's operand
+ * reads keep busy. */
+__device__ __forceinline__ void store32_tma(const float* v, int64_t col_first, int64_t row_first, bool row_ok,
+                                            const GemmParams& p, const float* __restrict__ crow, bool c_vec,
+                                            uint32_t stg, const CUtensorMap* map, int lane)
+{
+    if (lane == 0) tma_store_wait_read();        /* the previous box of this warp has been read */
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+        const int64_t col = col_first + j;
+        float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        if (crow && row_ok) {
+            if (c_vec && col + 3 < p.N) {
+                const float4 ci = __ldg(reinterpret_cast<const float4*>(crow + col));
+                o.x += ci.x; o.y += ci.y; o.z += ci.z; o.w += ci.w;
+            } else {
+                if (col < p.N) o.x += __ldg(crow + col);
+                if (col + 1 < p.N) o.y += __ldg(crow + col + 1);
+                if (col + 2 < p.N) o.z += __ldg(crow + col + 2);
+                if (col + 3 < p.N) o.w += __ldg(crow + col + 3);
+            }
+        }
+        if (p.bias) {
+            if (col < p.N) o.x += __ldg(p.bias + col);
+            if (col + 1 < p.N) o.y += __ldg(p.bias + col + 1);
+            if (col + 2 < p.N) o.z += __ldg(p.bias + col + 2);
+            if (col + 3 < p.N) o.w += __ldg(p.bias + col + 3);
+        }
+        if (p.act) {
+            o.x = apply_act(o.x, p.act); o.y = apply_act(o.y, p.act);
+            o.z = apply_act(o.z, p.act); o.w = apply_act(o.w, p.act);
+        }
+        const uint32_t dst = stg + (uint32_t)lane * 128u + ((uint32_t)((j >> 2) ^ (lane & 7)) << 4);
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" :: "r"(dst), "f"(o.x), "f"(o.y), "f"(o.z), "f"(o.w) : "memory");
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+        tma_store_2d(map, stg, (int)col_first, (int)row_first);
+        tma_store_commit();
+    }
+}
+
+/* k-blocks of the chunk that starts at k-block kb0 (chunked accumulation).  The first two chunks
+ * of a tile are twice as long as the rest: while the epilogue warps still write the previous
+ * tile's result they cannot take chunks, and the tensor core can only work two chunks (the two
+ * TMEM buffers) into the next tile before it has to wait for them. */
+template <int KCH>
+__device__ __forceinline__ int chunk_blocks(int kb0)
+{
+    return kb0 < 4 * KCH ? 2 * KCH : KCH;
+}
+
 /* Tile order: groups of 8 tile-rows, column by column inside a group, so that the CTAs
  * running at the same time share A row-panels and B column-panels in L2. */
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn)
@@ -367,20 +449,23 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
  *          on the next chunk in the other buffer.  (The tensor core's own accumulator rounds
  *          toward zero, which biases long sums of same-sign products; short chunks bound it.)
  * ------------------------------------------------------------------------------------ */
-template <int CTAS, int BN, int NSPLIT>
+template <int CTAS, int BN, int NSPLIT, int KCH = 0>
 struct Cfg {
     static constexpr int PARTS = NSPLIT == 3 ? 2 : 1;
+    static constexpr int EPI_WARPS = KCH ? 8 : 4;
+    /* one 32 x 32 fp32 box (4 KiB, 128-byte swizzled) per epilogue warp for the TMA result stores */
+    static constexpr int STAGING = NSPLIT == 16 ? 0 : EPI_WARPS * 4096;
     static constexpr int UMMA_M = BM_CTA * CTAS;
     static constexpr int UMMA_N = BN * CTAS;
     static constexpr int A_BYTES = BM_CTA * BK * 4;            /* 16 KiB */
     static constexpr int B_BYTES = BN * BK * 4;
     static constexpr int STAGE_BYTES = PARTS * (A_BYTES + B_BYTES);
-    static constexpr int STAGES_RAW = (SMEM_LIMIT - 2048) / STAGE_BYTES;
+    static constexpr int STAGES_RAW = (SMEM_LIMIT - 2048 - STAGING) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int TMEM_COLS_RAW = 2 * UMMA_N;
     static constexpr int TMEM_COLS = TMEM_COLS_RAW <= 32 ? 32 : TMEM_COLS_RAW <= 64 ? 64 : TMEM_COLS_RAW <= 128 ? 128
                                    : TMEM_COLS_RAW <= 256 ? 256 : 512;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING + 1024 /* alignment slack */ + 256 /* barriers */;
     static_assert(STAGES >= 2, "need at least two stages");
     static_assert(UMMA_N % 16 == 0 && UMMA_N >= 16 && UMMA_N <= 256, "UMMA N");
     static_assert(TMEM_COLS_RAW <= 512, "two accumulators must fit in TMEM");
@@ -390,13 +475,14 @@ template <int CTAS, int BN, int NSPLIT, bool CONV, int KCH>
 __global__ void __launch_bounds__(KCH ? NUM_THREADS_CHUNKED : NUM_THREADS, 1)
 decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                        const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
-                       const GemmParams p)
+                       const __grid_constant__ CUtensorMap map_d, const GemmParams p)
 {
-    using C = Cfg<CTAS, BN, NSPLIT>;
+    using C = Cfg<CTAS, BN, NSPLIT, KCH>;
     extern __shared__ uint8_t smem_raw[];
     /* 1024-byte alignment: the 128-byte swizzle pattern is a function of address bits 4-9. */
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bars = smem_base + C::STAGES * C::STAGE_BYTES;
+    const uint32_t staging = smem_base + C::STAGES * C::STAGE_BYTES;      /* 1024-byte aligned */
+    const uint32_t bars = staging + C::STAGING;
     auto full_bar   = [&](int s) { return bars + 8u * s; };
     auto empty_bar  = [&](int s) { return bars + 8u * (C::STAGES + s); };
     auto tfull_bar  = [&](int b) { return bars + 8u * (2 * C::STAGES + b); };
@@ -413,6 +499,9 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
     const int num_tiles = p.tiles_m * p.tiles_n;
 
     if (threadIdx.x == 0) {
+        prefetch_tensormap(&map_a_hi); prefetch_tensormap(&map_b_hi);
+        if (NSPLIT == 3) { prefetch_tensormap(&map_a_lo); prefetch_tensormap(&map_b_lo); }
+        if (p.tma_store) prefetch_tensormap(&map_d);
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), (KCH ? 8 : 4) * CTAS); }
         fence_barrier_init();
@@ -497,9 +586,9 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
             int stage = 0; uint32_t phase = 0;
             int unit = 0;              /* accumulation units so far: tiles, or (tile, chunk) pairs */
             bool alive = true;
-            const int per_unit = KCH ? KCH : p.num_kb;
             for (int t = cluster_id; t < num_tiles && alive; t += num_clusters) {
-                for (int kb0 = 0; kb0 < p.num_kb && alive; kb0 += per_unit, ++unit) {
+                for (int kb0 = 0, per_unit; kb0 < p.num_kb && alive; kb0 += per_unit, ++unit) {
+                    per_unit = KCH ? chunk_blocks<KCH ? KCH : 1>(kb0) : p.num_kb;
                     const int acc = unit & 1;
                     const uint32_t acc_phase = (uint32_t)(unit >> 1) & 1u;
                     if (!wait_bounded(tempty_bar(acc), acc_phase ^ 1u, p, 200 + acc, t)) { alive = false; break; }
@@ -546,6 +635,7 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
         int unit = 0;                             /* same count as the MMA issuer's */
         bool alive = true;
         const int eh = KCH ? (warp - 4) >> 2 : 0; /* chunked: column half this warp sums */
+        const uint32_t stg = staging + (uint32_t)(KCH ? warp - 4 : warp - 2) * 4096u;   /* this warp's TMA store box */
         for (int t = cluster_id; t < num_tiles && alive; t += num_clusters) {
             int tm, tn; tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
             const int bidx = (!CONV && p.tiles_m_per) ? tm / p.tiles_m_per : 0;
@@ -567,6 +657,7 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
             }
             const float* __restrict__ crow = (p.C && !CONV) ? p.C + bidx * p.c_batch_stride + row * p.ldc : nullptr;
             const bool vec = d_vec && (!crow || c_vec);
+            const int64_t row_first = row - lane;     /* first of the warp's 32 rows (TMA store path: plain GEMM only) */
             if constexpr (KCH > 0) {
                 /* chunked accumulation: this warp owns NCW columns of its 32 rows */
                 constexpr int NCW = C::UMMA_N / 2;
@@ -575,7 +666,7 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
                 float sum[NCW];
 #pragma unroll
                 for (int c = 0; c < NCW; ++c) sum[c] = 0.0f;
-                for (int kb0 = 0; kb0 < p.num_kb; kb0 += KCH, ++unit) {
+                for (int kb0 = 0; kb0 < p.num_kb; kb0 += chunk_blocks<KCH>(kb0), ++unit) {
                     const int acc = unit & 1;
                     const uint32_t acc_phase = (uint32_t)(unit >> 1) & 1u;
                     if (!wait_bounded(tfull_bar(acc), acc_phase, p, 400 + acc, t)) { alive = false; break; }
@@ -600,7 +691,12 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
                     }
                 }
                 if (!alive) break;
-                if (row_ok) {
+                if (p.tma_store) {
+#pragma unroll
+                    for (int c = 0; c < NCW; c += 32)
+                        if (col0 + eh * NCW + c < p.N)
+                            store32_tma(sum + c, col0 + eh * NCW + c, row_first, row_ok, p, crow, c_vec, stg, &map_d, lane);
+                } else if (row_ok) {
 #pragma unroll
                     for (int c = 0; c < NCW; c += 32) {
                         if (col0 + eh * NCW + c < p.N) store32_f32(sum + c, col0 + eh * NCW + c, p, drow, crow, vec);
@@ -648,6 +744,8 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
                             }
                         }
                     }
+                } else if (p.tma_store) {
+                    store32_tma(v, col0 + c, row_first, row_ok, p, crow, c_vec, stg, &map_d, lane);
                 } else if (row_ok) {
                     store32_f32(v, col0 + c, p, drow, crow, vec);
                 }
@@ -661,6 +759,7 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
             }
             }   /* whole-K accumulation */
         }
+        if (p.tma_store && lane == 0) tma_store_wait_all();   /* the boxes stay valid until the copy engine is done */
     }
 
     /* ---------------------------------------------------------------- teardown -------- */
@@ -759,9 +858,9 @@ int make_map_conv(decxb_ctx* ctx, CUtensorMap* map, const float* base, int64_t d
 
 template <int CTAS, int BN, int NSPLIT, bool CONV, int KCH = 0>
 int launch_kernel(decxb_ctx* ctx, const CUtensorMap& ma_hi, const CUtensorMap& ma_lo, const CUtensorMap& mb_hi,
-                  const CUtensorMap& mb_lo, const GemmParams& p, cudaStream_t s)
+                  const CUtensorMap& mb_lo, const CUtensorMap& md, const GemmParams& p, cudaStream_t s)
 {
-    using C = Cfg<CTAS, BN, NSPLIT>;
+    using C = Cfg<CTAS, BN, NSPLIT, KCH>;
     auto kernel = decxb_gemm_tf32_kernel<CTAS, BN, NSPLIT, CONV, KCH>;
     static std::once_flag once[16];
     static cudaError_t attr_err[16];
@@ -797,7 +896,7 @@ int launch_kernel(decxb_ctx* ctx, const CUtensorMap& ma_hi, const CUtensorMap& m
     cfg.attrs = attr; cfg.numAttrs = 1;
     {
         decxb_launch_scope scope(ctx, s, DECXB_K_GEMM);
-        DECXB_CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kernel, ma_hi, ma_lo, mb_hi, mb_lo, p));
+        DECXB_CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kernel, ma_hi, ma_lo, mb_hi, mb_lo, md, p));
     }
     return DECXB_OK;
 }
@@ -841,7 +940,7 @@ int launch_conv_cfg(decxb_ctx* ctx, const decxb_conv_gemm_args& a, cudaStream_t 
     p.num_kb = (int)(a.kW * a.kH * cblocks);
     p.wait_limit_ns = ctx->wait_limit_ns;
     p.status = ctx->d_status;
-    return launch_kernel<CTAS, BN, NSPLIT, true, KCH>(ctx, ma_hi, ma_lo, mb_hi, mb_lo, p, s);
+    return launch_kernel<CTAS, BN, NSPLIT, true, KCH>(ctx, ma_hi, ma_lo, mb_hi, mb_lo, ma_hi /* unused */, p, s);
 }
 
 template <int CTAS, int BN, int NSPLIT, int KCH = 0>
@@ -876,7 +975,14 @@ int launch_cfg(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s)
     p.num_kb = (int)decxb_ceil_div(a.K, BK);
     p.wait_limit_ns = ctx->wait_limit_ns;
     p.status = ctx->d_status;
-    return launch_kernel<CTAS, BN, NSPLIT, false, KCH>(ctx, ma_hi, ma_lo, mb_hi, mb_lo, p, s);
+    /* results through TMA stores when the result array can be described to the copy engine
+     * (16-byte aligned base and pitch); batched launches and odd layouts store from the threads */
+    CUtensorMap md = ma_hi;
+    if (a.nbatch <= 1 && (reinterpret_cast<uintptr_t>(a.D) & 15) == 0 && a.ldd % 4 == 0) {
+        if ((rc = make_map(ctx, &md, a.D, a.M, a.N, a.ldd, 32))) return rc;
+        p.tma_store = 1;
+    }
+    return launch_kernel<CTAS, BN, NSPLIT, false, KCH>(ctx, ma_hi, ma_lo, mb_hi, mb_lo, md, p, s);
 }
 
 
@@ -898,7 +1004,7 @@ int launch_cfg_f16(decxb_ctx* ctx, const decxb_gemm_f16_args& a, cudaStream_t s)
     p.num_kb = (int)decxb_ceil_div(a.K, 64);
     p.wait_limit_ns = ctx->wait_limit_ns;
     p.status = ctx->d_status;
-    return launch_kernel<CTAS, BN, 16, false>(ctx, ma, ma, mb, mb, p, s);
+    return launch_kernel<CTAS, BN, 16, false>(ctx, ma, ma, mb, mb, ma /* unused */, p, s);
 }
 
 }  // namespace
