@@ -139,6 +139,12 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                  :: "l"(map), "r"(src), "r"(x), "r"(y) : "memory");
 }
+/* The same box as a slice of a 4-D tensor (channel, x, y, image): 32 channels of bx_s x by_s pixels. */
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c, int x, int y, int n)
+{
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 :: "l"(map), "r"(src), "r"(c), "r"(x), "r"(y), "r"(n) : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 /* every bulk store of this thread has finished READING shared memory (the staging buffer may be rewritten) */
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
@@ -370,9 +376,11 @@ __device__ __forceinline__ void store32_f32(const float* v, int64_t col_first, c
  * clips what lies beyond M or N.  Against per-thread stores (32 rows per instruction, 16 bytes
  * each) this takes the result traffic off the load/store path that the tensor core's operand
  * reads keep busy. */
+template <bool CONV>
 __device__ __forceinline__ void store32_tma(const float* v, int64_t col_first, int64_t row_first, bool row_ok,
                                             const GemmParams& p, const float* __restrict__ crow, bool c_vec,
-                                            uint32_t stg, const CUtensorMap* map, int lane)
+                                            uint32_t stg, const CUtensorMap* map, int lane,
+                                            int box_x = 0, int box_y = 0, int box_img = 0)
 {
     if (lane == 0) tma_store_wait_read();        /* the previous box of this warp has been read */
     __syncwarp();
@@ -407,7 +415,9 @@ __device__ __forceinline__ void store32_tma(const float* v, int64_t col_first, i
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) {
-        tma_store_2d(map, stg, (int)col_first, (int)row_first);
+        /* convolution: the warp's 32 tile rows are the pixels (box_x.., box_y..) of one image, x fastest */
+        if (CONV) tma_store_4d(map, stg, (int)col_first, box_x, box_y, box_img);
+        else      tma_store_2d(map, stg, (int)col_first, (int)row_first);
         tma_store_commit();
     }
 }
@@ -644,16 +654,19 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
             const int64_t col0 = (int64_t)tn * C::UMMA_N;
             const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16);
             float* __restrict__ drow = p.D + bidx * p.d_batch_stride + row * p.ldd;
+            int box_x = 0, box_y = 0, box_img = 0;    /* convolution: first pixel of the warp's 32 tile rows */
             if (CONV) {
                 /* tile row i is pixel (px0 + i % bx, py0 + i / bx) of image img */
                 const int per_img = p.tiles_x * p.tiles_y;
                 const int img = tm / per_img;
                 const int r = tm - img * per_img;
                 const int i = q * 32 + lane;
-                const int y = ((r / p.tiles_x) * CTAS + (int)cta_rank) * p.by + i / p.bx;
-                const int x = (r % p.tiles_x) * p.bx + i % p.bx;
+                const int py0 = ((r / p.tiles_x) * CTAS + (int)cta_rank) * p.by, px0 = (r % p.tiles_x) * p.bx;
+                const int y = py0 + i / p.bx;
+                const int x = px0 + i % p.bx;
                 row_ok = (x < p.eq_w) && (y < p.out_h);
                 drow = p.D + (int64_t)img * p.dst_img_stride + ((int64_t)y * p.eq_w + x) * p.ldd;
+                box_x = px0 + (q * 32) % p.bx; box_y = py0 + (q * 32) / p.bx; box_img = img;
             }
             const float* __restrict__ crow = (p.C && !CONV) ? p.C + bidx * p.c_batch_stride + row * p.ldc : nullptr;
             const bool vec = d_vec && (!crow || c_vec);
@@ -695,7 +708,8 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
 #pragma unroll
                     for (int c = 0; c < NCW; c += 32)
                         if (col0 + eh * NCW + c < p.N)
-                            store32_tma(sum + c, col0 + eh * NCW + c, row_first, row_ok, p, crow, c_vec, stg, &map_d, lane);
+                            store32_tma<CONV>(sum + c, col0 + eh * NCW + c, row_first, row_ok, p, crow, c_vec, stg, &map_d, lane,
+                                              box_x, box_y, box_img);
                 } else if (row_ok) {
 #pragma unroll
                     for (int c = 0; c < NCW; c += 32) {
@@ -745,7 +759,7 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
                         }
                     }
                 } else if (p.tma_store) {
-                    store32_tma(v, col0 + c, row_first, row_ok, p, crow, c_vec, stg, &map_d, lane);
+                    store32_tma<CONV>(v, col0 + c, row_first, row_ok, p, crow, c_vec, stg, &map_d, lane, box_x, box_y, box_img);
                 } else if (row_ok) {
                     store32_f32(v, col0 + c, p, drow, crow, vec);
                 }
@@ -856,6 +870,25 @@ int make_map_conv(decxb_ctx* ctx, CUtensorMap* map, const float* base, int64_t d
     return DECXB_OK;
 }
 
+/* Destination tensor [nb][out_h][eq_w][Np] as a 4-D map (channel, x, y, image) for the result
+ * stores; box = 32 channels x (bx_s x by_s = 32 pixels) x 1 image, 128-byte swizzle. */
+int make_map_conv_dst(decxb_ctx* ctx, CUtensorMap* map, const float* base, int64_t Np, int64_t eq_w, int64_t out_h, int64_t nb,
+                      int64_t img_stride, int bx)
+{
+    auto fn = get_encode_fn();
+    if (!fn) return decxb_fail(ctx, DECXB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
+    const int bxs = bx < 32 ? bx : 32;
+    cuuint64_t dims[4] = {(cuuint64_t)Np, (cuuint64_t)eq_w, (cuuint64_t)out_h, (cuuint64_t)nb};
+    cuuint64_t strides[3] = {(cuuint64_t)Np * 4, (cuuint64_t)eq_w * Np * 4, (cuuint64_t)img_stride * 4};
+    cuuint32_t box[4] = {32, (cuuint32_t)bxs, (cuuint32_t)(32 / bxs), 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return decxb_fail(ctx, DECXB_ERR_CUDA, "cuTensorMapEncodeTiled (4-D result) failed: " + std::to_string((int)r));
+    return DECXB_OK;
+}
+
 template <int CTAS, int BN, int NSPLIT, bool CONV, int KCH = 0>
 int launch_kernel(decxb_ctx* ctx, const CUtensorMap& ma_hi, const CUtensorMap& ma_lo, const CUtensorMap& mb_hi,
                   const CUtensorMap& mb_lo, const CUtensorMap& md, const GemmParams& p, cudaStream_t s)
@@ -940,7 +973,13 @@ int launch_conv_cfg(decxb_ctx* ctx, const decxb_conv_gemm_args& a, cudaStream_t 
     p.num_kb = (int)(a.kW * a.kH * cblocks);
     p.wait_limit_ns = ctx->wait_limit_ns;
     p.status = ctx->d_status;
-    return launch_kernel<CTAS, BN, NSPLIT, true, KCH>(ctx, ma_hi, ma_lo, mb_hi, mb_lo, ma_hi /* unused */, p, s);
+    /* result stores through the copy engine when the destination can be described to it */
+    CUtensorMap md = ma_hi;
+    if ((reinterpret_cast<uintptr_t>(a.dst) & 15) == 0 && a.Np % 4 == 0 && a.dst_img_stride % 4 == 0) {
+        if ((rc = make_map_conv_dst(ctx, &md, a.dst, a.Np, a.eq_w, a.out_h, a.batch, a.dst_img_stride, bx))) return rc;
+        p.tma_store = 1;
+    }
+    return launch_kernel<CTAS, BN, NSPLIT, true, KCH>(ctx, ma_hi, ma_lo, mb_hi, mb_lo, md, p, s);
 }
 
 template <int CTAS, int BN, int NSPLIT, int KCH = 0>

@@ -232,7 +232,8 @@ DECXB_API int decxb_gemm_f32_batched_host(decxb_ctx* ctx, int mode, int tile, in
  *    complete.  Calls that would overlap on the GPU (from several threads or streams) race on
  *    the array: issue them one after another.
  *  - A, B, C, D are device pointers; `stream` is a cudaStream_t (NULL = default stream);
- *    `err` (optional, err_len bytes) receives a message when the status is not DECXB_OK. */
+ *    `err` (optional, err_len bytes) receives a message when the status is not DECXB_OK.
+ *  - Arithmetic: the DECXB_GEMM_3XTF32 mode (the tensor core accumulates over all of K). */
 DECXB_API int decxb_gemm_f32_noalloc(int device, int64_t M, int64_t N, int64_t K,
                                      const float* A, int64_t lda, const float* B, int64_t ldb,
                                      const float* C, int64_t ldc, float* D, int64_t ldd,
