@@ -147,7 +147,12 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t sr
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 /* every bulk store of this thread has finished READING shared memory (the staging buffer may be rewritten) */
-__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+template <int PENDING>
+__device__ __forceinline__ void tma_store_wait_read()
+{
+    if (PENDING == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    else              asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+}
 /* every bulk store of this thread is complete */
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 /* generic-proxy writes to shared memory become visible to the async proxy (TMA) */
@@ -376,14 +381,17 @@ __device__ __forceinline__ void store32_f32(const float* v, int64_t col_first, c
  * clips what lies beyond M or N.  Against per-thread stores (32 rows per instruction, 16 bytes
  * each) this takes the result traffic off the load/store path that the tensor core's operand
  * reads keep busy. */
-template <bool CONV>
+template <bool CONV, int BOXES>
 __device__ __forceinline__ void store32_tma(const float* v, int64_t col_first, int64_t row_first, bool row_ok,
                                             const GemmParams& p, const float* __restrict__ crow, bool c_vec,
-                                            uint32_t stg, const CUtensorMap* map, int lane,
+                                            uint32_t stg0, uint32_t& box_turn, const CUtensorMap* map, int lane,
                                             int box_x = 0, int box_y = 0, int box_img = 0)
 {
-    if (lane == 0) tma_store_wait_read();        /* the previous box of this warp has been read */
+    /* with two boxes the store issued before the last one must have been read: its box is reused now */
+    if (lane == 0) tma_store_wait_read<BOXES - 1>();
     __syncwarp();
+    const uint32_t stg = stg0 + (BOXES == 2 ? (box_turn & 1u) * 4096u : 0u);
+    ++box_turn;
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
         const int64_t col = col_first + j;
@@ -464,14 +472,17 @@ struct Cfg {
     static constexpr int PARTS = NSPLIT == 3 ? 2 : 1;
     static constexpr int EPI_WARPS = KCH ? 8 : 4;
     /* one 32 x 32 fp32 box (4 KiB, 128-byte swizzled) per epilogue warp for the TMA result stores */
-    static constexpr int STAGING = NSPLIT == 16 ? 0 : EPI_WARPS * 4096;
+    static constexpr int STAGING1 = NSPLIT == 16 ? 0 : EPI_WARPS * 4096;
     static constexpr int UMMA_M = BM_CTA * CTAS;
     static constexpr int UMMA_N = BN * CTAS;
     static constexpr int A_BYTES = BM_CTA * BK * 4;            /* 16 KiB */
     static constexpr int B_BYTES = BN * BK * 4;
     static constexpr int STAGE_BYTES = PARTS * (A_BYTES + B_BYTES);
-    static constexpr int STAGES_RAW = (SMEM_LIMIT - 2048 - STAGING) / STAGE_BYTES;
+    static constexpr int STAGES_RAW = (SMEM_LIMIT - 2048 - STAGING1) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+    /* a second box per warp (two result stores in flight) where it fits beside the stages */
+    static constexpr int BOXES = (NSPLIT != 16 && SMEM_LIMIT - 2048 - STAGES * STAGE_BYTES >= 2 * STAGING1) ? 2 : 1;
+    static constexpr int STAGING = STAGING1 * BOXES;
     static constexpr int TMEM_COLS_RAW = 2 * UMMA_N;
     static constexpr int TMEM_COLS = TMEM_COLS_RAW <= 32 ? 32 : TMEM_COLS_RAW <= 64 ? 64 : TMEM_COLS_RAW <= 128 ? 128
                                    : TMEM_COLS_RAW <= 256 ? 256 : 512;
@@ -645,7 +656,8 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
         int unit = 0;                             /* same count as the MMA issuer's */
         bool alive = true;
         const int eh = KCH ? (warp - 4) >> 2 : 0; /* chunked: column half this warp sums */
-        const uint32_t stg = staging + (uint32_t)(KCH ? warp - 4 : warp - 2) * 4096u;   /* this warp's TMA store box */
+        const uint32_t stg = staging + (uint32_t)(KCH ? warp - 4 : warp - 2) * (4096u * C::BOXES);   /* this warp's TMA store box(es) */
+        uint32_t box_turn = 0;
         for (int t = cluster_id; t < num_tiles && alive; t += num_clusters) {
             int tm, tn; tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
             const int bidx = (!CONV && p.tiles_m_per) ? tm / p.tiles_m_per : 0;
@@ -708,8 +720,8 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
 #pragma unroll
                     for (int c = 0; c < NCW; c += 32)
                         if (col0 + eh * NCW + c < p.N)
-                            store32_tma<CONV>(sum + c, col0 + eh * NCW + c, row_first, row_ok, p, crow, c_vec, stg, &map_d, lane,
-                                              box_x, box_y, box_img);
+                            store32_tma<CONV, C::BOXES>(sum + c, col0 + eh * NCW + c, row_first, row_ok, p, crow, c_vec, stg, box_turn,
+                                                        &map_d, lane, box_x, box_y, box_img);
                 } else if (row_ok) {
 #pragma unroll
                     for (int c = 0; c < NCW; c += 32) {
@@ -759,7 +771,8 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
                         }
                     }
                 } else if (p.tma_store) {
-                    store32_tma<CONV>(v, col0 + c, row_first, row_ok, p, crow, c_vec, stg, &map_d, lane, box_x, box_y, box_img);
+                    store32_tma<CONV, C::BOXES>(v, col0 + c, row_first, row_ok, p, crow, c_vec, stg, box_turn, &map_d, lane,
+                                                box_x, box_y, box_img);
                 } else if (row_ok) {
                     store32_f32(v, col0 + c, p, drow, crow, vec);
                 }
@@ -1095,8 +1108,10 @@ int decxb_launch_gemm_tn(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t 
     const bool x3 = a.a_lo != nullptr;
     int tile = a.tile;
     if (tile == DECXB_TILE_AUTO) tile = decxb_pick_tile(ctx, a.M, a.N, a.nbatch);
-    if (a.chunked) {
-        if (!x3) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "chunked accumulation needs the 3xTF32 operands");
+    /* a K that fits the first chunk gives the same bits either way: take the kernel with fewer threads */
+    const bool chunked = a.chunked && decxb_ceil_div(a.K, BK) > 2 * KCHUNK;
+    if (a.chunked && !x3) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "chunked accumulation needs the 3xTF32 operands");
+    if (chunked) {
         switch (tile) {
         case DECXB_TILE_1CTA_128x128: return launch_cfg<1, 128, 3, KCHUNK>(ctx, a, s);
         case DECXB_TILE_2CTA_256x256: return launch_cfg<2, 128, 3, KCHUNK>(ctx, a, s);
@@ -1117,8 +1132,8 @@ int decxb_launch_gemm_tn(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t 
 int decxb_launch_conv_implicit(decxb_ctx* ctx, const decxb_conv_gemm_args& a, cudaStream_t s)
 {
     const bool x3 = a.src_lo != nullptr;
-    if (a.chunked) {
-        if (!x3) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "chunked accumulation needs the 3xTF32 operands");
+    if (a.chunked && !x3) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "chunked accumulation needs the 3xTF32 operands");
+    if (a.chunked && a.kW * a.kH * decxb_ceil_div(a.dp, BK) > 2 * KCHUNK) {
         if (a.Np <= 64)  return launch_conv_cfg<1, 64, 3, KCHUNK>(ctx, a, s);
         if (a.Np <= 128) return launch_conv_cfg<1, 128, 3, KCHUNK>(ctx, a, s);
         return launch_conv_cfg<2, 128, 3, KCHUNK>(ctx, a, s);
