@@ -44,7 +44,8 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel, from the ncu
 # captures summarised under profiles/ (gemm_tf32_kernel_cfg2.md, im2col_pack_kernel_cfg3.md)
 NCU_TRAFFIC_BYTES = {("cfg2", "3xtf32", "gemm"): 727.8e6, ("cfg2", "strict", "gemm"): 731.1e6, ("cfg3", "3xtf32", "pack"): 70.7e6,
-                     ("cfg3", "strict", "pack"): 70.7e6}
+                     ("cfg3", "strict", "pack"): 70.7e6,
+                     ("cfg4", "strict", "gemm"): 2594e6, ("cfg4", "3xtf32", "gemm"): 2515e6}
 
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
@@ -337,8 +338,13 @@ def main():
         ach = flops_rank / launches_per_step / (avg_ms * 1e-3) / 1e12
         tf32 = peaks["bf16_tflops"] / 2.0
         peak = {"3xtf32": tf32 / 3.0, "strict": tf32 / 3.0, "1xtf32": tf32, "f16": peaks["bf16_tflops"]}[args.mode]
+        # DRAM traffic of one launch from the ncu capture of the same workload (profiles/); a rank of a strong-scaling
+        # run launches on its share of the images, and the traffic of this kernel grows with the images
+        traffic = NCU_TRAFFIC_BYTES.get((args.workload, args.mode, "gemm")) if args.tile == 0 else None
+        if traffic is not None and wl["kind"] == "conv":
+            traffic = traffic * nb / wl["batch"] if (algo == b.CONV_IMPLICIT and not args.batch) else None
         roofline = {"bound": "tensor", "kernel": "decxb_gemm_tf32_kernel", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
-                    "frac": ach / peak, "traffic": NCU_TRAFFIC_BYTES.get((args.workload, args.mode, "gemm")) if args.tile == 0 else None,
+                    "frac": ach / peak, "traffic": traffic,
                     "peak_basis": f"{peaks['basis']} bf16 dense burst {peaks['bf16_tflops']} TFLOP/s"
                                   + {"3xtf32": " / 2 (TF32) / 3 (3xTF32)", "strict": " / 2 (TF32) / 3 (3xTF32)", "1xtf32": " / 2 (TF32)",
                                      "f16": " (fp16 runs at the bf16 rate)"}[args.mode],
