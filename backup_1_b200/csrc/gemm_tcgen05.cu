@@ -1029,8 +1029,10 @@ int launch_cfg(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s)
     p.status = ctx->d_status;
     /* results through TMA stores when the result array can be described to the copy engine
      * (16-byte aligned base and pitch); batched launches and odd layouts store from the threads */
+    /* N must be a multiple of 4 as well: the copy engine clips a store at the tensor's edge in whole
+     * 16-byte pieces, so a ragged N would have the rest of the last piece of every row written */
     CUtensorMap md = ma_hi;
-    if (a.nbatch <= 1 && (reinterpret_cast<uintptr_t>(a.D) & 15) == 0 && a.ldd % 4 == 0) {
+    if (a.nbatch <= 1 && (reinterpret_cast<uintptr_t>(a.D) & 15) == 0 && a.ldd % 4 == 0 && a.N % 4 == 0) {
         if ((rc = make_map(ctx, &md, a.D, a.M, a.N, a.ldd, 32))) return rc;
         p.tma_store = 1;
     }

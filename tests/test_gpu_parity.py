@@ -193,6 +193,35 @@ def test_strict_mode_batched_and_convolution(ctx):
             assert np.all(Dv[..., Nf:] == 0)
 
 
+def test_gemm_seeded_random_shapes_and_pitches(ctx):
+    """40 seeded ragged shapes with random leading dimensions (aligned and unaligned bases and
+    pitches, so both the TMA-store and the per-thread-store epilogues run), with and without
+    addend, in both accumulation modes: within the bar of the fma chain, and nothing outside
+    the N columns of D is written."""
+    rng = np.random.default_rng(12345)
+    for case in range(40):
+        M, N, K = int(rng.integers(1, 700)), int(rng.integers(1, 700)), int(rng.integers(1, 900))
+        lda, ldb, ldd = K + int(rng.integers(0, 8)), N + int(rng.integers(0, 8)), N + int(rng.integers(0, 8))
+        off = int(rng.integers(0, 4))                      # result base offset in floats: 0 = 16-byte aligned
+        use_c = bool(rng.integers(0, 2))
+        mode = b.GEMM_DEFAULT if case % 2 == 0 else b.GEMM_3XTF32
+        A = np.zeros((M, lda), dtype=np.float32); A[:, :K] = o.fill_uniform(M * K, 100 + case).reshape(M, K)
+        B = np.zeros((K, ldb), dtype=np.float32); B[:, :N] = o.fill_uniform(K * N, 200 + case).reshape(K, N)
+        Cin = o.fill_uniform(M * N, 300 + case).reshape(M, N) if use_c else None
+        dbuf = torch.full((M * ldd + 4,), float("nan"), device=DEV)
+        dD = dbuf[off:off + M * ldd].view(M, ldd)
+        dC = dev(Cin) if use_c else None
+        ctx.gemm(M, N, K, dev(A), lda, dev(B), ldb, dD, ldd, Cin=dC, ldc=N if use_c else 0, mode=mode)
+        ctx.synchronize()
+        got = dD.cpu().numpy()
+        R = o.gemm_fmaf(np.ascontiguousarray(A[:, :K]), np.ascontiguousarray(B[:, :N]), Cin)
+        err = o.norm_err(got[:, :N], R, K, 1.0, 1.0)
+        assert err <= TOL_3X, f"case {case} {(M, N, K, lda, ldb, ldd, off, use_c, mode)}: {err:.3e}"
+        assert np.isnan(got[:, N:]).all(), f"case {case}: wrote beyond column N"
+        whole = dbuf.cpu().numpy()
+        assert np.isnan(whole[:off]).all() and np.isnan(whole[off + M * ldd:]).all()
+
+
 def test_gemm_pitched_operands(ctx):
     """Leading dimensions larger than the row length (DECX pitch = ceil8(width))."""
     M, N, K = 130, 100, 70
