@@ -318,6 +318,44 @@ def test_gemm_fp16_against_half_chain_and_exact(ctx, shape):
     assert np.array_equal(hD.view(np.uint16), dD.cpu().numpy().view(np.uint16)), "host path must give the device path's bits"
 
 
+def test_gemm_fp16_and_batched_seeded_random_shapes(ctx):
+    """Seeded ragged shapes with random pitches for the fp16 entry (sentinel beyond N untouched,
+    result within half rounding of the exact product) and for the batched fp32 entry in both
+    accumulation modes (every matrix against the oracle, gaps between matrices untouched)."""
+    rng = np.random.default_rng(4242)
+    for case in range(12):
+        M, N, K = int(rng.integers(1, 400)), int(rng.integers(1, 400)), int(rng.integers(1, 600))
+        lda, ldb, ldd = K + int(rng.integers(0, 3)) * 8, N + int(rng.integers(0, 3)) * 8, N + int(rng.integers(0, 9))
+        A = np.zeros((M, lda), dtype=np.float16); A[:, :K] = o.fill_uniform(M * K, 700 + case).reshape(M, K).astype(np.float16)
+        B = np.zeros((K, ldb), dtype=np.float16); B[:, :N] = o.fill_uniform(K * N, 800 + case).reshape(K, N).astype(np.float16)
+        dD = torch.full((M, ldd), float("nan"), device=DEV, dtype=torch.float16)
+        ctx.gemm_f16(M, N, K, dev(A), lda, dev(B), ldb, dD, ldd)
+        ctx.synchronize()
+        D = dD.cpu().numpy().astype(np.float64)
+        E = o.gemm_f16_exact(np.ascontiguousarray(A[:, :K]), np.ascontiguousarray(B[:, :N]), None)
+        bound = np.abs(E) * 2.0 ** -11 + K * 2.0 ** -22 + 2.0 ** -24
+        assert np.all(np.abs(D[:, :N] - E) <= bound), f"fp16 case {case} {(M, N, K, lda, ldb, ldd)}"
+        assert np.isnan(D[:, N:]).all(), f"fp16 case {case}: wrote beyond column N"
+    for case in range(10):
+        nb, M, N, K = int(rng.integers(2, 10)), int(rng.integers(1, 300)), int(rng.integers(1, 300)), int(rng.integers(1, 400))
+        lda, ldb, ldd = K + int(rng.integers(0, 6)), N + int(rng.integers(0, 6)), N + int(rng.integers(0, 6))
+        sA, sB, sD = M * lda + int(rng.integers(0, 9)), K * ldb + int(rng.integers(0, 9)), M * ldd + int(rng.integers(0, 9))
+        mode = b.GEMM_DEFAULT if case % 2 == 0 else b.GEMM_3XTF32
+        A = np.zeros((nb, sA), dtype=np.float32); B = np.zeros((nb, sB), dtype=np.float32)
+        for i in range(nb):
+            A[i, :M * lda] = o.fill_uniform_2d(M, K, lda, 900 + case, first_index=i * 100003).reshape(-1)
+            B[i, :K * ldb] = o.fill_uniform_2d(K, N, ldb, 950 + case, first_index=i * 100019).reshape(-1)
+        dD = torch.full((nb, sD), float("nan"), device=DEV)
+        ctx.gemm_batched(nb, M, N, K, dev(A), lda, sA, dev(B), ldb, sB, dD, ldd, sD, mode=mode)
+        ctx.synchronize()
+        D = dD.cpu().numpy()
+        for i in range(nb):
+            Ai = A[i, :M * lda].reshape(M, lda)[:, :K]; Bi = B[i, :K * ldb].reshape(K, ldb)[:, :N]
+            Di = D[i, :M * ldd].reshape(M, ldd)
+            assert o.norm_err(Di[:, :N], o.gemm_fmaf(np.ascontiguousarray(Ai), np.ascontiguousarray(Bi)), K, 1.0, 1.0) <= TOL_3X, (case, i)
+            assert np.isnan(Di[:, N:]).all() and np.isnan(D[i, M * ldd:]).all(), (case, i)
+
+
 @pytest.mark.parametrize("mode", [b.GEMM_3XTF32, b.GEMM_1XTF32])
 @pytest.mark.parametrize("tile", [b.TILE_AUTO, b.TILE_2CTA_256x256, b.TILE_1CTA_128x64])
 def test_gemm_batched_single_launch_many_small(ctx, mode, tile):
@@ -523,6 +561,28 @@ def test_conv_matches_oracle(ctx, case, algo):
     assert np.all(D[..., N:] == 0), "padding channels must be zero"
     Dh = run_conv(ctx, src, W, C, flt, kW, flag, algo=algo, host=True)
     assert np.array_equal(D, Dh), "host-resident path must give the device path's bits"
+
+
+def test_conv_seeded_random_geometries(ctx):
+    """30 seeded geometries (odd filter sizes 1..9 per axis, 1..70 channels, 1..90 filters, both
+    border flags, 1..3 images), both algorithms and both accumulation modes: every element of the
+    padded destination is written, filter padding is zero, values within the bar of the oracle."""
+    rng = np.random.default_rng(777)
+    for case in range(30):
+        kW, kH = int(rng.choice([1, 3, 5, 7, 9])), int(rng.choice([1, 3, 5, 7, 9]))
+        W, H = int(rng.integers(kW, 64)), int(rng.integers(kH, 48))
+        C, N, flag, nb = int(rng.integers(1, 71)), int(rng.integers(1, 91)), int(rng.integers(0, 2)), int(rng.integers(1, 4))
+        src = np.stack([o.make_tensor(W, H, C, 500 + case, first_index=i * W * H * C) for i in range(nb)])
+        flt = o.make_filters(kW, kH, C, N, 600 + case)
+        R = np.stack([o.conv2_im2col(src[i], W, C, flt, kW, flag) for i in range(nb)])
+        Kc = kW * kH * o.ceil4(C)
+        algo = ALGOS[case % 2]
+        mode = b.GEMM_DEFAULT if (case // 2) % 2 == 0 else b.GEMM_3XTF32
+        D = run_conv(ctx, src, W, C, flt, kW, flag, mode=mode, algo=algo)
+        tag = f"case {case} {(W, H, C, kW, kH, N, flag, nb, algo, mode)}"
+        assert not np.isnan(D).any(), tag + ": unwritten destination elements"
+        assert o.norm_err(D, R, Kc, 1.0, 1.0) <= TOL_3X, tag
+        assert np.all(D[..., N:] == 0), tag + ": padding channels must be zero"
 
 
 @pytest.mark.parametrize("algo", ALGOS)
