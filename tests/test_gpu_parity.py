@@ -479,6 +479,28 @@ def test_pack_variants_are_bit_identical(ctx, variant):
         ctx.set_pack_variant(0)
 
 
+@pytest.mark.parametrize("variant", [0, 1, 2])
+def test_pack_seeded_random_geometries_bit_exact(ctx, variant):
+    """25 seeded geometries (odd filter sizes 1..17, 1..300 channels, both flags) through each of
+    the three pack kernels: the bytes of the oracle's column matrix, NaN payloads included."""
+    rng = np.random.default_rng(999)
+    ctx.set_pack_variant(variant)
+    try:
+        for case in range(25):
+            kW, kH = int(rng.choice([1, 3, 5, 7, 9, 17])), int(rng.choice([1, 3, 5, 7, 9, 17]))
+            W, H = int(rng.integers(kW, 80)), int(rng.integers(kH, 40))
+            C, flag = int(rng.choice([1, 3, 4, 7, 16, 33, 64, 130, 300])), int(rng.integers(0, 2))
+            if kW * kH * o.ceil4(C) * o.ceil4(W) * H * 4 > 256 << 20:
+                continue
+            src = o.make_tensor(W, H, C, 40 + case)
+            src.view(np.uint32)[H // 2, 0, 0] = 0x7FC01234          # a NaN with a payload must survive
+            got = run_pack(ctx, src, W, C, kW, kH, flag)
+            assert np.array_equal(got.view(np.uint32), o.im2col_pack(src, W, C, kW, kH, flag).view(np.uint32)), \
+                (variant, case, W, H, C, kW, kH, flag)
+    finally:
+        ctx.set_pack_variant(0)
+
+
 def test_pack_golden_vectors_of_reference_kernel(ctx, golden):
     import hashlib
     z, cases = golden
