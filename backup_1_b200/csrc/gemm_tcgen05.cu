@@ -13,7 +13,8 @@
  *  - tcgen05.mma kind::tf32, accumulators in tensor memory (TMEM), fp32.  3xTF32 issues
  *    a_lo*b_hi, a_hi*b_lo, a_hi*b_hi into the same accumulator for every k-step of 8.
  *  - Warp-specialised, persistent: warp 0 = TMA producer, warp 1 = MMA issuer (and TMEM
- *    owner), warps 2..5 = epilogue (tcgen05.ld -> registers -> a swizzled 32 x 32 box in shared
+ *    owner), warps 2..9 = epilogue, four TMEM lane quarters x two column halves (warps 2..5 in
+ *    the fp16 kernel) (tcgen05.ld -> registers -> a swizzled 32 x 32 box in shared
  *    memory -> one TMA store per box; 128-bit stores from the threads for layouts the copy
  *    engine cannot describe).  The accumulator is double-buffered in TMEM so the epilogue of
  *    tile i overlaps the main loop of tile i+1.
@@ -35,7 +36,8 @@ namespace {
 constexpr int BM_CTA = 128;        /* rows of A (and of the accumulator) per CTA          */
 constexpr int BK = 32;             /* floats per k-block = one 128-byte swizzle row        */
 constexpr int UMMA_K = 8;          /* k per tcgen05.mma kind::tf32                          */
-constexpr int NUM_THREADS = 192;   /* 6 warps: producer, MMA issuer, 4 epilogue warps        */
+constexpr int NUM_THREADS_F16 = 192;   /* fp16 kernel: producer, MMA issuer, 4 epilogue warps     */
+constexpr int NUM_THREADS = 320;   /* fp32 whole-K kernels: producer, MMA issuer, 8 epilogue warps (4 lane quarters x 2 column halves) */
 constexpr int NUM_THREADS_CHUNKED = 384;   /* chunked accumulation: warp group 0 = producer, MMA issuer
                                               and two idle warps; warp groups 1, 2 = 8 epilogue warps */
 constexpr int KCHUNK = 4;          /* k-blocks per chunk of the chunked accumulation: 128 values of K
@@ -470,7 +472,8 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 template <int CTAS, int BN, int NSPLIT, int KCH = 0>
 struct Cfg {
     static constexpr int PARTS = NSPLIT == 3 ? 2 : 1;
-    static constexpr int EPI_WARPS = KCH ? 8 : 4;
+    static constexpr int EPI_WARPS = NSPLIT == 16 ? 4 : 8;
+    static constexpr int THREADS = KCH ? NUM_THREADS_CHUNKED : NSPLIT == 16 ? NUM_THREADS_F16 : NUM_THREADS;
     /* one 32 x 32 fp32 box (4 KiB, 128-byte swizzled) per epilogue warp for the TMA result stores */
     static constexpr int STAGING1 = NSPLIT == 16 ? 0 : EPI_WARPS * 4096;
     static constexpr int UMMA_M = BM_CTA * CTAS;
@@ -493,7 +496,7 @@ struct Cfg {
 };
 
 template <int CTAS, int BN, int NSPLIT, bool CONV, int KCH>
-__global__ void __launch_bounds__(KCH ? NUM_THREADS_CHUNKED : NUM_THREADS, 1)
+__global__ void __launch_bounds__((Cfg<CTAS, BN, NSPLIT, KCH>::THREADS), 1)
 decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                        const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
                        const __grid_constant__ CUtensorMap map_d, const GemmParams p)
@@ -524,7 +527,7 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
         if (NSPLIT == 3) { prefetch_tensormap(&map_a_lo); prefetch_tensormap(&map_b_lo); }
         if (p.tma_store) prefetch_tensormap(&map_d);
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), (KCH ? 8 : 4) * CTAS); }
+        for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), C::EPI_WARPS * CTAS); }
         fence_barrier_init();
     }
     if (warp == 1) {
@@ -655,7 +658,7 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
         const bool c_vec = p.C && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && (p.ldc % 4 == 0) && (p.c_batch_stride % 4 == 0);
         int unit = 0;                             /* same count as the MMA issuer's */
         bool alive = true;
-        const int eh = KCH ? (warp - 4) >> 2 : 0; /* chunked: column half this warp sums */
+        const int eh = KCH ? (warp - 4) >> 2 : C::EPI_WARPS == 8 ? (warp - 2) >> 2 : 0;   /* column half of this warp */
         const uint32_t stg = staging + (uint32_t)(KCH ? warp - 4 : warp - 2) * (4096u * C::BOXES);   /* this warp's TMA store box(es) */
         uint32_t box_turn = 0;
         for (int t = cluster_id; t < num_tiles && alive; t += num_clusters) {
@@ -736,8 +739,10 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
             if (!wait_bounded(tfull_bar(acc), acc_phase, p, 400 + acc, t)) { alive = false; break; }
             tc_fence_after();
             const uint32_t taddr = tlane + (uint32_t)(acc * C::UMMA_N);
+            constexpr int COLS_PER_WARP = C::UMMA_N / (C::EPI_WARPS / 4);
+            static_assert(COLS_PER_WARP % 32 == 0, "whole 32-column groups per epilogue warp");
 #pragma unroll 1
-            for (int c = 0; c < C::UMMA_N; c += 32) {
+            for (int c = eh * COLS_PER_WARP; c < (eh + 1) * COLS_PER_WARP; c += 32) {
                 if (col0 + c >= p.N) break;           /* warp-uniform */
                 float v[32];
                 tmem_ld_32x32(taddr + (uint32_t)c, v);
@@ -933,7 +938,7 @@ int launch_kernel(decxb_ctx* ctx, const CUtensorMap& ma_hi, const CUtensorMap& m
     if (clusters < 1) clusters = 1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(clusters * CTAS), 1, 1);
-    cfg.blockDim = dim3(KCH ? NUM_THREADS_CHUNKED : NUM_THREADS, 1, 1);
+    cfg.blockDim = dim3(C::THREADS, 1, 1);
     cfg.dynamicSmemBytes = C::SMEM_BYTES;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
