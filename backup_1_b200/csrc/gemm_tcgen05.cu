@@ -540,6 +540,10 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
     tc_fence_after();
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+    /* Programmatic dependent launch: everything above (barriers, tensor memory, descriptor prefetch)
+     * may run while the kernel before this one in the stream (the operand split) is still
+     * draining; nothing below touches global memory before that kernel has completed. */
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     /* Chunked accumulation with 128 running sums per thread: the epilogue warp groups take
      * registers that warp group 0 gives up (168 per thread at launch for 384 threads;
@@ -941,10 +945,12 @@ int launch_kernel(decxb_ctx* ctx, const CUtensorMap& ma_hi, const CUtensorMap& m
     cfg.blockDim = dim3(C::THREADS, 1, 1);
     cfg.dynamicSmemBytes = C::SMEM_BYTES;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CTAS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 2;
     {
         decxb_launch_scope scope(ctx, s, DECXB_K_GEMM);
         DECXB_CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kernel, ma_hi, ma_lo, mb_hi, mb_lo, md, p));

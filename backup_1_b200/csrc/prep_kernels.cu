@@ -26,6 +26,11 @@ __device__ __forceinline__ float uniform_pm1(uint32_t seed, uint64_t idx)
     return __fsub_rn(__fmul_rn((float)(u >> 8), 1.0f / 8388608.0f), 1.0f);
 }
 
+/* Programmatic dependent launch: lets the next kernel in the stream (the GEMM, launched with the
+ * matching attribute) be scheduled while this grid drains; that kernel still waits for this
+ * grid's completion (griddepcontrol.wait) before it touches memory.  A no-op otherwise. */
+__device__ __forceinline__ void allow_dependent_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __global__ void __launch_bounds__(256)
 decxb_fill_uniform_kernel(float* __restrict__ dst, uint64_t rows, uint64_t cols, uint64_t pitch,
                           uint32_t seed, uint64_t first_index)
@@ -83,6 +88,7 @@ decxb_split_rows_kernel(const float* __restrict__ in, int64_t rows, int64_t cols
 {
     /* nbatch matrices: matrix b reads rows [0, rows) at in + b*in_batch_stride and writes rows
      * [b*rows_out, (b+1)*rows_out) of the stacked output (rows beyond `rows` are zero) */
+    allow_dependent_launch();
     const int64_t q_per_row = ld_out >> 2;
     const int64_t total = nbatch * rows_out * q_per_row;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -136,6 +142,7 @@ decxb_split_transpose_kernel(const float* __restrict__ in, int64_t K, int64_t N,
                              int64_t tiles_n, int64_t nbatch, int64_t in_batch_stride, int64_t out_batch_rows)
 {
     __shared__ float tile[64][65];
+    allow_dependent_launch();
     const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;   /* 64 x 4 */
     const int64_t tiles_k = (ld_out + 63) / 64;
     const int64_t n_tiles = tiles_k * tiles_n;
@@ -178,6 +185,7 @@ decxb_split_transpose_vec_kernel(const float* __restrict__ in, int64_t K, int64_
                                  int64_t tiles_n, int64_t nbatch, int64_t in_batch_stride, int64_t out_batch_rows)
 {
     __shared__ float tile[64][65];
+    allow_dependent_launch();
     const int tid = threadIdx.x;
     const int64_t tiles_k = (ld_out + 63) / 64;
     const int64_t n_tiles = tiles_k * tiles_n;
@@ -257,6 +265,7 @@ __global__ void __launch_bounds__(256)
 decxb_filter_matrix_kernel(const float* __restrict__ filters, int kW, int kH, int dp, int cp, int64_t N,
                            float* __restrict__ hi, float* __restrict__ lo, int64_t rows_out, int64_t ld_out, int raw)
 {
+    allow_dependent_launch();
     const int64_t Kp = (int64_t)kW * kH * cp;
     const int64_t kwp = (kW + 3) / 4 * 4;
     const int64_t gap = (int64_t)dp * kwp * kH;
