@@ -671,7 +671,9 @@ extern "C" int decxb_conv2_im2col_f32_host(decxb_ctx* ctx, int mode, int algo, i
     if ((rc = scratch.get((size_t)batch * dst_img * 4, (void**)&d_dst))) return rc;
     if ((rc = fence_copy_streams(ctx, evs))) return rc;
     DECXB_CUDA_TRY(ctx, cudaMemcpyAsync(d_flt, h_filters, (size_t)N * kH * kwp * dp * 4, cudaMemcpyHostToDevice, up));
-    int64_t group = decxb_ceil_div(batch, 8);
+    /* many small groups: the first upload and the last download are not overlapped with anything,
+     * so they should be short; 1/32 of the batch, but at least 8 MiB per copy */
+    int64_t group = decxb_ceil_div(batch, 32);
     const int64_t min_group = decxb_ceil_div((int64_t)8 << 20, src_img * 4);      /* at least 8 MiB per upload */
     if (group < min_group) group = min_group;
     if (group > batch) group = batch;
