@@ -135,9 +135,47 @@ int sync_all_streams(decxb_ctx* ctx)
     return DECXB_OK;
 }
 
+/* Waits for all three streams whatever each one reports (the error path of the pipelines). */
+void drain_all_streams(decxb_ctx* ctx)
+{
+    cudaStreamSynchronize(ctx->copy_stream[0]);
+    cudaStreamSynchronize(ctx->stream);
+    cudaStreamSynchronize(ctx->copy_stream[1]);
+    cudaGetLastError();
+}
+
 cudaStream_t pick_stream(decxb_ctx* ctx, void* stream) { return stream ? (cudaStream_t)stream : ctx->stream; }
 
+/* Host-side fault injection for tests (decxb_inject_pipeline_error): true when the CUDA call
+ * about to be made by a host-resident pipeline is the one chosen to fail. */
+bool injected_failure(decxb_ctx* ctx)
+{
+    if (ctx->inject_countdown < 0) return false;
+    if (ctx->inject_countdown-- > 0) return false;
+    return true;
+}
+
+/* A CUDA call inside a host-resident pipeline.  When it fails, copies and kernels are already
+ * queued on three streams and use the call's scratch blocks and the caller's host buffers:
+ * `fail` (a local of the calling function) drains the streams before the function returns and
+ * the scratch goes back to the arena. */
+#define PIPE_TRY(expr)                                                                              \
+    do {                                                                                           \
+        cudaError_t _e = injected_failure(ctx) ? cudaErrorUnknown : (expr);                        \
+        if (_e != cudaSuccess) {                                                                   \
+            decxb_set_error(ctx, std::string(#expr) + ": " + cudaGetErrorString(_e));             \
+            return fail(DECXB_ERR_CUDA);                                                           \
+        }                                                                                          \
+    } while (0)
+
 }  // namespace
+
+extern "C" int decxb_inject_pipeline_error(decxb_ctx* ctx, int nth_call)
+{
+    if (!ctx) return DECXB_ERR_BAD_PARAM;
+    ctx->inject_countdown = nth_call;
+    return DECXB_OK;
+}
 
 extern "C" int decxb_gemm_f32(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_t K,
                               const float* A, int64_t lda, const float* B, int64_t ldb,
@@ -213,16 +251,7 @@ extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M
     if (ncol < 1024) ncol = 1024;
     if (N < 2048 || ncol > N) ncol = N;
 
-    auto fail = [&](int code) { sync_all_streams(ctx); return code; };
-    /* a failed call inside the pipeline drains the three streams before the scratch goes back */
-#define PIPE_TRY(expr)                                                                              \
-    do {                                                                                           \
-        cudaError_t _e = (expr);                                                                   \
-        if (_e != cudaSuccess) {                                                                   \
-            decxb_set_error(ctx, std::string(#expr) + ": " + cudaGetErrorString(_e));             \
-            return fail(DECXB_ERR_CUDA);                                                           \
-        }                                                                                          \
-    } while (0)
+    auto fail = [&](int code) { drain_all_streams(ctx); return code; };
     cudaEvent_t e_a0 = evs.make();
     if (!e_a0) return decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate");
     PIPE_TRY(cudaMemcpy2DAsync(dA, Kp * 4, hA, lda * 4, K * 4, rows0, cudaMemcpyHostToDevice, up));
@@ -276,7 +305,6 @@ extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M
     if ((rc = sync_all_streams(ctx))) return rc;
     scratch.release();
     return decxb_check_dev_status(ctx);
-#undef PIPE_TRY
 }
 
 /* ---- fp16 GEMM ------------------------------------------------------------------------------- */
@@ -334,13 +362,14 @@ extern "C" int decxb_gemm_f16_host(decxb_ctx* ctx, int64_t M, int64_t N, int64_t
     if ((rc = scratch.get((size_t)K * Np * 2, &dB))) return rc;
     if ((rc = scratch.get((size_t)M * Np * 2, &dD))) return rc;
     if (hC && (rc = scratch.get((size_t)M * Np * 2, &dC))) return rc;
-    DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dA, Kp * 2, hA, lda * 2, K * 2, M, cudaMemcpyHostToDevice, s));
-    DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dB, Np * 2, hB, ldb * 2, N * 2, K, cudaMemcpyHostToDevice, s));
-    if (hC) DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dC, Np * 2, hC, ldc * 2, N * 2, M, cudaMemcpyHostToDevice, s));
+    auto fail = [&](int code) { cudaStreamSynchronize(s); cudaGetLastError(); return code; };
+    PIPE_TRY(cudaMemcpy2DAsync(dA, Kp * 2, hA, lda * 2, K * 2, M, cudaMemcpyHostToDevice, s));
+    PIPE_TRY(cudaMemcpy2DAsync(dB, Np * 2, hB, ldb * 2, N * 2, K, cudaMemcpyHostToDevice, s));
+    if (hC) PIPE_TRY(cudaMemcpy2DAsync(dC, Np * 2, hC, ldc * 2, N * 2, M, cudaMemcpyHostToDevice, s));
     rc = gemm_f16_device(ctx, M, N, K, dA, Kp, dB, Np, dC, Np, dD, Np, s);
-    if (rc) { cudaStreamSynchronize(s); return rc; }
-    DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(hD, ldd * 2, dD, Np * 2, N * 2, M, cudaMemcpyDeviceToHost, s));
-    DECXB_CUDA_TRY(ctx, cudaStreamSynchronize(s));
+    if (rc) return fail(rc);
+    PIPE_TRY(cudaMemcpy2DAsync(hD, ldd * 2, dD, Np * 2, N * 2, M, cudaMemcpyDeviceToHost, s));
+    PIPE_TRY(cudaStreamSynchronize(s));
     scratch.release();
     return decxb_check_dev_status(ctx);
 }
@@ -439,30 +468,31 @@ extern "C" int decxb_gemm_f32_batched_host(decxb_ctx* ctx, int mode, int tile, i
         if (hC && (rc = scratch.get((size_t)group * M * Np * 4, (void**)&dC[k]))) return rc;
     }
     if ((rc = fence_copy_streams(ctx, evs))) return rc;
+    auto fail = [&](int code) { drain_all_streams(ctx); return code; };
     std::vector<cudaEvent_t> e_done(ngroups, nullptr), e_down(ngroups, nullptr);
     for (int64_t gi = 0; gi < ngroups; ++gi) {
         const int k = (int)(gi % nslots);
         const int64_t i0 = gi * group, nb = batch - i0 < group ? batch - i0 : group;
         cudaEvent_t e_up = evs.make();
         e_done[gi] = evs.make(); e_down[gi] = evs.make();
-        if (!e_up || !e_done[gi] || !e_down[gi]) { sync_all_streams(ctx); return decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"); }
-        if (gi >= nslots) DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(up, e_done[gi - nslots], 0));      /* operands of the slot consumed */
+        if (!e_up || !e_done[gi] || !e_down[gi]) return fail(decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"));
+        if (gi >= nslots) PIPE_TRY(cudaStreamWaitEvent(up, e_done[gi - nslots], 0));      /* operands of the slot consumed */
         for (int64_t j = 0; j < nb; ++j) {
-            DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dA[k] + j * M * Kp, Kp * 4, hA + (i0 + j) * strideA, lda * 4, K * 4, M, cudaMemcpyHostToDevice, up));
-            DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dB[k] + j * K * Np, Np * 4, hB + (i0 + j) * strideB, ldb * 4, N * 4, K, cudaMemcpyHostToDevice, up));
-            if (hC) DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(dC[k] + j * M * Np, Np * 4, hC + (i0 + j) * strideC, ldc * 4, N * 4, M, cudaMemcpyHostToDevice, up));
+            PIPE_TRY(cudaMemcpy2DAsync(dA[k] + j * M * Kp, Kp * 4, hA + (i0 + j) * strideA, lda * 4, K * 4, M, cudaMemcpyHostToDevice, up));
+            PIPE_TRY(cudaMemcpy2DAsync(dB[k] + j * K * Np, Np * 4, hB + (i0 + j) * strideB, ldb * 4, N * 4, K, cudaMemcpyHostToDevice, up));
+            if (hC) PIPE_TRY(cudaMemcpy2DAsync(dC[k] + j * M * Np, Np * 4, hC + (i0 + j) * strideC, ldc * 4, N * 4, M, cudaMemcpyHostToDevice, up));
         }
-        DECXB_CUDA_TRY(ctx, cudaEventRecord(e_up, up));
-        DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(s, e_up, 0));
-        if (gi >= nslots) DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(s, e_down[gi - nslots], 0));       /* result slot drained */
+        PIPE_TRY(cudaEventRecord(e_up, up));
+        PIPE_TRY(cudaStreamWaitEvent(s, e_up, 0));
+        if (gi >= nslots) PIPE_TRY(cudaStreamWaitEvent(s, e_down[gi - nslots], 0));       /* result slot drained */
         rc = gemm_batched_device(ctx, mode, tile, nb, M, N, K, dA[k], Kp, M * Kp, dB[k], Np, K * Np,
                                  dC[k], Np, M * Np, dD[k], Np, M * Np, s);
-        if (rc) { sync_all_streams(ctx); return rc; }
-        DECXB_CUDA_TRY(ctx, cudaEventRecord(e_done[gi], s));
-        DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(down, e_done[gi], 0));
+        if (rc) return fail(rc);
+        PIPE_TRY(cudaEventRecord(e_done[gi], s));
+        PIPE_TRY(cudaStreamWaitEvent(down, e_done[gi], 0));
         for (int64_t j = 0; j < nb; ++j)
-            DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(hD + (i0 + j) * strideD, ldd * 4, dD[k] + j * M * Np, Np * 4, N * 4, M, cudaMemcpyDeviceToHost, down));
-        DECXB_CUDA_TRY(ctx, cudaEventRecord(e_down[gi], down));
+            PIPE_TRY(cudaMemcpy2DAsync(hD + (i0 + j) * strideD, ldd * 4, dD[k] + j * M * Np, Np * 4, N * 4, M, cudaMemcpyDeviceToHost, down));
+        PIPE_TRY(cudaEventRecord(e_down[gi], down));
     }
     if ((rc = sync_all_streams(ctx))) return rc;
     scratch.release();
@@ -670,7 +700,8 @@ extern "C" int decxb_conv2_im2col_f32_host(decxb_ctx* ctx, int mode, int algo, i
     if ((rc = scratch.get((size_t)N * kH * kwp * dp * 4, (void**)&d_flt))) return rc;
     if ((rc = scratch.get((size_t)batch * dst_img * 4, (void**)&d_dst))) return rc;
     if ((rc = fence_copy_streams(ctx, evs))) return rc;
-    DECXB_CUDA_TRY(ctx, cudaMemcpyAsync(d_flt, h_filters, (size_t)N * kH * kwp * dp * 4, cudaMemcpyHostToDevice, up));
+    auto fail = [&](int code) { drain_all_streams(ctx); return code; };
+    PIPE_TRY(cudaMemcpyAsync(d_flt, h_filters, (size_t)N * kH * kwp * dp * 4, cudaMemcpyHostToDevice, up));
     /* many small groups: the first upload and the last download are not overlapped with anything,
      * so they should be short; 1/32 of the batch, but at least 8 MiB per copy */
     int64_t group = decxb_ceil_div(batch, 32);
@@ -680,17 +711,17 @@ extern "C" int decxb_conv2_im2col_f32_host(decxb_ctx* ctx, int mode, int algo, i
     for (int64_t b0 = 0; b0 < batch; b0 += group) {
         const int64_t nb = batch - b0 < group ? batch - b0 : group;
         cudaEvent_t e_up = evs.make(), e_done = evs.make();
-        if (!e_up || !e_done) { sync_all_streams(ctx); return decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"); }
-        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(d_src + b0 * src_img, src_img * 4, h_src + b0 * src_stride, src_stride * 4,
+        if (!e_up || !e_done) return fail(decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"));
+        PIPE_TRY(cudaMemcpy2DAsync(d_src + b0 * src_img, src_img * 4, h_src + b0 * src_stride, src_stride * 4,
                                              src_img * 4, nb, cudaMemcpyHostToDevice, up));
-        DECXB_CUDA_TRY(ctx, cudaEventRecord(e_up, up));
-        DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(s, e_up, 0));
+        PIPE_TRY(cudaEventRecord(e_up, up));
+        PIPE_TRY(cudaStreamWaitEvent(s, e_up, 0));
         rc = conv_device(ctx, mode, algo, flag, d_src + b0 * src_img, W, H, depth, d_flt, kW, kH, N, d_dst + b0 * dst_img,
                          nb, src_img, dst_img, s);
-        if (rc) { sync_all_streams(ctx); return rc; }
-        DECXB_CUDA_TRY(ctx, cudaEventRecord(e_done, s));
-        DECXB_CUDA_TRY(ctx, cudaStreamWaitEvent(down, e_done, 0));
-        DECXB_CUDA_TRY(ctx, cudaMemcpy2DAsync(h_dst + b0 * dst_stride, dst_stride * 4, d_dst + b0 * dst_img, dst_img * 4,
+        if (rc) return fail(rc);
+        PIPE_TRY(cudaEventRecord(e_done, s));
+        PIPE_TRY(cudaStreamWaitEvent(down, e_done, 0));
+        PIPE_TRY(cudaMemcpy2DAsync(h_dst + b0 * dst_stride, dst_stride * 4, d_dst + b0 * dst_img, dst_img * 4,
                                              dst_img * 4, nb, cudaMemcpyDeviceToHost, down));
     }
     if ((rc = sync_all_streams(ctx))) return rc;

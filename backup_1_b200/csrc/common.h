@@ -25,6 +25,10 @@ struct decxb_dev_status {
     int detail;      /* stage / tile index                                 */
 };
 
+/* Per-device tables (kernel attributes set once per device) are sized by this; decxb_init
+ * refuses device indices beyond it. */
+#define DECXB_MAX_DEVICES 64
+
 enum {
     DECXB_DEVERR_NONE = 0,
     DECXB_DEVERR_WAIT_EXPIRED = 1,
@@ -55,6 +59,7 @@ struct decxb_ctx {
     long long wait_limit_ns = 2000000000LL;
     int pack_variant = 0;               /* 0 = copy-engine (TMA) pack, 1 = shared-memory staged, 2 = direct */
     std::atomic<uint64_t> launches{0};
+    int inject_countdown = -1;          /* >= 0: that many pipeline CUDA calls from now, one reports a failure (tests) */
     std::string last_error;
     /* per-kernel event timing (decxb_profile_*) */
     bool profiling = false;

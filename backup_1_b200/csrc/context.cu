@@ -55,7 +55,7 @@ extern "C" int decxb_init(int device, decxb_ctx** out)
     *out = nullptr;
     int n = 0;
     if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) { cudaGetLastError(); return DECXB_ERR_NO_DEVICE; }
-    if (device < 0 || device >= n) return DECXB_ERR_BAD_PARAM;
+    if (device < 0 || device >= n || device >= DECXB_MAX_DEVICES) return DECXB_ERR_BAD_PARAM;
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return DECXB_ERR_CUDA;
     if (prop.major != 10) return DECXB_ERR_ARCH;
@@ -221,7 +221,16 @@ static int arena_give(decxb_ctx* ctx, void* dptr, cudaStream_t s, bool stream_or
 }
 
 extern "C" int decxb_malloc(decxb_ctx* ctx, size_t bytes, void** dptr) { return arena_take(ctx, bytes, dptr, nullptr, false); }
-extern "C" int decxb_free(decxb_ctx* ctx, void* dptr) { return arena_give(ctx, dptr, nullptr, false); }
+/* cudaFree would wait for the device; this free does not, so the block remembers an event on the
+ * context's compute stream: whoever takes it next waits for the library's own asynchronous work
+ * that may still use it.  Work the caller queued on a stream of its own is the caller's to
+ * finish before the free. */
+extern "C" int decxb_free(decxb_ctx* ctx, void* dptr)
+{
+    if (!ctx) return DECXB_ERR_BAD_PARAM;
+    if (decxb_bind(ctx) != DECXB_OK) return arena_give(ctx, dptr, nullptr, false);
+    return arena_give(ctx, dptr, ctx->stream, true);
+}
 int decxb_malloc_on_stream(decxb_ctx* ctx, size_t bytes, void** dptr, cudaStream_t s) { return arena_take(ctx, bytes, dptr, s, true); }
 int decxb_free_on_stream(decxb_ctx* ctx, void* dptr, cudaStream_t s) { return arena_give(ctx, dptr, s, true); }
 

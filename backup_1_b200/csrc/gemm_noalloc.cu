@@ -8,8 +8,19 @@
  * scratch from the context's arena, which grows with cudaMalloc; this one keeps that scratch
  * in a fixed array that is part of the library image.
  *
- * The array below lives in every CUDA context that loads this module, from the first use of
- * this entry point until the process exits, whether or not it is used again.
+ * The array below is part of this library's device code: every device whose CUDA context loads
+ * the library's module holds its 64 MiB until the process exits, whether or not this entry is
+ * ever called.  With the runtime's default lazy loading that is from the first use of anything in
+ * this file on that device; with CUDA_MODULE_LOADING=EAGER it is from the first CUDA call of
+ * any kind that the process makes on the device.
+ *
+ * Loading code also takes device memory, and it happens on first use: the first call on a device
+ * loads this module, and the first problem that selects a tile shape not used before in the
+ * process loads that kernel and sets its shared-memory attribute.  A caller that is about to
+ * hand the whole card to another allocator should therefore make, beforehand, one call per
+ * device with each problem shape it will use later (or one per tile shape: N <= 64-wide,
+ * 128 x 128, 128 x 256 and 256 x 256 outputs select the four kernels).  After that warm-up a
+ * call changes the device's free memory by nothing.
  */
 #include "common.h"
 
@@ -32,7 +43,14 @@ struct DeviceSlot {
     decxb_ctx ctx;                        /* host-side bookkeeping only; owns no device memory */
 };
 DeviceSlot g_slots[16];
-std::mutex g_slots_mtx;
+std::mutex g_slot_mtx[16];      /* one per device: calls on different devices do not wait for each other */
+
+/* Puts the calling thread's current device back when the entry point returns. */
+struct DeviceRestore {
+    int prev = -1;
+    DeviceRestore() { if (cudaGetDevice(&prev) != cudaSuccess) { cudaGetLastError(); prev = -1; } }
+    ~DeviceRestore() { if (prev >= 0) cudaSetDevice(prev); }
+};
 
 void say(char* buf, size_t len, const char* msg)
 {
@@ -42,9 +60,7 @@ void say(char* buf, size_t len, const char* msg)
 /* Once per device, with that device current: resolve the device addresses of the two symbols. */
 int setup_device(int device, DeviceSlot** out, char* err, size_t err_len)
 {
-    if (device < 0 || device >= 16) { say(err, err_len, "device index out of range (0..15)"); return DECXB_ERR_BAD_PARAM; }
-    std::lock_guard<std::mutex> lock(g_slots_mtx);
-    DeviceSlot& s = g_slots[device];
+    DeviceSlot& s = g_slots[device];        /* the caller holds g_slot_mtx[device] */
     if (cudaSetDevice(device) != cudaSuccess) { cudaGetLastError(); say(err, err_len, "cudaSetDevice failed"); return DECXB_ERR_NO_DEVICE; }
     if (!s.ready) {
         int major = 0, sms = 0;
@@ -95,14 +111,21 @@ extern "C" int decxb_gemm_f32_noalloc(int device, int64_t M, int64_t N, int64_t 
                      need, (size_t)DECXB_NOALLOC_SCRATCH_BYTES);
         return DECXB_ERR_TOO_LARGE;
     }
+    if (device < 0 || device >= 16) { say(err, err_len, "device index out of range (0..15)"); return DECXB_ERR_BAD_PARAM; }
+    DeviceRestore restore;
+    /* one call at a time per device on the host side (the entry blocks until D is complete, so
+     * calls through this lock never overlap on the GPU either) */
+    std::lock_guard<std::mutex> lock(g_slot_mtx[device]);
     DeviceSlot* slot = nullptr;
     int rc = setup_device(device, &slot, err, err_len);
     if (rc) return rc;
-    /* one call at a time per process on the host side; calls that overlap on the GPU (two
-     * streams) would still share the array and must be serialised by the caller */
-    std::lock_guard<std::mutex> lock(g_slots_mtx);
     decxb_ctx* ctx = &slot->ctx;
     cudaStream_t s = (cudaStream_t)stream;
+    if (s) {
+        int sdev = -1;
+        if (cudaStreamGetDevice(s, &sdev) != cudaSuccess) { cudaGetLastError(); say(err, err_len, "invalid stream"); return DECXB_ERR_BAD_PARAM; }
+        if (sdev != device) { say(err, err_len, "the stream belongs to another device"); return DECXB_ERR_BAD_PARAM; }
+    }
 
     float* a_hi = reinterpret_cast<float*>(slot->scratch);
     float* a_lo = reinterpret_cast<float*>(slot->scratch + a_part);

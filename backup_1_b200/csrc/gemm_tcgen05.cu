@@ -27,6 +27,7 @@
  *    memory is released and the kernel returns.
  */
 #include "common.h"
+#include "tc_ptx.cuh"
 
 #include <cudaTypedefs.h>
 #include <cuda_fp16.h>
@@ -46,241 +47,13 @@ constexpr int KCHUNK = 4;          /* k-blocks per chunk of the chunked accumula
                                       K max|a| max|b|, with uniform chunks of 64 -> 1.9e-7,
                                       128 -> 3.3e-7, 256 -> 6.5e-7, 512 -> 1.2e-6, whole K -> 2.9e-6 */
 constexpr int SMEM_LIMIT = 232448; /* 227 KiB opt-in maximum per CTA                        */
+#ifndef DECXB_A_COLLECTOR
+#define DECXB_A_COLLECTOR 0
+#endif
+constexpr bool A_COLLECTOR = DECXB_A_COLLECTOR != 0;   /* collector-buffer reuse of a_hi in the 3xTF32 k-step */
 
-/* ---------------------------------------------------------------- PTX wrappers ------ */
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+using namespace tcptx;
 
-__device__ __forceinline__ uint32_t cluster_ctarank()
-{
-    uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r;
-}
-
-__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank)
-{
-    uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank)); return r;
-}
-
-__device__ __forceinline__ void cluster_sync_all()
-{
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory");
-}
-
-__device__ __forceinline__ void fence_barrier_init()
-{
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
-}
-
-/* Arrive on a barrier given by a shared::cluster address (own CTA or the peer). */
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr)
-{
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(bar_cluster_addr) : "memory");
-}
-
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok;
-}
-
-__device__ __forceinline__ unsigned long long globaltimer_ns()
-{
-    unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t;
-}
-
-/* Plain 2-D tiled TMA load into this CTA's shared memory, completion on this CTA's barrier. */
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        :: "r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-
-/* Same load inside a CTA pair: data lands in the issuing CTA's shared memory, the
- * transaction bytes are counted on the barrier at `bar_cluster_addr` (the leader CTA's). */
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        :: "r"(dst), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y) : "memory");
-}
-
-/* 4-D tiled loads (channel, x, y, image) for the implicit-GEMM convolution: the box is
- * 32 channels x BX pixels x BY rows of one image, out-of-range pixels read as zero. */
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c, int x, int y, int n)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-        :: "r"(dst), "l"(map), "r"(bar), "r"(c), "r"(x), "r"(y), "r"(n) : "memory");
-}
-
-__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c, int x, int y, int n)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-        :: "r"(dst), "l"(map), "r"(bar_cluster_addr), "r"(c), "r"(x), "r"(y), "r"(n) : "memory");
-}
-
-/* Tiled TMA store of a 32 x 32 fp32 box from this CTA's shared memory (bulk async-group). */
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y)
-{
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                 :: "l"(map), "r"(src), "r"(x), "r"(y) : "memory");
-}
-/* The same box as a slice of a 4-D tensor (channel, x, y, image): 32 channels of bx_s x by_s pixels. */
-__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c, int x, int y, int n)
-{
-    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-                 :: "l"(map), "r"(src), "r"(c), "r"(x), "r"(y), "r"(n) : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-/* every bulk store of this thread has finished READING shared memory (the staging buffer may be rewritten) */
-template <int PENDING>
-__device__ __forceinline__ void tma_store_wait_read()
-{
-    if (PENDING == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-    else              asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-}
-/* every bulk store of this thread is complete */
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-/* generic-proxy writes to shared memory become visible to the async proxy (TMA) */
-__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-/* Brings a tensor map into the copy engine's descriptor cache ahead of its first use. */
-__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map)
-{
-    asm volatile("prefetch.tensormap [%0];" :: "l"(map) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-template <int CTAS>
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols)
-{
-    if (CTAS == 1) asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_dst), "r"(ncols) : "memory");
-    else           asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_dst), "r"(ncols) : "memory");
-}
-
-template <int CTAS>
-__device__ __forceinline__ void tmem_relinquish()
-{
-    if (CTAS == 1) asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    else           asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-
-template <int CTAS>
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols)
-{
-    if (CTAS == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(taddr), "r"(ncols) : "memory");
-    else           asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" :: "r"(taddr), "r"(ncols) : "memory");
-}
-
-/* D(tmem) (+)= A(smem desc) * B(smem desc), issued by one thread. */
-template <int CTAS>
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
-{
-    if (CTAS == 1) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-            :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-    } else {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-            :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-    }
-}
-
-template <int CTAS>
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
-{
-    if (CTAS == 1) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-            :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-    } else {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-            :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-    }
-}
-
-/* Make the barrier observe completion of every tcgen05.mma this thread issued so far.
- * In a CTA pair the arrival is delivered to the same barrier offset in both CTAs. */
-template <int CTAS>
-__device__ __forceinline__ void umma_commit(uint32_t bar)
-{
-    if (CTAS == 1) {
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
-    } else {
-        const uint16_t mask = 3;
-        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-                     :: "r"(bar), "h"(mask) : "memory");
-    }
-}
-
-/* 32 lanes x 32 consecutive fp32 columns of TMEM -> 32 registers per thread. */
-__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float* v)
-{
-    uint32_t* r = reinterpret_cast<uint32_t*>(v);
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-/* Shared-memory matrix descriptor for a K-contiguous tile whose rows are 128 bytes,
- * written by TMA with the 128-byte swizzle: 8-row groups lie 1024 bytes apart (stride
- * byte offset), the leading byte offset is unused for swizzled K-major layouts (set to 1),
- * descriptor version 1 (Blackwell), layout type 2 (128-byte swizzle). */
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr)
-{
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-
-/* Instruction descriptor: D fp32 (bits 4-5 = 1), A and B TF32 (bits 7-9, 10-12 = 2), both
- * K-major (bits 15, 16 = 0), N>>3 at bits 17-22, M>>4 at bits 24-28. */
-/* Same with fp16 operands (format code 0 at bits 7-9 and 10-12), fp32 accumulator. */
-__host__ __device__ constexpr uint32_t make_idesc_f16(int umma_m, int umma_n)
-{
-    return (1u << 4) | ((uint32_t)(umma_n >> 3) << 17) | ((uint32_t)(umma_m >> 4) << 24);
-}
-
-__host__ __device__ constexpr uint32_t make_idesc(int umma_m, int umma_n)
-{
-    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(umma_n >> 3) << 17) | ((uint32_t)(umma_m >> 4) << 24);
-}
 
 struct GemmParams {
     int64_t M, N, K;
@@ -557,6 +330,7 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
         /* ------------------------------------------------------------ TMA producer ---- */
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0;
+            uint32_t armed = 0, armed_parity = 0;     /* per stage: loads issued at least once / parity of the latest */
             bool alive = true;
             for (int t = cluster_id; t < num_tiles && alive; t += num_clusters) {
                 int tm, tn; tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
@@ -602,8 +376,22 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
                             tma_load_2d_pair(stage_b(stage, 1), &map_b_lo, fb, kx, row_b);
                         }
                     }
+                    armed |= 1u << stage;
+                    armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
                     if (CONV && ++cb == p.cblocks) { cb = 0; ++tap; }
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+            /* A wait gave up somewhere: the MMA issuer no longer consumes the stages, but copies this
+             * lane issued may still be on their way into shared memory.  Wait for them (again with a
+             * limit) before the block lets go of it.  The barriers are the leader CTA's and count
+             * both CTAs' bytes, so the leader's wait covers its peer, which leaves only after the
+             * cluster barrier of the teardown. */
+            if (is_leader && *reinterpret_cast<volatile int*>(&p.status->code) != 0) {
+                for (int s2 = 0; s2 < C::STAGES; ++s2) {
+                    if (!((armed >> s2) & 1u)) continue;
+                    for (int tries = 0; tries < 2048 && !mbar_try_wait(full_bar(s2), (armed_parity >> s2) & 1u); ++tries)
+                        __nanosleep(64);
                 }
             }
         }
@@ -636,9 +424,11 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
                             const uint64_t koff = (uint64_t)((kk * UMMA_K * 4) >> 4);
                             const uint32_t first = ((kb - kb0) | kk) != 0 ? 1u : 0u;
                             if (NSPLIT == 3) {
+                                /* a_hi feeds two consecutive MMAs: the first keeps it in the tensor core's
+                                 * collector buffer, the second takes it from there (A_COLLECTOR) */
                                 umma_tf32<CTAS>(tmem_d, da_lo + koff, db_hi + koff, idesc, first);
-                                umma_tf32<CTAS>(tmem_d, da_hi + koff, db_lo + koff, idesc, 1u);
-                                umma_tf32<CTAS>(tmem_d, da_hi + koff, db_hi + koff, idesc, 1u);
+                                umma_tf32<CTAS, A_COLLECTOR ? 1 : 0>(tmem_d, da_hi + koff, db_lo + koff, idesc, 1u);
+                                umma_tf32<CTAS, A_COLLECTOR ? 2 : 0>(tmem_d, da_hi + koff, db_hi + koff, idesc, 1u);
                             } else if (NSPLIT == 16) {
                                 umma_f16<CTAS>(tmem_d, da_hi + koff, db_hi + koff, idesc, first);
                             } else {
@@ -799,7 +589,6 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
     }
 
     /* ---------------------------------------------------------------- teardown -------- */
-    if (*reinterpret_cast<volatile int*>(&p.status->code) != 0) __nanosleep(20000);  /* let copies in flight land */
     tc_fence_before();
     __syncthreads();
     if (CTAS == 2) cluster_sync_all();
@@ -911,30 +700,47 @@ int make_map_conv_dst(decxb_ctx* ctx, CUtensorMap* map, const float* base, int64
     return DECXB_OK;
 }
 
+/* The chunked kernels whose epilogue warps hold 128 running sums move registers between warp
+ * groups (setmaxnreg) and count on exactly 168 registers per thread at launch.  Whether the
+ * toolkit compiled them that way is asked once per device; when it did not, the callers take
+ * the 128 x 128 tile, whose chunked kernel needs no register hand-over and gives the same bits. */
+template <int CTAS, int BN, bool CONV>
+bool chunked_regs_ok(decxb_ctx* ctx)
+{
+    using C = Cfg<CTAS, BN, 3, KCHUNK>;
+    if (C::UMMA_N / 2 <= 64) return true;
+    static std::atomic<int> regs[DECXB_MAX_DEVICES];
+    int r = regs[ctx->device].load();
+    if (r == 0) {
+        cudaFuncAttributes fa;
+        if (cudaFuncGetAttributes(&fa, decxb_gemm_tf32_kernel<CTAS, BN, 3, CONV, KCHUNK>) != cudaSuccess) { cudaGetLastError(); return false; }
+        r = fa.numRegs;
+        regs[ctx->device].store(r);
+    }
+    if (r != 168)
+        decxb_set_error(ctx, "note: chunked " + std::to_string(C::UMMA_M) + "x" + std::to_string(C::UMMA_N) + " kernel compiled to " +
+                             std::to_string(r) + " registers (168 expected); the 128x128 tile is used instead");
+    return r == 168;
+}
+
 template <int CTAS, int BN, int NSPLIT, bool CONV, int KCH = 0>
 int launch_kernel(decxb_ctx* ctx, const CUtensorMap& ma_hi, const CUtensorMap& ma_lo, const CUtensorMap& mb_hi,
                   const CUtensorMap& mb_lo, const CUtensorMap& md, const GemmParams& p, cudaStream_t s)
 {
     using C = Cfg<CTAS, BN, NSPLIT, KCH>;
     auto kernel = decxb_gemm_tf32_kernel<CTAS, BN, NSPLIT, CONV, KCH>;
-    static std::once_flag once[16];
-    static cudaError_t attr_err[16];
-    const int dev = ctx->device & 15;
+    static std::once_flag once[DECXB_MAX_DEVICES];
+    static cudaError_t attr_err[DECXB_MAX_DEVICES];
+    const int dev = ctx->device;           /* decxb_init refuses indices >= DECXB_MAX_DEVICES */
     std::call_once(once[dev], [&] {
         attr_err[dev] = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     });
     if (attr_err[dev] != cudaSuccess)
         return decxb_fail(ctx, DECXB_ERR_CUDA, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(attr_err[dev]));
-    if (KCH > 0 && C::UMMA_N / 2 > 64) {
-        /* the kernel moves registers between its warp groups and counts on 168 per thread at launch */
-        static int regs[16];
-        if (regs[dev] == 0) {
-            cudaFuncAttributes fa;
-            DECXB_CUDA_TRY(ctx, cudaFuncGetAttributes(&fa, kernel));
-            regs[dev] = fa.numRegs;
-        }
-        if (regs[dev] != 168)
-            return decxb_fail(ctx, DECXB_ERR_CUDA, "chunked GEMM kernel compiled to " + std::to_string(regs[dev]) + " registers, 168 expected");
+    /* never launch a register-moving kernel whose register count does not add up: its epilogue would wait forever */
+    if constexpr (KCH > 0 && NSPLIT == 3) {
+        if (!chunked_regs_ok<CTAS, BN, CONV>(ctx))
+            return decxb_fail(ctx, DECXB_ERR_CUDA, "chunked GEMM kernel was not compiled to 168 registers");
     }
     const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
     int64_t clusters = ctx->sm_count / CTAS;
@@ -1125,6 +931,11 @@ int decxb_launch_gemm_tn(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t 
     const bool chunked = a.chunked && decxb_ceil_div(a.K, BK) > 2 * KCHUNK;
     if (a.chunked && !x3) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "chunked accumulation needs the 3xTF32 operands");
     if (chunked) {
+        if ((tile == DECXB_TILE_2CTA_256x256 && !chunked_regs_ok<2, 128, false>(ctx)) ||
+            (tile == DECXB_TILE_1CTA_128x256 && !chunked_regs_ok<1, 256, false>(ctx))) {
+            if (a.nbatch > 1) return decxb_fail(ctx, DECXB_ERR_CUDA, "chunked GEMM kernel was not compiled to 168 registers");
+            tile = DECXB_TILE_1CTA_128x128;
+        }
         switch (tile) {
         case DECXB_TILE_1CTA_128x128: return launch_cfg<1, 128, 3, KCHUNK>(ctx, a, s);
         case DECXB_TILE_2CTA_256x256: return launch_cfg<2, 128, 3, KCHUNK>(ctx, a, s);
@@ -1148,7 +959,7 @@ int decxb_launch_conv_implicit(decxb_ctx* ctx, const decxb_conv_gemm_args& a, cu
     if (a.chunked && !x3) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "chunked accumulation needs the 3xTF32 operands");
     if (a.chunked && a.kW * a.kH * decxb_ceil_div(a.dp, BK) > 2 * KCHUNK) {
         if (a.Np <= 64)  return launch_conv_cfg<1, 64, 3, KCHUNK>(ctx, a, s);
-        if (a.Np <= 128) return launch_conv_cfg<1, 128, 3, KCHUNK>(ctx, a, s);
+        if (a.Np <= 128 || !chunked_regs_ok<2, 128, true>(ctx)) return launch_conv_cfg<1, 128, 3, KCHUNK>(ctx, a, s);
         return launch_conv_cfg<2, 128, 3, KCHUNK>(ctx, a, s);
     }
     if (a.Np <= 64)  return x3 ? launch_conv_cfg<1, 64, 3>(ctx, a, s)  : launch_conv_cfg<1, 64, 1>(ctx, a, s);

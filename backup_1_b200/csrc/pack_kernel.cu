@@ -139,25 +139,28 @@ decxb_im2col_pack_tma_kernel(const __grid_constant__ CUtensorMap src_map, float*
             :: "r"(stage), "l"(&src_map), "r"(b), "r"(0), "r"(x_begin + off_x), "r"(y + off_y), "r"(img) : "memory");
     }
     __syncthreads();
-    /* bounded wait for the load */
-    bool ok = true;
-    {
+    /* Bounded wait for the load.  On expiry the block records where it gave up, then waits once
+     * more, again with a limit, for its own copy (which cannot be cancelled) before it lets go of
+     * the shared memory that copy writes, and stores nothing. */
+    auto wait_load = [&](long long limit_ns) -> bool {
         unsigned long long t0 = 0; uint32_t spins = 0, done = 0;
         while (true) {
             asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                          : "=r"(done) : "r"(b) : "memory");
-            if (done) break;
+            if (done) return true;
             if ((++spins & 255u) == 0) {
                 unsigned long long now; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
                 if (t0 == 0) t0 = now;
-                if ((long long)(now - t0) > wait_limit_ns || *reinterpret_cast<volatile int*>(&status->code) != 0) {
-                    if (atomicCAS(&status->code, 0, DECXB_DEVERR_WAIT_EXPIRED) == 0) {
-                        status->where = 800; status->block = (int)blockIdx.x; status->detail = (int)blockIdx.y;
-                    }
-                    ok = false; break;
-                }
+                if ((long long)(now - t0) > limit_ns) return false;
             }
         }
+    };
+    bool ok = wait_load(wait_limit_ns);
+    if (!ok) {
+        if (atomicCAS(&status->code, 0, DECXB_DEVERR_WAIT_EXPIRED) == 0) {
+            status->where = 800; status->block = (int)blockIdx.x; status->detail = (int)blockIdx.y;
+        }
+        (void)wait_load(wait_limit_ns);
     }
     if (ok) {
         float* o_row = i2c + (int64_t)img * i2c_stride + ((int64_t)y * eq_w + x_begin) * Kp;
@@ -189,8 +192,8 @@ static int launch_pack_tma(decxb_ctx* ctx, const float* src, int64_t H, int64_t 
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return decxb_fail(ctx, DECXB_ERR_CUDA, "cuTensorMapEncodeTiled (pack) failed: " + std::to_string((int)r));
-    static std::once_flag once[16];
-    const int dev = ctx->device & 15;
+    static std::once_flag once[DECXB_MAX_DEVICES];
+    const int dev = ctx->device;
     std::call_once(once[dev], [] {
         cudaFuncSetAttribute(decxb_im2col_pack_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
     });
@@ -234,8 +237,8 @@ int decxb_launch_pack(decxb_ctx* ctx, const float* src, int64_t W, int64_t H, in
         return launch_pack_tma(ctx, src, H, wp, dp, batch, src_stride, (int)kW, (int)kH, off_y, off_x, g, i2c, i2c_stride,
                                grid, stage_bytes, s);
     if (ctx->pack_variant != 2 && stage_bytes <= 112 * 1024) {
-        static std::once_flag once[16];
-        const int dev = ctx->device & 15;
+        static std::once_flag once[DECXB_MAX_DEVICES];
+        const int dev = ctx->device;
         std::call_once(once[dev], [] {
             cudaFuncSetAttribute(decxb_im2col_pack_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
         });

@@ -41,6 +41,11 @@ class Profile(C.Structure):
         return {n: {"ms": self.ms[i], "launches": int(self.launches[i])} for i, n in enumerate(names)}
 
 
+class TensorProbe(C.Structure):
+    _fields_ = [("ms", C.c_double), ("tensor_tflops", C.c_double), ("algorithmic_tflops", C.c_double),
+                ("iterations", C.c_int64), ("sms", C.c_int)]
+
+
 _lib = None
 
 # name -> (restype, argtypes); every symbol include/decxb.h declares
@@ -87,6 +92,8 @@ SIGNATURES = {
     "decxb_selftest_bounded_wait": (_i, [_vp, _i]),
     "decxb_profile_enable": (_i, [_vp, _i]),
     "decxb_profile_read": (_i, [_vp, C.POINTER(Profile)]),
+    "decxb_inject_pipeline_error": (_i, [_vp, _i]),
+    "decxb_probe_tensor_peak": (_i, [_vp, _i, C.c_double, C.POINTER(TensorProbe)]),
     "decxb_version": (C.c_char_p, []),
 }
 
@@ -181,6 +188,13 @@ class Context:
         p = Profile()
         self._chk(self.L.decxb_profile_read(self.h, C.byref(p)))
         return p.as_dict()
+
+    def probe_tensor_peak(self, pattern: int, target_ms: float = 100.0) -> dict:
+        """Tensor-core ceiling probe (see decxb_probe_tensor_peak)."""
+        p = TensorProbe()
+        self._chk(self.L.decxb_probe_tensor_peak(self.h, pattern, float(target_ms), C.byref(p)))
+        return {"ms": p.ms, "tensor_tflops": p.tensor_tflops, "algorithmic_tflops": p.algorithmic_tflops,
+                "iterations": int(p.iterations), "sms": p.sms}
 
     def malloc(self, nbytes: int) -> int:
         p = _vp()

@@ -117,6 +117,9 @@ DECXB_API int decxb_set_wait_limit_ms(decxb_ctx* ctx, int ms);
  * 256-byte aligned, size_t-clean (the reference's `1 << n` int shift breaks at 2 GiB,
  * MemoryPool_D.h:129), thread-safe; freed blocks are cached for reuse. */
 DECXB_API int decxb_malloc(decxb_ctx* ctx, size_t bytes, void** dptr);
+/* Does not wait for the device (cudaFree would): the block is handed out again only after the
+ * work queued on the CONTEXT's stream at the time of the free has finished.  A block used by
+ * work on a caller-supplied stream must be freed only after that stream has been synchronised. */
 DECXB_API int decxb_free(decxb_ctx* ctx, void* dptr);
 /* Return every cached block to the driver: de::release_all_tmp
  * (srcs/core/memory_management/Memory_pool.h:28-38). */
@@ -225,8 +228,17 @@ DECXB_API int decxb_gemm_f32_batched_host(decxb_ctx* ctx, int mode, int tile, in
  *    64 MiB, e.g. 2048 x 2048 x 2048; larger problems return DECXB_ERR_TOO_LARGE and `err`
  *    says how much was asked for.
  *  - It calls no cudaMalloc, cudaFree or other allocating routine.  The first call on a
- *    device makes that device current and resolves the array's device address
- *    (cudaGetSymbolAddress); make that first call before any stream capture begins.
+ *    device resolves the array's device address (cudaGetSymbolAddress) with that device
+ *    current; make that first call before any stream capture begins.  The calling thread's
+ *    current device is the same after the call as before it.
+ *  - Loading device code takes device memory too, and CUDA does it on first use: the first call
+ *    on a device loads the module that carries the array (with CUDA_MODULE_LOADING=EAGER every
+ *    process that initialises CUDA with this library loaded pays the 64 MiB per device at once),
+ *    and the first problem that selects a tile shape not used before loads that kernel.  Warm up
+ *    before the other allocator takes the card: one call per device for each shape used later.
+ *    After that a call leaves the device's free memory unchanged.
+ *  - Calls on the same device take one host lock each; calls on different devices run side
+ *    by side.  `stream`, when given, must belong to `device` (DECXB_ERR_BAD_PARAM otherwise).
  *  - All calls share the one array and it keeps the previous call's contents; the entry
  *    rewrites the parts it uses and clears its status word itself.  It blocks until D is
  *    complete.  Calls that would overlap on the GPU (from several threads or streams) race on
@@ -337,6 +349,31 @@ DECXB_API int decxb_conv2_im2col_f32_batchshard(decxb_ctx* ctx, int mode, int al
                                                 const float* filters, int64_t kW, int64_t kH, int64_t N,
                                                 float* dst, int64_t batch, int64_t src_stride, int64_t dst_stride,
                                                 void* stream, int64_t* first, int64_t* last);
+
+/* Tensor-core ceiling probe: runs nothing but a stream of tcgen05.mma kind::tf32 256 x 256 x 8
+ * instructions (CTA pairs on all SMs, operands resident in shared memory, no TMA, no epilogue)
+ * for about target_ms and reports what the tensor pipe delivered.  pattern 0: one MMA per
+ * k-step, the TF32 issue peak; 1: the three MMAs of the GEMM kernel's 3xTF32 k-step on four
+ * distinct operand tiles, the ceiling its shared-memory operand reads leave; 2: as 1 with a_hi
+ * kept in the collector buffer.  algorithmic_tflops = tensor_tflops / MMAs per k-step, directly
+ * comparable with the GEMM's 2 M N K / t.  The denominators of the benchmark's roofline come
+ * from here.  No counterpart in the reference (it publishes no peak figure). */
+typedef struct decxb_tensor_probe {
+    double ms;                   /* duration of the measured launch                       */
+    double tensor_tflops;        /* flops the tensor pipe executed / ms                   */
+    double algorithmic_tflops;   /* the same divided by the MMAs per k-step (1 or 3)      */
+    int64_t iterations;          /* k-blocks (4 k-steps) issued per CTA pair              */
+    int sms;                     /* SMs that took part                                    */
+} decxb_tensor_probe;
+DECXB_API int decxb_probe_tensor_peak(decxb_ctx* ctx, int pattern, double target_ms, decxb_tensor_probe* out);
+
+/* Host-side fault injection for tests: the CUDA call number `nth_call` (0 = the next one) that a
+ * host-resident pipeline (decxb_gemm_f32_host, _f16_host, _batched_host,
+ * decxb_conv2_im2col_f32_host) makes from now on is not issued and reports a failure instead;
+ * the pipeline must drain its streams, return DECXB_ERR_CUDA and leave the context usable.
+ * nth_call < 0 switches it off.  Nothing on the device faults.  No counterpart in the reference
+ * (its error path prints and exits, srcs/core/error.h:33-42). */
+DECXB_API int decxb_inject_pipeline_error(decxb_ctx* ctx, int nth_call);
 
 /* Number of kernels this library has launched on the context since it was created. */
 DECXB_API uint64_t decxb_kernel_launch_count(decxb_ctx* ctx);

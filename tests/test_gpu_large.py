@@ -1,0 +1,121 @@
+"""Parity at the full sizes of the headline configurations, through the C ABI on a B200.
+
+The oracle cannot compute 32768^3 outputs in seconds, but every output element is its own
+ascending-k fma chain (srcs/GEMM/CUDA/large_squares/GEMM.cuh:53-94), so a sample of rows and
+columns of the device result is compared with the oracle run on exactly those rows of A and
+columns of B.  Operands are generated on the device by the seeded generator that the oracle
+carries a bit-identical twin of.  Bar: max|D - D_ref| / (K max|a| max|b|) <= 1e-6.
+Every test frees what it took (tens of GiB) before it returns.
+"""
+import numpy as np
+import pytest
+import torch
+
+import backup_1_b200 as b
+from oracle import oracle as o
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TOL_3X = 1e-6
+
+
+def _sample_rows(M):
+    """First and last row of the first, a middle and the last 256-row tile, plus neighbours."""
+    mid = (M // 2) // 256 * 256
+    return np.unique(np.array([0, 1, 127, 128, 255, mid, mid + 129, mid + 255, M - 256, M - 129, M - 128, M - 1]))
+
+
+def _sample_cols(N):
+    mid = (N // 2) // 256 * 256
+    return np.concatenate([np.arange(0, 256), np.arange(mid - 64, mid + 192), np.arange(N - 256, N)])
+
+
+def _release(ctx):
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    ctx.release_cached()
+
+
+def _check_sampled(dA, dB, dD, K):
+    M, N = dD.shape
+    rows, cols = _sample_rows(M), _sample_cols(N)
+    A = dA[torch.from_numpy(rows).to(DEV)].cpu().numpy()
+    Bc = dB[:, torch.from_numpy(cols).to(DEV)].contiguous().cpu().numpy()
+    X = dD[torch.from_numpy(rows).to(DEV)][:, torch.from_numpy(cols).to(DEV)].cpu().numpy()
+    assert not np.isnan(X).any()
+    return o.norm_err(X, o.gemm_fmaf(A, Bc), K, 1.0, 1.0)
+
+
+@pytest.mark.parametrize("size", [16384, 32768])
+def test_gemm_square_full_size_sampled_against_fma_chain(ctx, size):
+    """The north-star shape 16384^3 and BASELINE config 5 (32768^3) in both accumulation modes;
+    at 32768 also the row-blocks two ranks of eight would own, through decxb_gemm_f32_rowshard,
+    bit for bit equal to the same rows of the unsharded product."""
+    M = N = K = size
+    try:
+        dA = torch.empty((M, K), device=DEV); dB = torch.empty((K, N), device=DEV)
+        dD = torch.full((M, N), float("nan"), device=DEV)
+        ctx.fill_uniform(dA, M, K, K, 1); ctx.fill_uniform(dB, K, N, N, 2)
+        ctx.gemm(M, N, K, dA, K, dB, N, dD, N, mode=b.GEMM_3XTF32)
+        ctx.synchronize()
+        err_whole = _check_sampled(dA, dB, dD, K)
+        dD.fill_(float("nan"))
+        ctx.gemm(M, N, K, dA, K, dB, N, dD, N)                  # default mode: chunked accumulation
+        ctx.synchronize()
+        err_default = _check_sampled(dA, dB, dD, K)
+        print(f"\n{size}^3: default mode {err_default:.3e}, whole-K mode {err_whole:.3e} of K max|a| max|b|")
+        assert err_default <= TOL_3X and err_whole <= TOL_3X
+        if size == 32768:
+            world = 8
+            for rank in (0, 5):
+                f, l = b.shard_range(M, world, rank)
+                assert (f, l) == (rank * 4096, (rank + 1) * 4096)
+                dS = torch.full((l - f, N), float("nan"), device=DEV)
+                assert ctx.gemm_rowshard(world, rank, M, N, K, dA[f:], K, dB, N, dS, N) == (f, l)
+                ctx.synchronize()
+                assert torch.equal(dS, dD[f:l]), f"row-block of rank {rank} differs from the unsharded rows"
+                del dS
+    finally:
+        dA = dB = dD = None
+        _release(ctx)
+
+
+def test_conv_config4_full_batch(ctx):
+    """BASELINE config 4 at its full batch: 256 images 56x56x256 -> 256 filters 3x3, zero border.
+    Every 37th image (and the last) against the oracle's pack + fma chain; the batched call gives,
+    bit for bit, what one call per image gives; the explicit (pack + GEMM) path agrees within the bar."""
+    W = H = 56; C = 256; F = 256; kW = kH = 3; nb = 256
+    g = b.conv_geometry(W, H, C, kW, kH, F, 1)
+    dp, wp, kwp = C, W, 4
+    try:
+        dS = torch.empty((nb, H, wp, dp), device=DEV)
+        ctx.fill_uniform(dS, nb * H * wp, dp, dp, 4)
+        tmpF = torch.empty((F, kH, kW, dp), device=DEV)
+        ctx.fill_uniform(tmpF, F * kH * kW, dp, dp, 5)
+        ctx.synchronize()
+        dF = torch.zeros((F, kH, kwp, dp), device=DEV)
+        dF[:, :, :kW, :] = tmpF
+        dO = torch.full((nb, g.out_h, g.eq_w, g.Np), float("nan"), device=DEV)
+        ctx.conv2_im2col(dS, W, H, C, dF, kW, kH, F, dO, flag=1, batch=nb, algo=b.CONV_IMPLICIT)
+        ctx.synchronize()
+        assert not torch.isnan(dO).any()
+        flt = dF.cpu().numpy()
+        Kc = kW * kH * C
+        worst = 0.0
+        for i in list(range(0, nb, 37)) + [nb - 1]:
+            R = o.conv2_im2col(dS[i].cpu().numpy(), W, C, flt, kW, 1)
+            worst = max(worst, o.norm_err(dO[i].cpu().numpy(), R.reshape(dO[i].shape), Kc, 1.0, 1.0))
+        print(f"\ncfg4 full batch: worst sampled image {worst:.3e} of K max|a| max|b|")
+        assert worst <= TOL_3X
+        one = torch.empty_like(dO[0])
+        for i in range(nb):
+            ctx.conv2_im2col(dS[i], W, H, C, dF, kW, kH, F, one, flag=1, batch=1, algo=b.CONV_IMPLICIT)
+            ctx.synchronize()
+            assert torch.equal(one, dO[i]), f"image {i}: batched and single-image results differ"
+        dE = torch.full_like(dO, float("nan"))
+        ctx.conv2_im2col(dS, W, H, C, dF, kW, kH, F, dE, flag=1, batch=nb, algo=b.CONV_EXPLICIT)
+        ctx.synchronize()
+        assert float((dE - dO).abs().max()) / Kc <= TOL_3X
+    finally:
+        dS = dF = dO = dE = tmpF = one = None
+        _release(ctx)
