@@ -48,7 +48,7 @@ constexpr int KCHUNK = 4;          /* k-blocks per chunk of the chunked accumula
                                       128 -> 3.3e-7, 256 -> 6.5e-7, 512 -> 1.2e-6, whole K -> 2.9e-6 */
 constexpr int SMEM_LIMIT = 232448; /* 227 KiB opt-in maximum per CTA                        */
 #ifndef DECXB_A_COLLECTOR
-#define DECXB_A_COLLECTOR 0
+#define DECXB_A_COLLECTOR 1
 #endif
 constexpr bool A_COLLECTOR = DECXB_A_COLLECTOR != 0;   /* collector-buffer reuse of a_hi in the 3xTF32 k-step */
 

@@ -39,7 +39,15 @@ def test_reference_arm_times_the_reference_cpu_gemm():
 @pytest.mark.gpu
 def test_gpu_arm_prints_the_contract_line():
     j = run_bench("--workload", "cfg1", "--steps", "5", "--warmup", "3", "--no-cpu-baseline")
-    assert COMMON | {"roofline", "clocks"} <= set(j)
+    assert COMMON | {"roofline", "clocks", "also", "max_norm_err"} <= set(j)
+    assert j["max_norm_err"] <= 1e-6
+    assert {a["workload"] for a in j["also"]} == {"gemm16k", "cfg2", "cfg3", "cfg4"}
+    for a in j["also"]:
+        assert "failed" not in a, a
+        assert a["value"] > 0 and a["max_norm_err"] <= 1e-6
+    assert j["roofline"]["tf32_peak_probe"]["burst_tflops"] > 300 and j["roofline"]["x3_ceiling_probe"]["burst_tflops"] > 100
+    assert j["config"] == run_bench("--impl", "reference", "--workload", "cfg1", "--steps", "1", "--warmup", "1")["config"] \
+        or not o.ref_cpu_available()
     assert j["n_gpus"] == 1 and j["steps"] == 5 and j["warmup"] == 3 and j["vs_baseline"] is None
     assert j["value"] > 0 and j["gpu_launches"] > 0
     rf = j["roofline"]

@@ -745,6 +745,55 @@ def test_bounded_wait_expires_and_context_survives(ctx):
     assert o.norm_err(run_gemm(ctx, A, B), o.gemm_fmaf(A, B), 64, 1.0, 1.0) <= TOL_3X
 
 
+@pytest.mark.parametrize("nth", [0, 4, 9])
+def test_host_pipelines_survive_an_injected_host_side_failure(ctx, nth):
+    """A CUDA call in the middle of a host-resident pipeline reports a failure (injected on the host;
+    nothing on the device faults): the entry returns DECXB_ERR_CUDA after draining its streams, the
+    arena holds no block of the failed call, and the same call then succeeds with the right result."""
+    L = b.load_library()
+    M, N, K = 1500, 2304, 300
+    A = o.fill_uniform(M * K, 1).reshape(M, K); B = o.fill_uniform(K * N, 2).reshape(K, N)
+    R = o.gemm_fmaf(A[:64], B)
+    in_use = ctx.arena_stats().bytes_in_use
+
+    def gemm_host():
+        D = np.full((M, N), np.nan, np.float32)
+        ctx.gemm_host(M, N, K, A, K, B, N, D, N)
+        return D
+
+    def f16_host():
+        Ah, Bh = A.astype(np.float16), B.astype(np.float16)
+        D = np.zeros((M, N), np.float16)
+        ctx.gemm_f16_host(M, N, K, Ah, K, Bh, N, D, N)
+        return D
+
+    def batched_host():
+        nb, m, n, k = 6, 70, 90, 52
+        Ab = o.fill_uniform(nb * m * k, 7).reshape(nb, m, k); Bb = o.fill_uniform(nb * k * n, 8).reshape(nb, k, n)
+        D = np.full((nb, m, n), np.nan, np.float32)
+        ctx.gemm_batched_host(nb, m, n, k, Ab, k, m * k, Bb, n, k * n, D, n, m * n)
+        return D
+
+    def conv_host():
+        W, H, Cc, kW, F, nb = 20, 12, 8, 3, 16, 5
+        src = np.stack([o.make_tensor(W, H, Cc, 40 + i) for i in range(nb)])
+        flt = o.make_filters(kW, kW, Cc, F, 5)
+        return run_conv(ctx, src, W, Cc, flt, kW, 1, algo=b.CONV_IMPLICIT, host=True)
+
+    for call in (gemm_host, f16_host, batched_host, conv_host):
+        good = call()
+        assert L.decxb_inject_pipeline_error(ctx.h, nth) == 0
+        with pytest.raises(b.DecxbError) as e:
+            call()
+        L.decxb_inject_pipeline_error(ctx.h, -1)
+        assert e.value.status == 100
+        ctx.synchronize()
+        assert ctx.arena_stats().bytes_in_use == in_use
+        again = call()
+        assert np.array_equal(good, again, equal_nan=True)
+    assert o.norm_err(gemm_host()[:64], R, K, 1.0, 1.0) <= TOL_3X
+
+
 def test_arena_reuses_blocks(ctx):
     p = ctx.malloc(1 << 20)
     ctx.free(p)
