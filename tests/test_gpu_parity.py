@@ -745,7 +745,7 @@ def test_bounded_wait_expires_and_context_survives(ctx):
     assert o.norm_err(run_gemm(ctx, A, B), o.gemm_fmaf(A, B), 64, 1.0, 1.0) <= TOL_3X
 
 
-@pytest.mark.parametrize("nth", [0, 4, 9])
+@pytest.mark.parametrize("nth", [0, 2, 3])      # the shortest pipeline (fp16) makes four CUDA calls
 def test_host_pipelines_survive_an_injected_host_side_failure(ctx, nth):
     """A CUDA call in the middle of a host-resident pipeline reports a failure (injected on the host;
     nothing on the device faults): the entry returns DECXB_ERR_CUDA after draining its streams, the
