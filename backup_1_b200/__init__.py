@@ -7,6 +7,7 @@ raw device/host pointers.  There is no CPU fallback: if the library is missing o
 sm_100 device is present, calls fail loudly.
 """
 from .lib import (  # noqa: F401
+    Comm,
     Context,
     DecxbError,
     GEMM_1XTF32,

@@ -177,6 +177,83 @@ extern "C" int decxb_inject_pipeline_error(decxb_ctx* ctx, int nth_call)
     return DECXB_OK;
 }
 
+/* ---- B prepared once, used by many products ------------------------------------------------------
+ * Weights are constant across calls in the use this path is for; the hi/lo split and the transposition
+ * of B cost a tenth of a large product and a third of a small one.  A handle keeps the prepared
+ * (K-contiguous, split) operand in arena memory until it is released. */
+struct decxb_prepared_b {
+    decxb_ctx* ctx;
+    int mode;
+    int64_t K, N, ld;
+    float *hi, *lo;
+};
+
+extern "C" int decxb_gemm_prepare_b(decxb_ctx* ctx, int mode, int64_t K, int64_t N, const float* B, int64_t ldb,
+                                    void* stream, decxb_prepared_b** out)
+{
+    if (!out) return DECXB_ERR_BAD_PARAM;
+    *out = nullptr;
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    if (mode != DECXB_GEMM_3XTF32 && mode != DECXB_GEMM_1XTF32 && mode != DECXB_GEMM_3XTF32_STRICT)
+        return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "gemm mode");
+    if (K <= 0 || N <= 0 || !B) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "prepare_b arguments");
+    if (ldb < N) return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
+    cudaStream_t s = pick_stream(ctx, stream);
+    const bool x3 = mode != DECXB_GEMM_1XTF32;
+    const int64_t Kp = decxb_ceil_to(K, 4);
+    float *hi = nullptr, *lo = nullptr;
+    if ((rc = decxb_malloc_on_stream(ctx, (size_t)N * Kp * sizeof(float), (void**)&hi, s))) return rc;
+    if (x3 && (rc = decxb_malloc_on_stream(ctx, (size_t)N * Kp * sizeof(float), (void**)&lo, s))) { decxb_free_on_stream(ctx, hi, s); return rc; }
+    if ((rc = decxb_launch_split_transpose(ctx, B, K, N, ldb, hi, lo, Kp, x3 ? 0 : 1, s))) {
+        decxb_free_on_stream(ctx, hi, s); if (lo) decxb_free_on_stream(ctx, lo, s);
+        return rc;
+    }
+    *out = new decxb_prepared_b{ctx, mode, K, N, Kp, hi, lo};
+    return DECXB_OK;
+}
+
+extern "C" int decxb_gemm_release_b(decxb_ctx* ctx, decxb_prepared_b* pb, void* stream)
+{
+    if (!pb) return DECXB_OK;
+    if (!ctx || pb->ctx != ctx) return DECXB_ERR_BAD_PARAM;
+    cudaStream_t s = pick_stream(ctx, stream);
+    decxb_free_on_stream(ctx, pb->hi, s);
+    if (pb->lo) decxb_free_on_stream(ctx, pb->lo, s);
+    delete pb;
+    return DECXB_OK;
+}
+
+/* Rows of D = A * B (+C) with B prepared (internal form shared with the gathering entry). */
+int decxb_gemm_rows_prepared_b(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
+                               const decxb_prepared_b* pb, const float* C, int64_t ldc, float* D, int64_t ldd, cudaStream_t s,
+                               const float* bias, int act)
+{
+    if (!pb || pb->ctx != ctx) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "prepared operand of another context");
+    if (pb->mode != mode || pb->K != K || pb->N != N) return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "prepared operand does not match the call");
+    if (act < DECXB_ACT_NONE || act > DECXB_ACT_TANH) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "activation");
+    if (M <= 0) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "gemm dims must be positive");
+    if (!A || !D) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null operand");
+    if (lda < K || ldd < N || (C && ldc < N)) return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
+    Scratch scratch(ctx, s);
+    const bool strict = mode == DECXB_GEMM_3XTF32_STRICT;
+    PreparedB p = {pb->hi, pb->lo, pb->ld};
+    int rc = gemm_prepared(ctx, scratch, mode != DECXB_GEMM_1XTF32, tile, M, N, K, A, lda, p, C, ldc, D, ldd, s, bias, act, strict);
+    scratch.release();
+    return rc;
+}
+
+extern "C" int decxb_gemm_f32_prepared(decxb_ctx* ctx, int tile, int64_t M, const float* A, int64_t lda,
+                                       const decxb_prepared_b* pb, const float* C, int64_t ldc,
+                                       const float* bias, int activation, float* D, int64_t ldd, void* stream)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    if (!pb) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null prepared operand");
+    return decxb_gemm_rows_prepared_b(ctx, pb->mode, tile, M, pb->N, pb->K, A, lda, pb, C, ldc, D, ldd, pick_stream(ctx, stream),
+                                      bias, activation);
+}
+
 extern "C" int decxb_gemm_f32(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_t K,
                               const float* A, int64_t lda, const float* B, int64_t ldb,
                               const float* C, int64_t ldc, float* D, int64_t ldd, void* stream)

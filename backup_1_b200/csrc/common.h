@@ -59,6 +59,7 @@ struct decxb_ctx {
     long long wait_limit_ns = 2000000000LL;
     int pack_variant = 0;               /* 0 = copy-engine (TMA) pack, 1 = shared-memory staged, 2 = direct */
     std::atomic<uint64_t> launches{0};
+    int reserved_sms = 0;               /* SMs the next GEMM launches leave free (a transfer kernel runs beside them) */
     int inject_countdown = -1;          /* >= 0: that many pipeline CUDA calls from now, one reports a failure (tests) */
     std::string last_error;
     /* per-kernel event timing (decxb_profile_*) */
@@ -161,6 +162,11 @@ struct decxb_conv_gemm_args {
     int chunked;                      /* as decxb_gemm_args::chunked */
 };
 int decxb_launch_conv_implicit(decxb_ctx* ctx, const decxb_conv_gemm_args& a, cudaStream_t s);
+
+/* Rows of D = A * B (+C) (+bias, activation) with B prepared by decxb_gemm_prepare_b. */
+int decxb_gemm_rows_prepared_b(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
+                               const decxb_prepared_b* pb, const float* C, int64_t ldc, float* D, int64_t ldd, cudaStream_t s,
+                               const float* bias = nullptr, int act = DECXB_ACT_NONE);
 
 /* cuTensorMapEncodeTiled, resolved through cudaGetDriverEntryPoint (NULL if unavailable). */
 void* decxb_tensor_map_encoder();

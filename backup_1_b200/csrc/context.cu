@@ -22,6 +22,7 @@ extern "C" const char* decxb_status_string(int status)
     case DECXB_ERR_ARCH: return "device is not compute capability 10.x (sm_100a code only)";
     case DECXB_ERR_TIMEOUT: return "a bounded device-side wait expired";
     case DECXB_ERR_TOO_LARGE: return "request exceeds a fixed limit";
+    case DECXB_ERR_COMM: return "communication library failure";
     default: return "unknown status";
     }
 }

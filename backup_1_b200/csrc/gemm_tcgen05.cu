@@ -743,7 +743,7 @@ int launch_kernel(decxb_ctx* ctx, const CUtensorMap& ma_hi, const CUtensorMap& m
             return decxb_fail(ctx, DECXB_ERR_CUDA, "chunked GEMM kernel was not compiled to 168 registers");
     }
     const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
-    int64_t clusters = ctx->sm_count / CTAS;
+    int64_t clusters = (ctx->sm_count - ctx->reserved_sms) / CTAS;
     if (clusters > tiles) clusters = tiles;
     if (clusters < 1) clusters = 1;
     cudaLaunchConfig_t cfg = {};

@@ -93,6 +93,18 @@ SIGNATURES = {
     "decxb_profile_enable": (_i, [_vp, _i]),
     "decxb_profile_read": (_i, [_vp, C.POINTER(Profile)]),
     "decxb_inject_pipeline_error": (_i, [_vp, _i]),
+    "decxb_gemm_prepare_b": (_i, [_vp, _i, _i64, _i64, _vp, _i64, _vp, C.POINTER(_vp)]),
+    "decxb_gemm_f32_prepared": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _i, _vp, _i64, _vp]),
+    "decxb_gemm_release_b": (_i, [_vp, _vp, _vp]),
+    "decxb_comm_unique_id": (_i, [_vp]),
+    "decxb_comm_init": (_i, [_vp, _i, _i, _vp, _i, C.POINTER(_vp)]),
+    "decxb_comm_destroy": (_i, [_vp]),
+    "decxb_comm_last_error": (C.c_char_p, [_vp]),
+    "decxb_comm_set_reserved_sms": (_i, [_vp, _i]),
+    "decxb_comm_synchronize": (_i, [_vp]),
+    "decxb_comm_allgather_blocks": (_i, [_vp, _vp, _sz, _i64, _vp]),
+    "decxb_gemm_f32_rowshard_gather": (_i, [_vp, _vp, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i, _vp]),
+    "decxb_comm_selftest_handshake": (_i, [C.c_char_p, _i, _i, _vp, _i, C.c_char_p, _sz]),
     "decxb_probe_tensor_peak": (_i, [_vp, _i, C.c_double, C.POINTER(TensorProbe)]),
     "decxb_version": (C.c_char_p, []),
 }
@@ -249,6 +261,19 @@ class Context:
         self._chk(self.L.decxb_gemm_f32_batched_host(self.h, mode, tile, batch, M, N, K, _ptr(A), lda, sA, _ptr(B), ldb, sB,
                                                      _ptr(Cin), ldc, sC, _ptr(D), ldd, sD))
 
+    def prepare_b(self, K, N, B, ldb, mode=GEMM_DEFAULT, stream=None) -> int:
+        """Splits and transposes B once (decxb_gemm_prepare_b); returns the handle."""
+        h = _vp()
+        self._chk(self.L.decxb_gemm_prepare_b(self.h, mode, K, N, _ptr(B), ldb, stream, C.byref(h)))
+        return h.value
+
+    def gemm_prepared(self, M, A, lda, pb, D, ldd, Cin=None, ldc=0, bias=None, act=ACT_NONE, tile=TILE_AUTO, stream=None):
+        self._chk(self.L.decxb_gemm_f32_prepared(self.h, tile, M, _ptr(A), lda, pb, _ptr(Cin), ldc, _ptr(bias), act,
+                                                 _ptr(D), ldd, stream))
+
+    def release_b(self, pb, stream=None):
+        self._chk(self.L.decxb_gemm_release_b(self.h, pb, stream))
+
     # -- convolution ----------------------------------------------------------------------
     def set_pack_variant(self, variant: int):
         self._chk(self.L.decxb_set_pack_variant(self.h, variant))
@@ -291,3 +316,47 @@ class Context:
                           src_stride=0, dst_stride=0, mode=GEMM_DEFAULT, algo=CONV_EXPLICIT):
         self._chk(self.L.decxb_conv2_im2col_f32_host(self.h, mode, algo, flag, _ptr(src), W, H, depth, _ptr(filters),
                                                      kW, kH, N, _ptr(dst), batch, src_stride, dst_stride))
+
+
+class Comm:
+    """A communicator over NCCL for gathering the blocks of a sharded result (decxb_comm_*).
+    Rank 0 makes the id with Comm.unique_id() and hands the 128 bytes to the other ranks."""
+
+    def __init__(self, ctx: Context, world: int, rank: int, uid: bytes, timeout_ms: int = 30000):
+        self.ctx, self.L = ctx, ctx.L
+        h = _vp()
+        buf = C.create_string_buffer(bytes(uid), 128)
+        rc = self.L.decxb_comm_init(ctx.h, world, rank, buf, timeout_ms, C.byref(h))
+        if rc:
+            raise DecxbError(rc, self.L.decxb_last_error(ctx.h).decode() or self.L.decxb_status_string(rc).decode())
+        self.h, self.world, self.rank = h, world, rank
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = C.create_string_buffer(128)
+        rc = load_library().decxb_comm_unique_id(buf)
+        if rc:
+            raise DecxbError(rc, "decxb_comm_unique_id (is libnccl.so.2 loadable?)")
+        return buf.raw
+
+    def _chk(self, rc):
+        if rc:
+            raise DecxbError(rc, self.L.decxb_comm_last_error(self.h).decode() or self.L.decxb_status_string(rc).decode())
+
+    def set_reserved_sms(self, sms: int):
+        self._chk(self.L.decxb_comm_set_reserved_sms(self.h, sms))
+
+    def synchronize(self):
+        self._chk(self.L.decxb_comm_synchronize(self.h))
+
+    def allgather_blocks(self, base, unit_bytes: int, total_units: int, stream=None):
+        self._chk(self.L.decxb_comm_allgather_blocks(self.h, _ptr(base), unit_bytes, total_units, stream))
+
+    def gemm_rowshard_gather(self, M, N, K, A_rows, lda, B, ldb, D_full, groups=4, mode=GEMM_DEFAULT, tile=TILE_AUTO, stream=None):
+        self._chk(self.L.decxb_gemm_f32_rowshard_gather(self.ctx.h, self.h, mode, tile, M, N, K, _ptr(A_rows), lda, _ptr(B), ldb,
+                                                        _ptr(D_full), groups, stream))
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.L.decxb_comm_destroy(self.h)
+            self.h = None

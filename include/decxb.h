@@ -46,7 +46,8 @@ typedef enum decxb_status {
     DECXB_ERR_NO_DEVICE    = 101,
     DECXB_ERR_ARCH         = 102, /* device is not compute capability 10.x                              */
     DECXB_ERR_TIMEOUT      = 103, /* a bounded device-side wait expired; the context stays usable       */
-    DECXB_ERR_TOO_LARGE    = 104  /* request exceeds a documented fixed limit                           */
+    DECXB_ERR_TOO_LARGE    = 104, /* request exceeds a documented fixed limit                           */
+    DECXB_ERR_COMM         = 105  /* the communication library failed or could not be loaded            */
 } decxb_status;
 
 /* Precision of the tensor-core GEMM.  3xTF32 (default) splits every fp32 operand into a
@@ -216,6 +217,23 @@ DECXB_API int decxb_gemm_f32_batched_host(decxb_ctx* ctx, int mode, int tile, in
                                           const float* hC, int64_t ldc, int64_t strideC,
                                           float* hD, int64_t ldd, int64_t strideD);
 
+/* B prepared once for many products.  In the use this path is made for, B holds weights that
+ * stay the same from call to call, while every call of decxb_gemm_f32 splits and transposes it
+ * again (a tenth of the time of a large product, a third of a small one).  decxb_gemm_prepare_b
+ * does that work once, into arena memory owned by the handle; decxb_gemm_f32_prepared then
+ * computes D[M][N] = act(A[M][K] * B (+C) (+bias[column])) with results bit-identical to
+ * decxb_gemm_f32 / decxb_gemm_f32_act in the handle's mode; decxb_gemm_release_b gives the memory
+ * back (in stream order on `stream`).  The handle is bound to its context; B may be overwritten
+ * once decxb_gemm_prepare_b's work on `stream` has run.  No counterpart in the reference, which
+ * re-stages both operands on every call (srcs/GEMM/CUDA/large_squares/GEMM.h:398-454). */
+typedef struct decxb_prepared_b decxb_prepared_b;
+DECXB_API int decxb_gemm_prepare_b(decxb_ctx* ctx, int mode, int64_t K, int64_t N, const float* B, int64_t ldb,
+                                   void* stream, decxb_prepared_b** out);
+DECXB_API int decxb_gemm_f32_prepared(decxb_ctx* ctx, int tile, int64_t M, const float* A, int64_t lda,
+                                      const decxb_prepared_b* B, const float* C, int64_t ldc,
+                                      const float* bias, int activation, float* D, int64_t ldd, void* stream);
+DECXB_API int decxb_gemm_release_b(decxb_ctx* ctx, decxb_prepared_b* B, void* stream);
+
 /* The 3xTF32 product D = A*B (+C) of decxb_gemm_f32 for callers that must not allocate
  * device memory (this entry has no counterpart in the reference).  Such callers exist: a
  * process in which a framework's caching pool has reserved the whole card, so that a
@@ -329,8 +347,8 @@ DECXB_API int decxb_profile_read(decxb_ctx* ctx, decxb_profile* out);
  * The reference is single-GPU ("supports only single GPU", DECX_cpu/DECX_CPU.cpp:9); these
  * entries have no counterpart there.  The path shards into independent units: GEMM by rows of A
  * and C (B replicated), the convolution by images (filters replicated).  No data crosses
- * ranks to compute; gathering the result blocks is the caller's collective (the benchmark
- * uses torch.distributed all-gather over NCCL).
+ * ranks to compute; gathering the result blocks, when the caller wants the whole result on every
+ * rank, is what the decxb_comm_* entries further down do.
  *
  * decxb_shard_range: units [first, last) of `total` owned by `rank` of `world`; contiguous
  * blocks, the first total % world ranks own one unit more.
@@ -374,6 +392,47 @@ DECXB_API int decxb_probe_tensor_peak(decxb_ctx* ctx, int pattern, double target
  * nth_call < 0 switches it off.  Nothing on the device faults.  No counterpart in the reference
  * (its error path prints and exits, srcs/core/error.h:33-42). */
 DECXB_API int decxb_inject_pipeline_error(decxb_ctx* ctx, int nth_call);
+
+/* ---- gathering the blocks of a sharded result (NCCL over NVLink) ---------------------------
+ * No counterpart in the reference (single GPU).  The shards above need no communication; these
+ * entries serve callers that want the WHOLE result on every rank.  NCCL is loaded at run time
+ * (libnccl.so.2, or the file the environment variable DECXB_NCCL_LIB names); a process that
+ * never calls them never loads it.
+ *
+ * decxb_comm_unique_id: 128 bytes that rank 0 creates and hands to every rank by its own means
+ *   (a file, a socket, MPI, torch.distributed).
+ * decxb_comm_init: joins `world` ranks, one per GPU; blocks until all have joined or timeout_ms
+ *   (<= 0: 30 s) has passed, then DECXB_ERR_TIMEOUT.  The same limit bounds every later wait on
+ *   this communicator; after a timeout or an NCCL error the communicator has been aborted and
+ *   only decxb_comm_destroy may be called on it.
+ * decxb_comm_allgather_blocks: `base` holds total_units units of unit_bytes each, laid out alike
+ *   on every rank; the rank's own units (decxb_shard_range) are valid, the others arrive.  Ordered
+ *   after the work queued on `stream`, and `stream` continues after the transfer (no host wait).
+ * decxb_gemm_f32_rowshard_gather: this rank's rows of D = A * B computed in `groups` row-panel
+ *   groups (1..64) straight into D_full[M][N] (dense, leading dimension N), each group sent to
+ *   the peers while the next is multiplied; on return everything is queued, and `stream`
+ *   continues only after all rows of D_full have arrived.  groups = 1 computes, then gathers.
+ *   While transfers run, the GEMM leaves decxb_comm_set_reserved_sms SMs (default 16) to
+ *   NCCL's kernels.  A_rows points at the rank's first row; B is the whole matrix.
+ * decxb_comm_synchronize: waits (bounded) until the transfers queued so far have finished. */
+#define DECXB_COMM_ID_BYTES 128
+typedef struct decxb_comm decxb_comm;
+DECXB_API int decxb_comm_unique_id(void* id128);
+DECXB_API int decxb_comm_init(decxb_ctx* ctx, int world, int rank, const void* id128, int timeout_ms, decxb_comm** out);
+DECXB_API int decxb_comm_destroy(decxb_comm* comm);
+DECXB_API const char* decxb_comm_last_error(decxb_comm* comm);
+DECXB_API int decxb_comm_set_reserved_sms(decxb_comm* comm, int sms);
+DECXB_API int decxb_comm_synchronize(decxb_comm* comm);
+DECXB_API int decxb_comm_allgather_blocks(decxb_comm* comm, void* base, size_t unit_bytes, int64_t total_units, void* stream);
+DECXB_API int decxb_gemm_f32_rowshard_gather(decxb_ctx* ctx, decxb_comm* comm, int mode, int tile,
+                                             int64_t M, int64_t N, int64_t K,
+                                             const float* A_rows, int64_t lda, const float* B, int64_t ldb,
+                                             float* D_full, int groups, void* stream);
+/* Failure-detection self-test on the host: the joining half of decxb_comm_init (load the library at
+ * nccl_path, non-blocking init, bounded poll, abort on expiry) with no CUDA call, so that a rank
+ * which never arrives can be played by a stand-in library on a machine without a GPU. */
+DECXB_API int decxb_comm_selftest_handshake(const char* nccl_path, int world, int rank, const void* id128, int timeout_ms,
+                                            char* err, size_t err_len);
 
 /* Number of kernels this library has launched on the context since it was created. */
 DECXB_API uint64_t decxb_kernel_launch_count(decxb_ctx* ctx);
