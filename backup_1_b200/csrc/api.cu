@@ -39,7 +39,7 @@ struct PreparedB { const float* hi; const float* lo; int64_t ld; };
 int prepare_b(decxb_ctx* ctx, Scratch& scratch, bool x3, int64_t N, int64_t K,
               const float* B, int64_t ldb, bool b_is_nt, cudaStream_t s, PreparedB* out)
 {
-    const int64_t Kp = decxb_ceil_to(K, 4);
+    const int64_t Kp = decxb_split_pitch(K);
     int rc;
     if (b_is_nt && !x3 && tma_ok(B, ldb)) { out->hi = B; out->lo = nullptr; out->ld = ldb; return DECXB_OK; }
     float *hi = nullptr, *lo = nullptr;
@@ -61,7 +61,7 @@ int gemm_prepared(decxb_ctx* ctx, Scratch& scratch, bool x3, int tile, int64_t M
                   const float* C, int64_t ldc, float* D, int64_t ldd, cudaStream_t s,
                   const float* bias = nullptr, int act = DECXB_ACT_NONE, bool chunked = false)
 {
-    const int64_t Kp = decxb_ceil_to(K, 4);
+    const int64_t Kp = decxb_split_pitch(K);
     decxb_gemm_args g = {};
     g.chunked = chunked ? 1 : 0;
     g.M = M; g.N = N; g.K = K; g.C = C; g.ldc = ldc; g.D = D; g.ldd = ldd; g.tile = tile; g.b_rows = N;
@@ -96,8 +96,30 @@ int gemm_device(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_
     /* the strict mode is the 3xTF32 product with K accumulated in chunks (see gemm_tcgen05.cu) */
     const bool strict = mode == DECXB_GEMM_3XTF32_STRICT;
     const bool x3 = mode == DECXB_GEMM_3XTF32 || strict;
+    int rc;
+    if (x3 && !b_is_nt && (M + N) * K <= ((int64_t)1 << 25)) {
+        /* small product: both operand splits in one launch */
+        const int64_t Kp = decxb_split_pitch(K);
+        float *a_hi = nullptr, *a_lo = nullptr, *b_hi = nullptr, *b_lo = nullptr;
+        if ((rc = scratch.get((size_t)M * Kp * 4, (void**)&a_hi)) || (rc = scratch.get((size_t)M * Kp * 4, (void**)&a_lo)) ||
+            (rc = scratch.get((size_t)N * Kp * 4, (void**)&b_hi)) || (rc = scratch.get((size_t)N * Kp * 4, (void**)&b_lo))) return rc;
+        if (decxb_split_ab_possible(B, ldb, b_hi, b_lo)) {
+            if ((rc = decxb_launch_split_ab(ctx, A, M, K, lda, a_hi, a_lo, B, N, ldb, b_hi, b_lo, Kp, s))) return rc;
+        } else {
+            if ((rc = decxb_launch_split_rows(ctx, A, M, K, lda, a_hi, a_lo, Kp, M, s))) return rc;
+            if ((rc = decxb_launch_split_transpose(ctx, B, K, N, ldb, b_hi, b_lo, Kp, 0, s))) return rc;
+        }
+        decxb_gemm_args g = {};
+        g.chunked = strict ? 1 : 0;
+        g.M = M; g.N = N; g.K = K; g.C = C; g.ldc = ldc; g.D = D; g.ldd = ldd; g.tile = tile; g.b_rows = N;
+        g.a_hi = a_hi; g.a_lo = a_lo; g.lda = Kp; g.b_hi = b_hi; g.b_lo = b_lo; g.ldb = Kp;
+        g.bias = bias; g.act = act;
+        rc = decxb_launch_gemm_tn(ctx, g, s);
+        scratch.release();
+        return rc;
+    }
     PreparedB pb;
-    int rc = prepare_b(ctx, scratch, x3, N, K, B, ldb, b_is_nt, s, &pb);
+    rc = prepare_b(ctx, scratch, x3, N, K, B, ldb, b_is_nt, s, &pb);
     if (rc == DECXB_OK) rc = gemm_prepared(ctx, scratch, x3, tile, M, N, K, A, lda, pb, C, ldc, D, ldd, s, bias, act, strict);
     scratch.release();
     return rc;
@@ -201,7 +223,7 @@ extern "C" int decxb_gemm_prepare_b(decxb_ctx* ctx, int mode, int64_t K, int64_t
     if (ldb < N) return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
     cudaStream_t s = pick_stream(ctx, stream);
     const bool x3 = mode != DECXB_GEMM_1XTF32;
-    const int64_t Kp = decxb_ceil_to(K, 4);
+    const int64_t Kp = decxb_split_pitch(K);
     float *hi = nullptr, *lo = nullptr;
     if ((rc = decxb_malloc_on_stream(ctx, (size_t)N * Kp * sizeof(float), (void**)&hi, s))) return rc;
     if (x3 && (rc = decxb_malloc_on_stream(ctx, (size_t)N * Kp * sizeof(float), (void**)&lo, s))) { decxb_free_on_stream(ctx, hi, s); return rc; }
@@ -307,7 +329,7 @@ extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M
     ChunkEvents evs;
     const bool strict = mode == DECXB_GEMM_3XTF32_STRICT;
     const bool x3 = mode == DECXB_GEMM_3XTF32 || strict;
-    const int64_t Kp = decxb_ceil_to(K, 4), Np = decxb_ceil_to(N, 4);
+    const int64_t Kp = decxb_split_pitch(K), Np = decxb_ceil_to(N, 4);
     float *dA, *dB, *dC = nullptr, *dD, *b_hi = nullptr, *b_lo = nullptr;
     if ((rc = scratch.get((size_t)M * Kp * 4, (void**)&dA))) return rc;
     if ((rc = scratch.get((size_t)K * Np * 4, (void**)&dB))) return rc;
@@ -473,7 +495,7 @@ static int gemm_batched_device(decxb_ctx* ctx, int mode, int tile, int64_t batch
     if (tile == DECXB_TILE_AUTO) tile = decxb_pick_tile(ctx, M, N, batch);
     int tm = 128, tn = 128;
     decxb_tile_shape(tile, &tm, &tn);
-    const int64_t Kp = decxb_ceil_to(K, 4), m_pad = decxb_ceil_to(M, tm), n_pad = decxb_ceil_to(N, tn);
+    const int64_t Kp = decxb_split_pitch(K), m_pad = decxb_ceil_to(M, tm), n_pad = decxb_ceil_to(N, tn);
     Scratch scratch(ctx, s);
     float *a_hi = nullptr, *a_lo = nullptr, *b_hi = nullptr, *b_lo = nullptr;
     int rc;
@@ -605,19 +627,27 @@ extern "C" int decxb_im2col_pack_f32(decxb_ctx* ctx, const float* src, int64_t W
     return decxb_launch_pack(ctx, src, W, H, depth, kW, kH, flag, i2c, batch, src_stride, i2c_stride, pick_stream(ctx, stream));
 }
 
+/* Filter bank prepared once (gathered into the filter matrix of the chosen algorithm, split into hi/lo). */
+struct decxb_prepared_filters {
+    decxb_ctx* ctx;
+    int mode, algo;
+    int64_t kW, kH, depth, N, ld;      /* ld: columns of the filter matrix */
+    float *hi, *lo;
+};
+
 namespace {
 
 int conv_device(decxb_ctx* ctx, int mode, int algo, int flag,
                 const float* src, int64_t W, int64_t H, int64_t depth,
                 const float* filters, int64_t kW, int64_t kH, int64_t N,
                 float* dst, int64_t batch, int64_t src_stride, int64_t dst_stride, cudaStream_t s,
-                const float* bias = nullptr, int act = DECXB_ACT_NONE)
+                const float* bias = nullptr, int act = DECXB_ACT_NONE, const decxb_prepared_filters* pf = nullptr)
 {
     if (mode != DECXB_GEMM_3XTF32 && mode != DECXB_GEMM_1XTF32 && mode != DECXB_GEMM_3XTF32_STRICT)
         return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "gemm mode");
     if (act < DECXB_ACT_NONE || act > DECXB_ACT_TANH) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "activation");
     if (algo != DECXB_CONV_EXPLICIT && algo != DECXB_CONV_IMPLICIT) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "conv algo");
-    if (!src || !filters || !dst) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null tensor");
+    if (!src || (!filters && !pf) || !dst) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null tensor");
     decxb_conv_geom g;
     int rc = decxb_conv_geometry(W, H, depth, kW, kH, N, flag, &g);
     if (rc) return decxb_fail(ctx, rc, "convolution geometry");
@@ -636,9 +666,12 @@ int conv_device(decxb_ctx* ctx, int mode, int algo, int flag,
         if (H * wp * dp > 0x7fffffffffLL || batch > 0x7fffffffLL) return decxb_fail(ctx, DECXB_ERR_TOO_LARGE, "tensor");
         const int64_t cp = decxb_ceil_to(dp, 32), Kc = kW * kH * cp;
         float *k_hi = nullptr, *k_lo = nullptr, *s_hi = nullptr, *s_lo = nullptr;
-        if ((rc = scratch.get((size_t)g.Np * Kc * 4, (void**)&k_hi))) return rc;
-        if (x3 && (rc = scratch.get((size_t)g.Np * Kc * 4, (void**)&k_lo))) return rc;
-        if ((rc = decxb_launch_filter_matrix(ctx, filters, kW, kH, depth, N, k_hi, k_lo, g.Np, Kc, x3 ? 0 : 1, s, cp))) return rc;
+        if (pf) { k_hi = pf->hi; k_lo = pf->lo; }
+        else {
+            if ((rc = scratch.get((size_t)g.Np * Kc * 4, (void**)&k_hi))) return rc;
+            if (x3 && (rc = scratch.get((size_t)g.Np * Kc * 4, (void**)&k_lo))) return rc;
+            if ((rc = decxb_launch_filter_matrix(ctx, filters, kW, kH, depth, N, k_hi, k_lo, g.Np, Kc, x3 ? 0 : 1, s, cp))) return rc;
+        }
         decxb_conv_gemm_args a = {};
         const int64_t img = H * wp * dp;
         if (x3) {
@@ -669,9 +702,12 @@ int conv_device(decxb_ctx* ctx, int mode, int algo, int flag,
 
     /* filter matrix [Np][Kp] (hi/lo), rows >= N zero so padding channels come out 0 */
     float *k_hi = nullptr, *k_lo = nullptr;
-    if ((rc = scratch.get((size_t)g.Np * g.Kp * 4, (void**)&k_hi))) return rc;
-    if (x3 && (rc = scratch.get((size_t)g.Np * g.Kp * 4, (void**)&k_lo))) return rc;
-    if ((rc = decxb_launch_filter_matrix(ctx, filters, kW, kH, depth, N, k_hi, k_lo, g.Np, g.Kp, x3 ? 0 : 1, s))) return rc;
+    if (pf) { k_hi = pf->hi; k_lo = pf->lo; }
+    else {
+        if ((rc = scratch.get((size_t)g.Np * g.Kp * 4, (void**)&k_hi))) return rc;
+        if (x3 && (rc = scratch.get((size_t)g.Np * g.Kp * 4, (void**)&k_lo))) return rc;
+        if ((rc = decxb_launch_filter_matrix(ctx, filters, kW, kH, depth, N, k_hi, k_lo, g.Np, g.Kp, x3 ? 0 : 1, s))) return rc;
+    }
 
     /* images are processed in groups so that the column matrix of a group stays a few hundred MB */
     const int64_t i2c_bytes_img = g.M * g.Kp * 4;
@@ -727,6 +763,55 @@ int conv_device(decxb_ctx* ctx, int mode, int algo, int flag,
 
 }  // namespace
 
+extern "C" int decxb_conv_prepare_filters(decxb_ctx* ctx, int mode, int algo, const float* filters, int64_t kW, int64_t kH,
+                                          int64_t depth, int64_t N, void* stream, decxb_prepared_filters** out)
+{
+    if (!out) return DECXB_ERR_BAD_PARAM;
+    *out = nullptr;
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    if (mode != DECXB_GEMM_3XTF32 && mode != DECXB_GEMM_1XTF32 && mode != DECXB_GEMM_3XTF32_STRICT)
+        return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "gemm mode");
+    if (algo != DECXB_CONV_EXPLICIT && algo != DECXB_CONV_IMPLICIT) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "conv algo");
+    decxb_conv_geom g;
+    if (!filters || (rc = decxb_conv_geometry(2 * kW, 2 * kH, depth, kW, kH, N, DECXB_CONV_ZERO_COMPENSATE, &g)))
+        return decxb_fail(ctx, rc ? rc : DECXB_ERR_BAD_PARAM, "filter bank");
+    cudaStream_t s = pick_stream(ctx, stream);
+    const bool x3 = mode != DECXB_GEMM_1XTF32;
+    const int64_t dp = decxb_ceil_to(depth, 4);
+    const int64_t cp = algo == DECXB_CONV_IMPLICIT ? decxb_ceil_to(dp, 32) : dp;
+    const int64_t ld = kW * kH * cp;
+    float *hi = nullptr, *lo = nullptr;
+    if ((rc = decxb_malloc_on_stream(ctx, (size_t)g.Np * ld * 4, (void**)&hi, s))) return rc;
+    if (x3 && (rc = decxb_malloc_on_stream(ctx, (size_t)g.Np * ld * 4, (void**)&lo, s))) { decxb_free_on_stream(ctx, hi, s); return rc; }
+    rc = decxb_launch_filter_matrix(ctx, filters, kW, kH, depth, N, hi, lo, g.Np, ld, x3 ? 0 : 1, s, algo == DECXB_CONV_IMPLICIT ? cp : 0);
+    if (rc) { decxb_free_on_stream(ctx, hi, s); if (lo) decxb_free_on_stream(ctx, lo, s); return rc; }
+    *out = new decxb_prepared_filters{ctx, mode, algo, kW, kH, depth, N, ld, hi, lo};
+    return DECXB_OK;
+}
+
+extern "C" int decxb_conv_release_filters(decxb_ctx* ctx, decxb_prepared_filters* pf, void* stream)
+{
+    if (!pf) return DECXB_OK;
+    if (!ctx || pf->ctx != ctx) return DECXB_ERR_BAD_PARAM;
+    cudaStream_t s = pick_stream(ctx, stream);
+    decxb_free_on_stream(ctx, pf->hi, s);
+    if (pf->lo) decxb_free_on_stream(ctx, pf->lo, s);
+    delete pf;
+    return DECXB_OK;
+}
+
+extern "C" int decxb_conv2_im2col_f32_prepared(decxb_ctx* ctx, int flag, const float* src, int64_t W, int64_t H,
+                                               const decxb_prepared_filters* pf, const float* bias, int activation,
+                                               float* dst, int64_t batch, int64_t src_stride, int64_t dst_stride, void* stream)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    if (!pf || pf->ctx != ctx) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "prepared filters of another context");
+    return conv_device(ctx, pf->mode, pf->algo, flag, src, W, H, pf->depth, nullptr, pf->kW, pf->kH, pf->N, dst, batch, src_stride,
+                       dst_stride, pick_stream(ctx, stream), bias, activation, pf);
+}
+
 extern "C" int decxb_conv2_im2col_f32(decxb_ctx* ctx, int mode, int algo, int flag,
                                       const float* src, int64_t W, int64_t H, int64_t depth,
                                       const float* filters, int64_t kW, int64_t kH, int64_t N,
@@ -779,6 +864,14 @@ extern "C" int decxb_conv2_im2col_f32_host(decxb_ctx* ctx, int mode, int algo, i
     if ((rc = fence_copy_streams(ctx, evs))) return rc;
     auto fail = [&](int code) { drain_all_streams(ctx); return code; };
     PIPE_TRY(cudaMemcpyAsync(d_flt, h_filters, (size_t)N * kH * kwp * dp * 4, cudaMemcpyHostToDevice, up));
+    /* the filter matrix is built once for all image groups, as soon as the bank has landed */
+    cudaEvent_t e_flt = evs.make();
+    if (!e_flt) return fail(decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"));
+    PIPE_TRY(cudaEventRecord(e_flt, up));
+    PIPE_TRY(cudaStreamWaitEvent(s, e_flt, 0));
+    decxb_prepared_filters* pf = nullptr;
+    if ((rc = decxb_conv_prepare_filters(ctx, mode, algo, d_flt, kW, kH, depth, N, s, &pf))) return fail(rc);
+    struct PfGuard { decxb_ctx* c; decxb_prepared_filters* p; cudaStream_t st; ~PfGuard() { decxb_conv_release_filters(c, p, st); } } pf_guard{ctx, pf, s};
     /* many small groups: the first upload and the last download are not overlapped with anything,
      * so they should be short; 1/32 of the batch, but at least 8 MiB per copy */
     int64_t group = decxb_ceil_div(batch, 32);
@@ -793,8 +886,8 @@ extern "C" int decxb_conv2_im2col_f32_host(decxb_ctx* ctx, int mode, int algo, i
                                              src_img * 4, nb, cudaMemcpyHostToDevice, up));
         PIPE_TRY(cudaEventRecord(e_up, up));
         PIPE_TRY(cudaStreamWaitEvent(s, e_up, 0));
-        rc = conv_device(ctx, mode, algo, flag, d_src + b0 * src_img, W, H, depth, d_flt, kW, kH, N, d_dst + b0 * dst_img,
-                         nb, src_img, dst_img, s);
+        rc = conv_device(ctx, mode, algo, flag, d_src + b0 * src_img, W, H, depth, nullptr, kW, kH, N, d_dst + b0 * dst_img,
+                         nb, src_img, dst_img, s, nullptr, DECXB_ACT_NONE, pf);
         if (rc) return fail(rc);
         PIPE_TRY(cudaEventRecord(e_done, s));
         PIPE_TRY(cudaStreamWaitEvent(down, e_done, 0));

@@ -59,6 +59,7 @@ struct decxb_ctx {
     long long wait_limit_ns = 2000000000LL;
     int pack_variant = 0;               /* 0 = copy-engine (TMA) pack, 1 = shared-memory staged, 2 = direct */
     std::atomic<uint64_t> launches{0};
+    int tile_group = 8;                 /* tile-rows per group of the GEMM kernel's tile order (decxb_set_tile_group) */
     int reserved_sms = 0;               /* SMs the next GEMM launches leave free (a transfer kernel runs beside them) */
     int inject_countdown = -1;          /* >= 0: that many pipeline CUDA calls from now, one reports a failure (tests) */
     std::string last_error;
@@ -100,6 +101,10 @@ int decxb_check_dev_status(decxb_ctx* ctx);
 
 static inline int64_t decxb_ceil_to(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 static inline int64_t decxb_ceil_div(int64_t v, int64_t m) { return (v + m - 1) / m; }
+/* Row pitch (floats) of the library's own hi/lo operand arrays for a row of K values: a multiple of 4
+ * (16 bytes, the copy engine's rule).  (Padding power-of-two pitches by a line was measured at
+ * 16384^3 and changed neither the DRAM traffic nor the time.) */
+static inline int64_t decxb_split_pitch(int64_t K) { return decxb_ceil_to(K, 4); }
 
 /* ---- internal kernels' launchers (each returns a decxb_status) ------------------------ */
 
@@ -111,6 +116,12 @@ int decxb_launch_split_rows(decxb_ctx* ctx, const float* in, int64_t rows, int64
 int decxb_launch_split_transpose(decxb_ctx* ctx, const float* in, int64_t K, int64_t N, int64_t ld_in,
                                  float* hi, float* lo, int64_t ld_out, int raw, cudaStream_t s,
                                  int64_t nbatch = 1, int64_t in_batch_stride = 0, int64_t out_batch_rows = 0);
+
+/* A -> hi/lo [M][ld_out] and B[K][N] -> hi/lo [N][ld_out] in one launch (3xTF32 operands of one product);
+ * possible when B and its outputs allow 128-bit accesses. */
+bool decxb_split_ab_possible(const float* B, int64_t ldb, const float* b_hi, const float* b_lo);
+int decxb_launch_split_ab(decxb_ctx* ctx, const float* A, int64_t M, int64_t K, int64_t lda, float* a_hi, float* a_lo,
+                          const float* B, int64_t N, int64_t ldb, float* b_hi, float* b_lo, int64_t ld_out, cudaStream_t s);
 
 /* The tensor-core GEMM on K-contiguous operands.  a_hi/a_lo: [M][lda], b_hi/b_lo: [N][ldb]
  * (lo pointers NULL for plain TF32).  C optional addend, D output. */

@@ -105,6 +105,13 @@ extern "C" int decxb_set_wait_limit_ms(decxb_ctx* ctx, int ms)
     return DECXB_OK;
 }
 
+extern "C" int decxb_set_tile_group(decxb_ctx* ctx, int tile_rows)
+{
+    if (!ctx || tile_rows < 1 || tile_rows > 64) return DECXB_ERR_BAD_PARAM;
+    ctx->tile_group = tile_rows;
+    return DECXB_OK;
+}
+
 extern "C" int decxb_set_pack_variant(decxb_ctx* ctx, int variant)
 {
     if (!ctx || variant < 0 || variant > 2) return DECXB_ERR_BAD_PARAM;

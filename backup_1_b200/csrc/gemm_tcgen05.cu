@@ -78,6 +78,7 @@ struct GemmParams {
     const float* bias;          /* per output column (filter), or NULL                            */
     int act;                    /* DECXB_ACT_*                                                    */
     int tma_store;              /* 1 = results leave through shared memory and TMA stores (map_d)   */
+    int tile_group;             /* tile-rows per group of the tile order                            */
 };
 
 /* Activations with the reference's formulas (srcs/nn/operators/ReLU.h:48-75 keeps x when its
@@ -217,9 +218,8 @@ __device__ __forceinline__ int chunk_blocks(int kb0)
 
 /* Tile order: groups of 8 tile-rows, column by column inside a group, so that the CTAs
  * running at the same time share A row-panels and B column-panels in L2. */
-__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn)
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int GROUP, int& tm, int& tn)
 {
-    constexpr int GROUP = 8;
     const int per_group = GROUP * tiles_n;
     const int g = t / per_group;
     const int first_m = g * GROUP;
@@ -333,7 +333,7 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
             uint32_t armed = 0, armed_parity = 0;     /* per stage: loads issued at least once / parity of the latest */
             bool alive = true;
             for (int t = cluster_id; t < num_tiles && alive; t += num_clusters) {
-                int tm, tn; tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+                int tm, tn; tile_coords(t, p.tiles_m, p.tiles_n, p.tile_group, tm, tn);
                 const int row_a = tm * C::UMMA_M + (int)cta_rank * BM_CTA;
                 int row_b = tn * C::UMMA_N + (int)cta_rank * BN;
                 if (!CONV && p.tiles_m_per) row_b += (tm / p.tiles_m_per) * (int)p.b_batch_rows;   /* matrix of the batch */
@@ -456,7 +456,7 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
         const uint32_t stg = staging + (uint32_t)(KCH ? warp - 4 : warp - 2) * (4096u * C::BOXES);   /* this warp's TMA store box(es) */
         uint32_t box_turn = 0;
         for (int t = cluster_id; t < num_tiles && alive; t += num_clusters) {
-            int tm, tn; tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+            int tm, tn; tile_coords(t, p.tiles_m, p.tiles_n, p.tile_group, tm, tn);
             const int bidx = (!CONV && p.tiles_m_per) ? tm / p.tiles_m_per : 0;
             int64_t row = (int64_t)(tm - bidx * p.tiles_m_per) * C::UMMA_M + (int64_t)cta_rank * BM_CTA + q * 32 + lane;
             bool row_ok = row < p.M;
@@ -757,9 +757,11 @@ int launch_kernel(decxb_ctx* ctx, const CUtensorMap& ma_hi, const CUtensorMap& m
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 2;
+    GemmParams pp = p;
+    pp.tile_group = ctx->tile_group > 0 ? ctx->tile_group : 8;
     {
         decxb_launch_scope scope(ctx, s, DECXB_K_GEMM);
-        DECXB_CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kernel, ma_hi, ma_lo, mb_hi, mb_lo, md, p));
+        DECXB_CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kernel, ma_hi, ma_lo, mb_hi, mb_lo, md, pp));
     }
     return DECXB_OK;
 }

@@ -81,37 +81,46 @@ __device__ __forceinline__ void split1(float a, float& hi, float& lo)
 
 /* in[rows][ld_in] -> hi/lo[rows_out][ld_out]; columns >= cols and rows >= rows are written
  * as zero.  One thread per 4 output columns. */
-__global__ void __launch_bounds__(256)
-decxb_split_rows_kernel(const float* __restrict__ in, int64_t rows, int64_t cols, int64_t ld_in,
-                        float* __restrict__ hi, float* __restrict__ lo, int64_t ld_out, int64_t rows_out,
-                        int in_vec_ok, int64_t nbatch, int64_t in_batch_stride, int raw)
+struct SplitRowsArgs {
+    const float* in; int64_t rows, cols, ld_in;
+    float *hi, *lo; int64_t ld_out, rows_out;
+    int in_vec_ok; int64_t nbatch, in_batch_stride; int raw;
+};
+
+/* The work of block `bid` of `nblocks` blocks of 256 threads. */
+__device__ __forceinline__ void split_rows_body(const SplitRowsArgs& a, int64_t bid, int64_t nblocks)
 {
     /* nbatch matrices: matrix b reads rows [0, rows) at in + b*in_batch_stride and writes rows
      * [b*rows_out, (b+1)*rows_out) of the stacked output (rows beyond `rows` are zero) */
-    allow_dependent_launch();
-    const int64_t q_per_row = ld_out >> 2;
-    const int64_t total = nbatch * rows_out * q_per_row;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t q_per_row = a.ld_out >> 2;
+    const int64_t total = a.nbatch * a.rows_out * q_per_row;
+    for (int64_t i = bid * blockDim.x + threadIdx.x; i < total; i += nblocks * blockDim.x) {
         const int64_t r_all = i / q_per_row, c = (i - r_all * q_per_row) << 2;
-        const int64_t b = nbatch > 1 ? r_all / rows_out : 0, r = r_all - b * rows_out;
+        const int64_t b = a.nbatch > 1 ? r_all / a.rows_out : 0, r = r_all - b * a.rows_out;
         float v[4] = {0.f, 0.f, 0.f, 0.f};
-        if (r < rows) {
-            const float* p = in + b * in_batch_stride + r * ld_in + c;
-            if (in_vec_ok && c + 3 < cols) {
+        if (r < a.rows) {
+            const float* p = a.in + b * a.in_batch_stride + r * a.ld_in + c;
+            if (a.in_vec_ok && c + 3 < a.cols) {
                 const float4 t = __ldg(reinterpret_cast<const float4*>(p));
                 v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
             } else {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) if (c + j < cols) v[j] = __ldg(p + j);
+                for (int j = 0; j < 4; ++j) if (c + j < a.cols) v[j] = __ldg(p + j);
             }
         }
         float4 h, l;
-        if (raw) { h = make_float4(v[0], v[1], v[2], v[3]); l = h; }
+        if (a.raw) { h = make_float4(v[0], v[1], v[2], v[3]); l = h; }
         else { split1(v[0], h.x, l.x); split1(v[1], h.y, l.y); split1(v[2], h.z, l.z); split1(v[3], h.w, l.w); }
-        *reinterpret_cast<float4*>(hi + r_all * ld_out + c) = h;
-        if (lo && !raw) *reinterpret_cast<float4*>(lo + r_all * ld_out + c) = l;
+        *reinterpret_cast<float4*>(a.hi + r_all * a.ld_out + c) = h;
+        if (a.lo && !a.raw) *reinterpret_cast<float4*>(a.lo + r_all * a.ld_out + c) = l;
     }
+}
+
+__global__ void __launch_bounds__(256)
+decxb_split_rows_kernel(const SplitRowsArgs a)
+{
+    allow_dependent_launch();
+    split_rows_body(a, blockIdx.x, gridDim.x);
 }
 
 int decxb_launch_split_rows(decxb_ctx* ctx, const float* in, int64_t rows, int64_t cols, int64_t ld_in,
@@ -127,8 +136,8 @@ int decxb_launch_split_rows(decxb_ctx* ctx, const float* in, int64_t rows, int64
     if (blocks > (int64_t)ctx->sm_count * 32) blocks = (int64_t)ctx->sm_count * 32;
     {
         decxb_launch_scope scope(ctx, s, DECXB_K_SPLIT);
-        decxb_split_rows_kernel<<<(int)blocks, 256, 0, s>>>(in, rows, cols, ld_in, hi, lo, ld_out, rows_out, vec_ok,
-                                                            nbatch, in_batch_stride, raw);
+        const SplitRowsArgs a = {in, rows, cols, ld_in, hi, lo, ld_out, rows_out, vec_ok, nbatch, in_batch_stride, raw};
+        decxb_split_rows_kernel<<<(int)blocks, 256, 0, s>>>(a);
     }
     DECXB_CUDA_TRY(ctx, cudaGetLastError());
     return DECXB_OK;
@@ -179,34 +188,36 @@ decxb_split_transpose_kernel(const float* __restrict__ in, int64_t K, int64_t N,
  * loads along n into the tile, 128-bit stores along k out of it.  A thread of the store phase
  * owns 4 consecutive k of one n, so a 16-thread group writes one 256-byte run of an output
  * row.  (The tile pitch of 65 words keeps the column reads at most 2-way bank conflicted.) */
-__global__ void __launch_bounds__(256)
-decxb_split_transpose_vec_kernel(const float* __restrict__ in, int64_t K, int64_t N, int64_t ld_in,
-                                 float* __restrict__ hi, float* __restrict__ lo, int64_t ld_out, int raw,
-                                 int64_t tiles_n, int64_t nbatch, int64_t in_batch_stride, int64_t out_batch_rows)
+struct SplitTransposeArgs {
+    const float* in; int64_t K, N, ld_in;
+    float *hi, *lo; int64_t ld_out; int raw;
+    int64_t tiles_n, nbatch, in_batch_stride, out_batch_rows;
+};
+
+__device__ __forceinline__ void split_transpose_vec_body(const SplitTransposeArgs& a, float (*tile)[65], int64_t bid, int64_t nblocks)
 {
-    __shared__ float tile[64][65];
-    allow_dependent_launch();
     const int tid = threadIdx.x;
-    const int64_t tiles_k = (ld_out + 63) / 64;
-    const int64_t n_tiles = tiles_k * tiles_n;
-    const float* const in0 = in; float* const hi0 = hi; float* const lo0 = lo;
-    for (int64_t tt = blockIdx.x; tt < n_tiles * nbatch; tt += gridDim.x) {
+    const int64_t tiles_k = (a.ld_out + 63) / 64;
+    const int64_t n_tiles = tiles_k * a.tiles_n;
+    for (int64_t tt = bid; tt < n_tiles * a.nbatch; tt += nblocks) {
         const int64_t bb = tt / n_tiles, t = tt - bb * n_tiles;
-        in = in0 + bb * in_batch_stride; hi = hi0 + bb * out_batch_rows * ld_out; lo = lo0 ? lo0 + bb * out_batch_rows * ld_out : nullptr;
-        const int64_t k0 = (t / tiles_n) * 64, n0 = (t % tiles_n) * 64;
+        const float* in = a.in + bb * a.in_batch_stride;
+        float* hi = a.hi + bb * a.out_batch_rows * a.ld_out;
+        float* lo = a.lo ? a.lo + bb * a.out_batch_rows * a.ld_out : nullptr;
+        const int64_t k0 = (t / a.tiles_n) * 64, n0 = (t % a.tiles_n) * 64;
         /* load: 64 k-rows x 16 float4 along n */
 #pragma unroll
         for (int i = tid; i < 1024; i += 256) {
             const int kr = i >> 4, n4 = (i & 15) << 2;
             const int64_t k = k0 + kr, n = n0 + n4;
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (k < K) {
-                const float* p = in + k * ld_in + n;
-                if (n + 3 < N) v = __ldg(reinterpret_cast<const float4*>(p));
+            if (k < a.K) {
+                const float* p = in + k * a.ld_in + n;
+                if (n + 3 < a.N) v = __ldg(reinterpret_cast<const float4*>(p));
                 else {
-                    if (n < N) v.x = __ldg(p);
-                    if (n + 1 < N) v.y = __ldg(p + 1);
-                    if (n + 2 < N) v.z = __ldg(p + 2);
+                    if (n < a.N) v.x = __ldg(p);
+                    if (n + 1 < a.N) v.y = __ldg(p + 1);
+                    if (n + 2 < a.N) v.z = __ldg(p + 2);
                 }
             }
             tile[kr][n4] = v.x; tile[kr][n4 + 1] = v.y; tile[kr][n4 + 2] = v.z; tile[kr][n4 + 3] = v.w;
@@ -217,17 +228,63 @@ decxb_split_transpose_vec_kernel(const float* __restrict__ in, int64_t K, int64_
         for (int i = tid; i < 1024; i += 256) {
             const int nr = i >> 4, k4 = (i & 15) << 2;
             const int64_t n = n0 + nr, k = k0 + k4;
-            if (n < N && k < ld_out) {
+            if (n < a.N && k < a.ld_out) {
                 const float a0 = tile[k4][nr], a1 = tile[k4 + 1][nr], a2 = tile[k4 + 2][nr], a3 = tile[k4 + 3][nr];
                 float4 h, l;
-                if (raw) { h = make_float4(a0, a1, a2, a3); }
+                if (a.raw) { h = make_float4(a0, a1, a2, a3); }
                 else { split1(a0, h.x, l.x); split1(a1, h.y, l.y); split1(a2, h.z, l.z); split1(a3, h.w, l.w); }
-                *reinterpret_cast<float4*>(hi + n * ld_out + k) = h;
-                if (!raw) *reinterpret_cast<float4*>(lo + n * ld_out + k) = l;
+                *reinterpret_cast<float4*>(hi + n * a.ld_out + k) = h;
+                if (!a.raw) *reinterpret_cast<float4*>(lo + n * a.ld_out + k) = l;
             }
         }
         __syncthreads();
     }
+}
+
+__global__ void __launch_bounds__(256)
+decxb_split_transpose_vec_kernel(const SplitTransposeArgs a)
+{
+    __shared__ float tile[64][65];
+    allow_dependent_launch();
+    split_transpose_vec_body(a, tile, blockIdx.x, gridDim.x);
+}
+
+/* Both operands of a product in ONE grid: the first `blocks_rows` blocks split A row-wise, the rest
+ * split and transpose B.  A small product is otherwise three launches, two of which only write the
+ * hi/lo copies and each of which fills a fraction of the GPU. */
+__global__ void __launch_bounds__(256)
+decxb_split_ab_kernel(const SplitRowsArgs ra, const SplitTransposeArgs ta, int blocks_rows)
+{
+    __shared__ float tile[64][65];
+    allow_dependent_launch();
+    if ((int)blockIdx.x < blocks_rows) split_rows_body(ra, blockIdx.x, blocks_rows);
+    else split_transpose_vec_body(ta, tile, (int64_t)blockIdx.x - blocks_rows, (int64_t)gridDim.x - blocks_rows);
+}
+
+bool decxb_split_ab_possible(const float* B, int64_t ldb, const float* b_hi, const float* b_lo)
+{
+    return ((uintptr_t)B % 16 == 0) && (ldb % 4 == 0) && ((uintptr_t)b_hi % 16 == 0) && ((uintptr_t)b_lo % 16 == 0);
+}
+
+int decxb_launch_split_ab(decxb_ctx* ctx, const float* A, int64_t M, int64_t K, int64_t lda, float* a_hi, float* a_lo,
+                          const float* B, int64_t N, int64_t ldb, float* b_hi, float* b_lo, int64_t ld_out, cudaStream_t s)
+{
+    if (ld_out % 4 || ld_out < K) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "split pitch");
+    const int64_t total_rows = M * (ld_out / 4);
+    const int64_t tiles_n = (N + 63) / 64, tiles_k = (ld_out + 63) / 64;
+    int64_t blocks_rows = (total_rows + 255) / 256, blocks_t = tiles_n * tiles_k;
+    const int64_t cap = (int64_t)ctx->sm_count * 16;
+    if (blocks_rows > cap) blocks_rows = cap;
+    if (blocks_t > cap) blocks_t = cap;
+    const int vec_ok = ((uintptr_t)A % 16 == 0) && (lda % 4 == 0);
+    const SplitRowsArgs ra = {A, M, K, lda, a_hi, a_lo, ld_out, M, vec_ok, 1, 0, 0};
+    const SplitTransposeArgs ta = {B, K, N, ldb, b_hi, b_lo, ld_out, 0, tiles_n, 1, 0, 0};
+    {
+        decxb_launch_scope scope(ctx, s, DECXB_K_SPLIT);
+        decxb_split_ab_kernel<<<(int)(blocks_rows + blocks_t), 256, 0, s>>>(ra, ta, (int)blocks_rows);
+    }
+    DECXB_CUDA_TRY(ctx, cudaGetLastError());
+    return DECXB_OK;
 }
 
 int decxb_launch_split_transpose(decxb_ctx* ctx, const float* in, int64_t K, int64_t N, int64_t ld_in,
@@ -243,8 +300,8 @@ int decxb_launch_split_transpose(decxb_ctx* ctx, const float* in, int64_t K, int
     if (((uintptr_t)in % 16 == 0) && (ld_in % 4 == 0) && (in_batch_stride % 4 == 0) && ((uintptr_t)hi % 16 == 0) &&
         (raw || (uintptr_t)lo % 16 == 0)) {
         decxb_launch_scope scope(ctx, s, DECXB_K_SPLIT);
-        decxb_split_transpose_vec_kernel<<<(int)blocks, 256, 0, s>>>(in, K, N, ld_in, hi, lo, ld_out, raw, tiles_n,
-                                                                     nbatch, in_batch_stride, out_batch_rows);
+        const SplitTransposeArgs a = {in, K, N, ld_in, hi, lo, ld_out, raw, tiles_n, nbatch, in_batch_stride, out_batch_rows};
+        decxb_split_transpose_vec_kernel<<<(int)blocks, 256, 0, s>>>(a);
         DECXB_CUDA_TRY(ctx, cudaGetLastError());
         return DECXB_OK;
     }

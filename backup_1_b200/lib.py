@@ -80,6 +80,7 @@ SIGNATURES = {
     "decxb_conv_geometry": (_i, [_i64, _i64, _i64, _i64, _i64, _i64, _i, C.POINTER(ConvGeom)]),
     "decxb_im2col_pack_f32": (_i, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _i, _vp, _i64, _i64, _i64, _vp]),
     "decxb_set_pack_variant": (_i, [_vp, _i]),
+    "decxb_set_tile_group": (_i, [_vp, _i]),
     "decxb_conv2_im2col_f32": (_i, [_vp, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp]),
     "decxb_conv2_im2col_f32_act": (_i, [_vp, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i, _vp, _i64, _i64, _i64, _vp]),
     "decxb_conv2_im2col_f32_host": (_i, [_vp, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64]),
@@ -96,6 +97,9 @@ SIGNATURES = {
     "decxb_gemm_prepare_b": (_i, [_vp, _i, _i64, _i64, _vp, _i64, _vp, C.POINTER(_vp)]),
     "decxb_gemm_f32_prepared": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _i, _vp, _i64, _vp]),
     "decxb_gemm_release_b": (_i, [_vp, _vp, _vp]),
+    "decxb_conv_prepare_filters": (_i, [_vp, _i, _i, _vp, _i64, _i64, _i64, _i64, _vp, C.POINTER(_vp)]),
+    "decxb_conv2_im2col_f32_prepared": (_i, [_vp, _i, _vp, _i64, _i64, _vp, _vp, _i, _vp, _i64, _i64, _i64, _vp]),
+    "decxb_conv_release_filters": (_i, [_vp, _vp, _vp]),
     "decxb_comm_unique_id": (_i, [_vp]),
     "decxb_comm_init": (_i, [_vp, _i, _i, _vp, _i, C.POINTER(_vp)]),
     "decxb_comm_destroy": (_i, [_vp]),
@@ -189,6 +193,9 @@ class Context:
 
     def set_wait_limit_ms(self, ms: int):
         self._chk(self.L.decxb_set_wait_limit_ms(self.h, ms))
+
+    def set_tile_group(self, tile_rows: int):
+        self._chk(self.L.decxb_set_tile_group(self.h, tile_rows))
 
     def launches(self) -> int:
         return int(self.L.decxb_kernel_launch_count(self.h))
@@ -286,6 +293,19 @@ class Context:
                      src_stride=0, dst_stride=0, mode=GEMM_DEFAULT, algo=CONV_EXPLICIT, stream=None):
         self._chk(self.L.decxb_conv2_im2col_f32(self.h, mode, algo, flag, _ptr(src), W, H, depth, _ptr(filters),
                                                 kW, kH, N, _ptr(dst), batch, src_stride, dst_stride, stream))
+
+    def conv_prepare_filters(self, filters, kW, kH, depth, N, mode=GEMM_DEFAULT, algo=CONV_IMPLICIT, stream=None) -> int:
+        h = _vp()
+        self._chk(self.L.decxb_conv_prepare_filters(self.h, mode, algo, _ptr(filters), kW, kH, depth, N, stream, C.byref(h)))
+        return h.value
+
+    def conv2_im2col_prepared(self, src, W, H, pf, dst, flag=CONV_ZERO_COMPENSATE, batch=1, src_stride=0, dst_stride=0,
+                              bias=None, act=ACT_NONE, stream=None):
+        self._chk(self.L.decxb_conv2_im2col_f32_prepared(self.h, flag, _ptr(src), W, H, pf, _ptr(bias), act, _ptr(dst),
+                                                         batch, src_stride, dst_stride, stream))
+
+    def conv_release_filters(self, pf, stream=None):
+        self._chk(self.L.decxb_conv_release_filters(self.h, pf, stream))
 
     def gemm_rowshard(self, world, rank, M, N, K, A_rows, lda, B, ldb, D_rows, ldd, C_rows=None, ldc=0,
                       mode=GEMM_DEFAULT, tile=TILE_AUTO, stream=None):

@@ -305,7 +305,12 @@ class Bench:
                 M_rank, row0 = r1 - r0, r0
             else:
                 M_rank, row0 = M, rank * M
-            dA = torch.empty((M_rank, K), device=dev); dB = torch.empty((K, N), device=dev); dD = torch.empty((M_rank, N), device=dev)
+            dA = torch.empty((M_rank, K), device=dev); dB = torch.empty((K, N), device=dev)
+            if wl["scaling"] == "strong" and world > 1 and mode_name != "f16":
+                w["full"] = torch.empty((M, N), device=dev)          # the whole result: this rank's rows are computed in place
+                dD = w["full"][row0:row0 + M_rank]
+            else:
+                dD = torch.empty((M_rank, N), device=dev)
             ctx.fill_uniform(dA, M_rank, K, K, 1, first_index=row0 * K)
             ctx.fill_uniform(dB, K, N, N, 2)
             w.update(flops=2.0 * M_rank * N * K, M_rank=M_rank, row0=row0, dA=dA, dB=dB, dD=dD, K_err=K)
@@ -351,7 +356,11 @@ class Bench:
             ctx.fill_uniform(tmpF, F * kH * kW, dp, dp, 5)
             ctx.synchronize()
             dF[:, :, :kW, :] = tmpF
-            dO = torch.empty((max(nb, 1), g.out_h, g.eq_w, g.Np), device=dev)
+            if wl["scaling"] == "strong" and world > 1:
+                w["full"] = torch.empty((batch, g.out_h, g.eq_w, g.Np), device=dev)
+                dO = w["full"][img0:img0 + max(nb, 1)]
+            else:
+                dO = torch.empty((max(nb, 1), g.out_h, g.eq_w, g.Np), device=dev)
             w.update(flops=2.0 * nb * (H * W) * (kW * kH * C) * F, nb=nb, dS=dS, dF=dF, dO=dO, g=g, K_err=kW * kH * C,
                      dims=(W, H, C, kW, kH, F, dp, wp))
 
@@ -629,29 +638,42 @@ def main():
     h2d, d2h = w["h2d"], w["d2h"]
     w.pop("host", None); w.pop("step_host", None)
 
-    # ---- all-gather of the result blocks (N > 1; timed separately) --------------------------------------
+    # ---- gathering the result blocks over NCCL (N > 1): after the step, and overlapped with it ------------
     gather = None
-    if world > 1 and not args.no_gather and wl["scaling"] == "strong":
+    if world > 1 and not args.no_gather and wl["scaling"] == "strong" and "full" in w:
         from backup_1_b200 import shard
 
-        local = w["dD"] if wl["kind"] == "gemm" else w["dO"][: w["nb"]]
+        uid = [bench.b.Comm.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        comm = bench.b.Comm(ctx, world, rank, uid[0], timeout_ms=120000)
+        full = w["full"]
         total_units = wl["M"] if wl["kind"] == "gemm" else wl["batch"]
-        full = None
-        for _ in range(2):
-            del full
-            full = shard.all_gather_blocks(local, total_units)
-        bench.barrier()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record()
-        del full
-        full = shard.all_gather_blocks(local, total_units)
-        g1.record()
-        torch.cuda.synchronize()
-        gms = bench.max_over_ranks(g0.elapsed_time(g1))
-        nbytes = local.numel() * local.element_size()
-        # the gathered copy of a peer's block equals what this rank computes for a sample of those rows itself
-        gerr = None
-        if wl["kind"] == "gemm" and args.mode != "f16":
+        unit_bytes = full[0].numel() * 4
+        mine = (w["M_rank"] if wl["kind"] == "gemm" else w["nb"]) * unit_bytes
+
+        def timed(fn, reps):
+            fn(); comm.synchronize()
+            bench.barrier()
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g0.record(bench.ts)
+            for _ in range(reps):
+                fn()
+            g1.record(bench.ts)
+            comm.synchronize()
+            bench.barrier()
+            return bench.max_over_ranks(g0.elapsed_time(g1)) / reps
+
+        gms = timed(lambda: comm.allgather_blocks(full, unit_bytes, total_units, stream=bench.st), 2)
+        gather = {"ms": gms, "bytes_per_rank": mine, "busbw_gbs": mine * (world - 1) / (gms * 1e-3) / 1e9,
+                  "how": "decxb_comm_allgather_blocks (NCCL, in place in the whole-result array) after the step, timed alone"}
+        if wl["kind"] == "gemm":
+            mode = {"3xtf32": bench.b.GEMM_3XTF32, "1xtf32": bench.b.GEMM_1XTF32, "strict": bench.b.GEMM_3XTF32_STRICT}[args.mode]
+            A_rows, Bm = w["dA"], w["dB"]
+            for groups in (1, 4, 8):
+                ms = timed(lambda: comm.gemm_rowshard_gather(wl["M"], wl["N"], wl["K"], A_rows, wl["K"], Bm, wl["N"], full, groups=groups,
+                                                             mode=mode, tile=args.tile, stream=bench.st), max(2, min(args.steps, 5)))
+                gather[f"step_with_gather_ms_groups{groups}"] = ms
+            # a peer's gathered rows equal what this rank computes for a sample of those rows itself (fp64 checker)
             peer = (rank + 1) % world
             p0, p1 = shard.gemm_row_shard(wl["M"], world, peer)
             rows = torch.tensor([p0, (p0 + p1) // 2, p1 - 1], device=bench.dev)
@@ -660,13 +682,15 @@ def main():
                 ctx.fill_uniform(a[i], 1, wl["K"], wl["K"], 1, first_index=r * wl["K"])
             ctx.synchronize()
             cols = torch.arange(0, 256, device=bench.dev)
-            ref = a.double() @ w["dB"][:, cols].double()
-            gerr = bench.max_over_ranks(float((full[rows][:, cols].double() - ref).abs().max()) / wl["K"])
-        gather = {"ms": gms, "bytes_per_rank": nbytes, "busbw_gbs": nbytes * (world - 1) / (gms * 1e-3) / 1e9,
-                  "how": "shard.all_gather_blocks (torch.distributed all_gather_into_tensor over NCCL) after the last step",
-                  "gathered_rows_max_norm_err": gerr}
-        del full
-        local = None
+            ref = a.double() @ Bm[:, cols].double()
+            gather["gathered_rows_max_norm_err"] = bench.max_over_ranks(float((full[rows][:, cols].double() - ref).abs().max()) / wl["K"])
+            best = min((gather[f"step_with_gather_ms_groups{g}"], g) for g in (4, 8))
+            gather["overlapped_groups"] = best[1]
+            gather["step_with_overlapped_gather_ms"] = best[0]
+            gather["how_overlapped"] = ("decxb_gemm_f32_rowshard_gather: the rank's rows in row-panel groups, each group sent to the peers "
+                                        "(NCCL send/receive on a side stream) while the next is multiplied")
+        comm.close()
+        full = None
     per_rank_ms = bench.per_rank(res["ms_rank_per_step"])
     per_rank_mhz = bench.per_rank(res["clocks"]["sm_mhz"] if res["clocks"] else None)
 
@@ -751,6 +775,8 @@ def main():
         if gather:
             line["allgather"] = gather
             line["value_with_gather"] = res["total_flops"] / ((res["ms_per_step"] + gather["ms"]) * 1e-3) / 1e12
+            if "step_with_overlapped_gather_ms" in gather:
+                line["value_with_overlapped_gather"] = res["total_flops"] / (gather["step_with_overlapped_gather_ms"] * 1e-3) / 1e12
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -323,6 +323,20 @@ DECXB_API int decxb_conv2_im2col_f32_act(decxb_ctx* ctx, int mode, int algo, int
                                          float* dst, int64_t batch, int64_t src_stride, int64_t dst_stride,
                                          void* stream);
 
+/* Filter bank prepared once for many convolutions (weights stay the same from call to call): the
+ * gather of the bank into the filter matrix and its hi/lo split are done by
+ * decxb_conv_prepare_filters into arena memory owned by the handle; decxb_conv2_im2col_f32_prepared
+ * is decxb_conv2_im2col_f32_act on that handle (mode and algorithm are the handle's; results are
+ * bit-identical); decxb_conv_release_filters gives the memory back.  The reference re-stages the
+ * bank with one copy per filter on every call (conv2_mk_im2col.h:226-231); no counterpart there. */
+typedef struct decxb_prepared_filters decxb_prepared_filters;
+DECXB_API int decxb_conv_prepare_filters(decxb_ctx* ctx, int mode, int algo, const float* filters, int64_t kW, int64_t kH,
+                                         int64_t depth, int64_t N, void* stream, decxb_prepared_filters** out);
+DECXB_API int decxb_conv2_im2col_f32_prepared(decxb_ctx* ctx, int flag, const float* src, int64_t W, int64_t H,
+                                              const decxb_prepared_filters* filters, const float* bias, int activation,
+                                              float* dst, int64_t batch, int64_t src_stride, int64_t dst_stride, void* stream);
+DECXB_API int decxb_conv_release_filters(decxb_ctx* ctx, decxb_prepared_filters* filters, void* stream);
+
 /* Host-resident tensors; blocks until dst is in host memory. */
 DECXB_API int decxb_conv2_im2col_f32_host(decxb_ctx* ctx, int mode, int algo, int flag,
                                           const float* h_src, int64_t W, int64_t H, int64_t depth,
@@ -330,6 +344,10 @@ DECXB_API int decxb_conv2_im2col_f32_host(decxb_ctx* ctx, int mode, int algo, in
                                           float* h_dst, int64_t batch, int64_t src_stride, int64_t dst_stride);
 
 /* ---- introspection for tests and benchmarks --------------------------------------- */
+/* Tile order of the GEMM kernel: tiles are walked in groups of `tile_rows` tile-rows, column by
+ * column inside a group, so that the blocks running at the same time share A row-panels and B
+ * column-panels in L2 (1..64, default 8).  Results do not depend on it.  For measurement. */
+DECXB_API int decxb_set_tile_group(decxb_ctx* ctx, int tile_rows);
 /* Per-kernel device timing.  While enabled, every kernel the library launches is bracketed
  * by CUDA events on its own stream; decxb_profile_read synchronises the device, adds the
  * elapsed times to the totals below and returns them (decxb_profile_enable(ctx, 1) also
@@ -373,7 +391,8 @@ DECXB_API int decxb_conv2_im2col_f32_batchshard(decxb_ctx* ctx, int mode, int al
  * for about target_ms and reports what the tensor pipe delivered.  pattern 0: one MMA per
  * k-step, the TF32 issue peak; 1: the three MMAs of the GEMM kernel's 3xTF32 k-step on four
  * distinct operand tiles, the ceiling its shared-memory operand reads leave; 2: as 1 with a_hi
- * kept in the collector buffer.  algorithmic_tflops = tensor_tflops / MMAs per k-step, directly
+ * kept in the collector buffer; 3, 4, 5: pattern 2 on the single-CTA tiles 128 x 64, 128 x 128,
+ * 128 x 256.  algorithmic_tflops = tensor_tflops / MMAs per k-step, directly
  * comparable with the GEMM's 2 M N K / t.  The denominators of the benchmark's roofline come
  * from here.  No counterpart in the reference (it publishes no peak figure). */
 typedef struct decxb_tensor_probe {

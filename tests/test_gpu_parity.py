@@ -698,6 +698,26 @@ def test_conv_config3_full_size(ctx, algo):
     assert o.norm_err(D[rows], R, P.shape[1], 1.0, 1.0) <= TOL_3X
 
 
+@pytest.mark.parametrize("algo", ALGOS)
+@pytest.mark.parametrize("mode", [b.GEMM_DEFAULT, b.GEMM_1XTF32])
+def test_conv_with_prepared_filters_gives_the_bits_of_the_plain_entry(ctx, algo, mode):
+    W, H, C, kW, F, nb = 37, 21, 40, 3, 50, 3
+    src = np.stack([o.make_tensor(W, H, C, 60 + i) for i in range(nb)])
+    flt = o.make_filters(kW, kW, C, F, 5)
+    bias = np.zeros(o.ceil4(F), np.float32); bias[:F] = o.fill_uniform(F, 9)
+    dS, dF, dB = dev(src), dev(flt), dev(bias)
+    _, oh, eq, _, _ = o.conv_geometry(W, H, C, kW, kW, 1)
+    want = torch.full((nb, oh, eq, o.ceil4(F)), float("nan"), device=DEV); got = torch.full_like(want, float("nan"))
+    ctx.conv2_im2col_act(dS, W, H, C, dF, kW, kW, F, want, bias=dB, act=b.ACT_TANH, batch=nb, mode=mode, algo=algo)
+    pf = ctx.conv_prepare_filters(dF, kW, kW, C, F, mode=mode, algo=algo)
+    dF.zero_()                                   # the bank itself is no longer needed once prepared
+    for _ in range(2):
+        ctx.conv2_im2col_prepared(dS, W, H, pf, got, batch=nb, bias=dB, act=b.ACT_TANH)
+    ctx.synchronize()
+    ctx.conv_release_filters(pf)
+    assert torch.equal(got, want)
+
+
 def test_rank_shards_assemble_the_unsharded_result(ctx):
     """decxb_gemm_f32_rowshard / decxb_conv2_im2col_f32_batchshard: the shards of 3 ranks (run one
     after the other on this GPU, each on its own block) assemble, bit for bit, the result of the

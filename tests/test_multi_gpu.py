@@ -79,3 +79,36 @@ def test_gather_over_nccl_one_process_per_gpu(world, tmp_path):
         outs.append(out)
     for r, (p, out) in enumerate(zip(procs, outs)):
         assert p.returncode == 0 and f"rank {r} ok" in out, f"rank {r}:\n{out[-3000:]}"
+
+
+_NEVER_JOINS = r"""
+import sys, time
+import torch
+import backup_1_b200 as b
+ctx = b.Context(0)
+uid = b.Comm.unique_id()
+t0 = time.perf_counter()
+try:
+    b.Comm(ctx, 2, 0, uid, timeout_ms=1500)        # rank 1 of 2 is never started
+    print("joined?!"); sys.exit(1)
+except b.DecxbError as e:
+    dt = time.perf_counter() - t0
+    assert e.status == 103, e
+    assert 1.4 <= dt < 30.0, dt
+# the context (and NCCL) are still usable: a single-rank communicator and a product
+c = b.Comm(ctx, 1, 0, b.Comm.unique_id(), timeout_ms=20000)
+A = torch.rand((256, 64), device="cuda:0"); B = torch.rand((64, 256), device="cuda:0"); D = torch.empty((256, 256), device="cuda:0")
+c.gemm_rowshard_gather(256, 256, 64, A, 64, B, 256, D, groups=2)
+c.synchronize(); ctx.synchronize()
+assert float((D.double() - A.double() @ B.double()).abs().max()) / 64 <= 1e-6
+c.close(); ctx.close()
+print("never-joins ok")
+"""
+
+
+def test_a_rank_that_never_joins_times_out_with_the_real_library():
+    """Over the real NCCL: rank 0 of 2 waits for a rank that is never started; the join gives up after its
+    limit with DECXB_ERR_TIMEOUT (no kernel is in flight at that point, nothing on the GPU is touched), and the
+    process goes on to use the GPU.  Runs in a child process so that a stuck join could not stall the suite."""
+    r = subprocess.run([sys.executable, "-c", _NEVER_JOINS], cwd=HERE.parent, capture_output=True, text=True, timeout=180)
+    assert r.returncode == 0 and "never-joins ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
