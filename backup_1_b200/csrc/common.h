@@ -32,7 +32,51 @@ struct decxb_dev_status {
 enum {
     DECXB_DEVERR_NONE = 0,
     DECXB_DEVERR_WAIT_EXPIRED = 1,
+    DECXB_DEVERR_BOUNDS = 2,          /* debug bounds build: an access outside its array was caught and skipped */
 };
+
+/* Debug bounds build (compile the library with -DDECXB_BOUNDS; `make bounds` builds it beside the
+ * normal one): every global load and store that the threads of the memory-bound kernels make
+ * (operand split, transposes, filter matrix, pack, fill) is checked against the extent of the array
+ * it belongs to.  The first violation is recorded in the context's status word (kernel id, block,
+ * element offset) and the access is skipped, so nothing faults; the host reports
+ * DECXB_ERR_BOUNDS at its next status check.  In the normal build the checks compile to nothing.
+ * (compute-sanitizer would do this job and is not available where this library is developed.) */
+struct decxb_extent { const char* lo; const char* hi; };      /* [lo, hi) */
+struct decxb_bounds {
+    decxb_dev_status* status;
+    decxb_extent in, out0, out1;
+    int kernel;                       /* DECXB_BK_* */
+};
+enum { DECXB_BK_FILL = 1, DECXB_BK_SPLIT_ROWS, DECXB_BK_SPLIT_TRANSPOSE, DECXB_BK_FILTER_MATRIX, DECXB_BK_TRANSPOSE_F16, DECXB_BK_PACK };
+
+static inline decxb_extent decxb_make_extent(const void* base, size_t bytes)
+{
+    return decxb_extent{static_cast<const char*>(base), static_cast<const char*>(base) + (base ? bytes : 0)};
+}
+
+#if defined(__CUDACC__)
+#ifdef DECXB_BOUNDS
+__device__ __forceinline__ bool decxb_access_ok(const decxb_bounds& b, const decxb_extent& e, const void* p, size_t bytes)
+{
+    const char* c = static_cast<const char*>(p);
+    if (c >= e.lo && c + bytes <= e.hi) return true;
+    if (atomicCAS(&b.status->code, 0, DECXB_DEVERR_BOUNDS) == 0) {
+        b.status->where = b.kernel; b.status->block = (int)blockIdx.x;
+        b.status->detail = (int)((c - e.lo) >> 2);
+        __threadfence_system();
+    }
+    return false;
+}
+#define DECXB_OK_IN(b, p, n)   decxb_access_ok((b), (b).in, (p), (n))
+#define DECXB_OK_OUT0(b, p, n) decxb_access_ok((b), (b).out0, (p), (n))
+#define DECXB_OK_OUT1(b, p, n) decxb_access_ok((b), (b).out1, (p), (n))
+#else
+#define DECXB_OK_IN(b, p, n)   true
+#define DECXB_OK_OUT0(b, p, n) true
+#define DECXB_OK_OUT1(b, p, n) true
+#endif
+#endif
 
 /* A cached block remembers the stream that used it last and an event recorded there when it
  * was released, so the same stream can take it again at once (stream order protects it) and
@@ -48,6 +92,13 @@ struct decxb_arena {
     uint64_t n_driver_allocs = 0, n_reuses = 0;
 };
 
+/* Encoded 2-D tensor maps of recent GEMM operands (see make_map in gemm_tcgen05.cu). */
+struct decxb_map_key {
+    const void* base; int64_t rows, K, ld; int box_rows;
+    bool operator==(const decxb_map_key& o) const { return base == o.base && rows == o.rows && K == o.K && ld == o.ld && box_rows == o.box_rows; }
+};
+struct decxb_map_entry { bool used = false; decxb_map_key key = {}; CUtensorMap map; uint64_t stamp = 0; };
+
 struct decxb_ctx {
     int device = -1;
     int sm_count = 0;
@@ -59,6 +110,9 @@ struct decxb_ctx {
     long long wait_limit_ns = 2000000000LL;
     int pack_variant = 0;               /* 0 = copy-engine (TMA) pack, 1 = shared-memory staged, 2 = direct */
     std::atomic<uint64_t> launches{0};
+    std::mutex map_mtx;
+    decxb_map_entry map_cache[16];
+    uint64_t map_clock = 0;
     int tile_group = 8;                 /* tile-rows per group of the GEMM kernel's tile order (decxb_set_tile_group) */
     int reserved_sms = 0;               /* SMs the next GEMM launches leave free (a transfer kernel runs beside them) */
     int inject_countdown = -1;          /* >= 0: that many pipeline CUDA calls from now, one reports a failure (tests) */

@@ -7,6 +7,15 @@ static const char* kVersion = "decxb 0.1 (sm_100a)";
 
 extern "C" const char* decxb_version(void) { return kVersion; }
 
+extern "C" int decxb_bounds_build(void)
+{
+#ifdef DECXB_BOUNDS
+    return 1;
+#else
+    return 0;
+#endif
+}
+
 extern "C" const char* decxb_status_string(int status)
 {
     switch (status) {
@@ -23,6 +32,7 @@ extern "C" const char* decxb_status_string(int status)
     case DECXB_ERR_TIMEOUT: return "a bounded device-side wait expired";
     case DECXB_ERR_TOO_LARGE: return "request exceeds a fixed limit";
     case DECXB_ERR_COMM: return "communication library failure";
+    case DECXB_ERR_BOUNDS: return "debug bounds check caught an access outside its array";
     default: return "unknown status";
     }
 }
@@ -123,11 +133,16 @@ int decxb_check_dev_status(decxb_ctx* ctx)
 {
     DECXB_CUDA_TRY(ctx, cudaMemcpy(ctx->h_status, ctx->d_status, sizeof(decxb_dev_status), cudaMemcpyDeviceToHost));
     if (ctx->h_status->code != DECXB_DEVERR_NONE) {
-        char buf[160];
-        snprintf(buf, sizeof buf, "device wait gave up: code %d at role/barrier %d, block %d, detail %d",
-                 ctx->h_status->code, ctx->h_status->where, ctx->h_status->block, ctx->h_status->detail);
+        char buf[200];
+        const bool bounds = ctx->h_status->code == DECXB_DEVERR_BOUNDS;
+        if (bounds)
+            snprintf(buf, sizeof buf, "bounds check: kernel %d, block %d touched element offset %d outside its array (access skipped)",
+                     ctx->h_status->where, ctx->h_status->block, ctx->h_status->detail);
+        else
+            snprintf(buf, sizeof buf, "device wait gave up: code %d at role/barrier %d, block %d, detail %d",
+                     ctx->h_status->code, ctx->h_status->where, ctx->h_status->block, ctx->h_status->detail);
         cudaMemset(ctx->d_status, 0, sizeof(decxb_dev_status));
-        return decxb_fail(ctx, DECXB_ERR_TIMEOUT, buf);
+        return decxb_fail(ctx, bounds ? DECXB_ERR_BOUNDS : DECXB_ERR_TIMEOUT, buf);
     }
     return DECXB_OK;
 }

@@ -651,6 +651,25 @@ int make_map(decxb_ctx* ctx, CUtensorMap* map, const float* base, int64_t rows, 
     if (!fn) return decxb_fail(ctx, DECXB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
     if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld % 4))
         return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "TMA operand must be 16-byte aligned with a pitch that is a multiple of 4 floats");
+    /* A repeated call (same arrays, same shape: a benchmark step, a layer applied again) finds its five
+     * descriptors in a small per-context table instead of encoding them again. */
+    const decxb_map_key key = {base, rows, K, ld, box_rows};
+    {
+        std::lock_guard<std::mutex> lock(ctx->map_mtx);
+        for (auto& e : ctx->map_cache)
+            if (e.used && e.key == key) { *map = e.map; e.stamp = ++ctx->map_clock; return DECXB_OK; }
+    }
+    struct Store {
+        decxb_ctx* c; const decxb_map_key& k; CUtensorMap* m; bool ok = false;
+        ~Store()
+        {
+            if (!ok) return;
+            std::lock_guard<std::mutex> lock(c->map_mtx);
+            decxb_map_entry* victim = &c->map_cache[0];
+            for (auto& e : c->map_cache) { if (!e.used) { victim = &e; break; } if (e.stamp < victim->stamp) victim = &e; }
+            victim->used = true; victim->key = k; victim->map = *m; victim->stamp = ++c->map_clock;
+        }
+    } store{ctx, key, map};
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
     cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
@@ -659,6 +678,7 @@ int make_map(decxb_ctx* ctx, CUtensorMap* map, const float* base, int64_t rows, 
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return decxb_fail(ctx, DECXB_ERR_CUDA, "cuTensorMapEncodeTiled failed: " + std::to_string((int)r));
+    store.ok = true;
     return DECXB_OK;
 }
 

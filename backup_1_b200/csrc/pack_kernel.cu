@@ -27,7 +27,7 @@ __global__ void __launch_bounds__(256)
 decxb_im2col_pack_kernel(const float4* __restrict__ src, float4* __restrict__ i2c,
                          int H, int wp, int dp4, int kW, int kH, int off_y, int off_x,
                          int out_h, int eq_w, int Kp4, int TX, int TY,
-                         int64_t src_stride4, int64_t i2c_stride4)
+                         int64_t src_stride4, int64_t i2c_stride4, const decxb_bounds bnd)
 {
     const int tid = threadIdx.x;
     if (tid >= TX * TY) return;
@@ -51,8 +51,8 @@ decxb_im2col_pack_kernel(const float4* __restrict__ src, float4* __restrict__ i2
         for (int x = x_begin + ty; x < x_end; x += TY) {
             const int q = x + dq;
             float4 v = zero;
-            if (row_ok && q >= 0 && q < wp) v = __ldg(s_row + (int64_t)q * dp4);
-            o_row[(int64_t)x * Kp4 + t] = v;
+            if (row_ok && q >= 0 && q < wp && DECXB_OK_IN(bnd, s_row + (int64_t)q * dp4, 16)) v = __ldg(s_row + (int64_t)q * dp4);
+            if (DECXB_OK_OUT0(bnd, o_row + (int64_t)x * Kp4 + t, 16)) o_row[(int64_t)x * Kp4 + t] = v;
         }
     }
 }
@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(256)
 decxb_im2col_pack_staged_kernel(const float4* __restrict__ src, float4* __restrict__ i2c,
                                 int H, int wp, int dp4, int kW, int kH, int off_y, int off_x,
                                 int out_h, int eq_w, int Kp4, int TX, int TY,
-                                int64_t src_stride4, int64_t i2c_stride4)
+                                int64_t src_stride4, int64_t i2c_stride4, const decxb_bounds bnd)
 {
     extern __shared__ float4 stage[];                 /* [kH][PX][dp4], PX = PACK_X_PER_BLOCK + kW - 1 */
     const int tid = threadIdx.x;
@@ -89,7 +89,7 @@ decxb_im2col_pack_staged_kernel(const float4* __restrict__ src, float4* __restri
         const float4* __restrict__ s_row = s_img + ((int64_t)r * wp + q0) * dp4;
         float4* st = stage + ky * row4;
         for (int i = tid; i < row4; i += blockDim.x)
-            st[i] = (row_ok && i >= i_lo && i < i_hi) ? __ldg(s_row + i) : zero;
+            st[i] = (row_ok && i >= i_lo && i < i_hi && DECXB_OK_IN(bnd, s_row + i, 16)) ? __ldg(s_row + i) : zero;
     }
     __syncthreads();
 
@@ -102,7 +102,7 @@ decxb_im2col_pack_staged_kernel(const float4* __restrict__ src, float4* __restri
         const float4* st = stage + ky * row4 + (t - ky * seg4);
 #pragma unroll 4
         for (int x = x_begin + ty; x < x_end; x += TY)
-            o_row[(int64_t)x * Kp4 + t] = st[(x - x_begin) * dp4];
+            if (DECXB_OK_OUT0(bnd, o_row + (int64_t)x * Kp4 + t, 16)) o_row[(int64_t)x * Kp4 + t] = st[(x - x_begin) * dp4];
     }
 }
 
@@ -231,6 +231,8 @@ int decxb_launch_pack(decxb_ctx* ctx, const float* src, int64_t W, int64_t H, in
     const int off_x = flag == DECXB_CONV_ZERO_COMPENSATE ? -(int)(kW / 2) : 0;
     const int block = (TX * TY + 31) / 32 * 32;
     const size_t stage_bytes = (size_t)kH * (PACK_X_PER_BLOCK + kW - 1) * dp * sizeof(float);
+    const decxb_bounds bnd = {ctx->d_status, decxb_make_extent(src, (size_t)((batch - 1) * src_stride + H * wp * dp) * 4),
+                              decxb_make_extent(i2c, (size_t)((batch - 1) * i2c_stride + g.M * g.Kp) * 4), {}, DECXB_BK_PACK};
     /* copy-engine path: channels fit one TMA box, the staged rows fit shared memory, batch fits
      * a tensor-map dimension */
     if (ctx->pack_variant == 0 && dp <= 256 && stage_bytes + 128 <= 112 * 1024 && batch <= 0x7fffffffLL)
@@ -246,7 +248,7 @@ int decxb_launch_pack(decxb_ctx* ctx, const float* src, int64_t W, int64_t H, in
         decxb_im2col_pack_staged_kernel<<<grid, block < 128 ? 128 : block, stage_bytes, s>>>(
             reinterpret_cast<const float4*>(src), reinterpret_cast<float4*>(i2c),
             (int)H, (int)wp, (int)(dp / 4), (int)kW, (int)kH, off_y, off_x,
-            (int)g.out_h, (int)g.eq_w, Kp4, TX, TY, src_stride / 4, i2c_stride / 4);
+            (int)g.out_h, (int)g.eq_w, Kp4, TX, TY, src_stride / 4, i2c_stride / 4, bnd);
         DECXB_CUDA_TRY(ctx, cudaGetLastError());
         return DECXB_OK;
     }
@@ -254,7 +256,7 @@ int decxb_launch_pack(decxb_ctx* ctx, const float* src, int64_t W, int64_t H, in
     decxb_im2col_pack_kernel<<<grid, block, 0, s>>>(
         reinterpret_cast<const float4*>(src), reinterpret_cast<float4*>(i2c),
         (int)H, (int)wp, (int)(dp / 4), (int)kW, (int)kH, off_y, off_x,
-        (int)g.out_h, (int)g.eq_w, Kp4, TX, TY, src_stride / 4, i2c_stride / 4);
+        (int)g.out_h, (int)g.eq_w, Kp4, TX, TY, src_stride / 4, i2c_stride / 4, bnd);
     DECXB_CUDA_TRY(ctx, cudaGetLastError());
     return DECXB_OK;
 }

@@ -33,13 +33,13 @@ __device__ __forceinline__ void allow_dependent_launch() { asm volatile("griddep
 
 __global__ void __launch_bounds__(256)
 decxb_fill_uniform_kernel(float* __restrict__ dst, uint64_t rows, uint64_t cols, uint64_t pitch,
-                          uint32_t seed, uint64_t first_index)
+                          uint32_t seed, uint64_t first_index, const decxb_bounds bnd)
 {
     const uint64_t total = rows * pitch;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (uint64_t)gridDim.x * blockDim.x) {
         const uint64_t r = i / pitch, c = i - r * pitch;
-        dst[i] = c < cols ? uniform_pm1(seed, first_index + r * cols + c) : 0.0f;
+        if (DECXB_OK_OUT0(bnd, dst + i, 4)) dst[i] = c < cols ? uniform_pm1(seed, first_index + r * cols + c) : 0.0f;
     }
 }
 
@@ -55,7 +55,8 @@ extern "C" int decxb_fill_uniform_f32(decxb_ctx* ctx, float* dptr, uint64_t rows
     int blocks = (int)((total + 255) / 256 < (uint64_t)ctx->sm_count * 16 ? (total + 255) / 256 : (uint64_t)ctx->sm_count * 16);
     {
         decxb_launch_scope scope(ctx, s, DECXB_K_FILL);
-        decxb_fill_uniform_kernel<<<blocks, 256, 0, s>>>(dptr, rows, cols, pitch, seed, first_index);
+        const decxb_bounds bnd = {ctx->d_status, {}, decxb_make_extent(dptr, (size_t)total * 4), {}, DECXB_BK_FILL};
+        decxb_fill_uniform_kernel<<<blocks, 256, 0, s>>>(dptr, rows, cols, pitch, seed, first_index, bnd);
     }
     DECXB_CUDA_TRY(ctx, cudaGetLastError());
     return DECXB_OK;
@@ -85,6 +86,7 @@ struct SplitRowsArgs {
     const float* in; int64_t rows, cols, ld_in;
     float *hi, *lo; int64_t ld_out, rows_out;
     int in_vec_ok; int64_t nbatch, in_batch_stride; int raw;
+    decxb_bounds bnd;
 };
 
 /* The work of block `bid` of `nblocks` blocks of 256 threads. */
@@ -101,18 +103,20 @@ __device__ __forceinline__ void split_rows_body(const SplitRowsArgs& a, int64_t 
         if (r < a.rows) {
             const float* p = a.in + b * a.in_batch_stride + r * a.ld_in + c;
             if (a.in_vec_ok && c + 3 < a.cols) {
-                const float4 t = __ldg(reinterpret_cast<const float4*>(p));
-                v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+                if (DECXB_OK_IN(a.bnd, p, 16)) {
+                    const float4 t = __ldg(reinterpret_cast<const float4*>(p));
+                    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+                }
             } else {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) if (c + j < a.cols) v[j] = __ldg(p + j);
+                for (int j = 0; j < 4; ++j) if (c + j < a.cols && DECXB_OK_IN(a.bnd, p + j, 4)) v[j] = __ldg(p + j);
             }
         }
         float4 h, l;
         if (a.raw) { h = make_float4(v[0], v[1], v[2], v[3]); l = h; }
         else { split1(v[0], h.x, l.x); split1(v[1], h.y, l.y); split1(v[2], h.z, l.z); split1(v[3], h.w, l.w); }
-        *reinterpret_cast<float4*>(a.hi + r_all * a.ld_out + c) = h;
-        if (a.lo && !a.raw) *reinterpret_cast<float4*>(a.lo + r_all * a.ld_out + c) = l;
+        if (DECXB_OK_OUT0(a.bnd, a.hi + r_all * a.ld_out + c, 16)) *reinterpret_cast<float4*>(a.hi + r_all * a.ld_out + c) = h;
+        if (a.lo && !a.raw && DECXB_OK_OUT1(a.bnd, a.lo + r_all * a.ld_out + c, 16)) *reinterpret_cast<float4*>(a.lo + r_all * a.ld_out + c) = l;
     }
 }
 
@@ -121,6 +125,15 @@ decxb_split_rows_kernel(const SplitRowsArgs a)
 {
     allow_dependent_launch();
     split_rows_body(a, blockIdx.x, gridDim.x);
+}
+
+static decxb_bounds split_rows_bounds(decxb_ctx* ctx, const float* in, int64_t rows, int64_t cols, int64_t ld_in, float* hi, float* lo,
+                                      int64_t ld_out, int64_t rows_out, int64_t nbatch, int64_t in_batch_stride)
+{
+    const size_t in_elems = rows > 0 ? (size_t)((nbatch - 1) * in_batch_stride + (rows - 1) * ld_in + cols) : 0;
+    const size_t out_elems = (size_t)(nbatch * rows_out * ld_out);
+    return decxb_bounds{ctx->d_status, decxb_make_extent(in, in_elems * 4), decxb_make_extent(hi, out_elems * 4),
+                        decxb_make_extent(lo, out_elems * 4), DECXB_BK_SPLIT_ROWS};
 }
 
 int decxb_launch_split_rows(decxb_ctx* ctx, const float* in, int64_t rows, int64_t cols, int64_t ld_in,
@@ -136,7 +149,8 @@ int decxb_launch_split_rows(decxb_ctx* ctx, const float* in, int64_t rows, int64
     if (blocks > (int64_t)ctx->sm_count * 32) blocks = (int64_t)ctx->sm_count * 32;
     {
         decxb_launch_scope scope(ctx, s, DECXB_K_SPLIT);
-        const SplitRowsArgs a = {in, rows, cols, ld_in, hi, lo, ld_out, rows_out, vec_ok, nbatch, in_batch_stride, raw};
+        const SplitRowsArgs a = {in, rows, cols, ld_in, hi, lo, ld_out, rows_out, vec_ok, nbatch, in_batch_stride, raw,
+                                 split_rows_bounds(ctx, in, rows, cols, ld_in, hi, lo, ld_out, rows_out, nbatch, in_batch_stride)};
         decxb_split_rows_kernel<<<(int)blocks, 256, 0, s>>>(a);
     }
     DECXB_CUDA_TRY(ctx, cudaGetLastError());
@@ -145,45 +159,6 @@ int decxb_launch_split_rows(decxb_ctx* ctx, const float* in, int64_t rows, int64
 
 /* in[K][ld_in] (K rows, N columns) -> hi/lo[N][ld_out] with K contiguous.  64x64 tiles
  * through shared memory; `raw` stores hi = a unrounded (plain-TF32 mode) and skips lo. */
-__global__ void __launch_bounds__(256)
-decxb_split_transpose_kernel(const float* __restrict__ in, int64_t K, int64_t N, int64_t ld_in,
-                             float* __restrict__ hi, float* __restrict__ lo, int64_t ld_out, int raw,
-                             int64_t tiles_n, int64_t nbatch, int64_t in_batch_stride, int64_t out_batch_rows)
-{
-    __shared__ float tile[64][65];
-    allow_dependent_launch();
-    const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;   /* 64 x 4 */
-    const int64_t tiles_k = (ld_out + 63) / 64;
-    const int64_t n_tiles = tiles_k * tiles_n;
-    const float* const in0 = in; float* const hi0 = hi; float* const lo0 = lo;
-    for (int64_t tt = blockIdx.x; tt < n_tiles * nbatch; tt += gridDim.x) {
-        const int64_t bb = tt / n_tiles, t = tt - bb * n_tiles;
-        in = in0 + bb * in_batch_stride; hi = hi0 + bb * out_batch_rows * ld_out; lo = lo0 ? lo0 + bb * out_batch_rows * ld_out : nullptr;
-        const int64_t k0 = (t / tiles_n) * 64, n0 = (t % tiles_n) * 64;
-#pragma unroll 4
-        for (int j = ty; j < 64; j += 4) {
-            const int64_t k = k0 + j, n = n0 + tx;
-            tile[j][tx] = (k < K && n < N) ? __ldg(in + k * ld_in + n) : 0.0f;
-        }
-        __syncthreads();
-#pragma unroll 4
-        for (int j = ty; j < 64; j += 4) {
-            const int64_t n = n0 + j, k = k0 + tx;
-            if (n < N && k < ld_out) {
-                const float a = tile[tx][j];
-                if (raw) {
-                    hi[n * ld_out + k] = a;
-                } else {
-                    float h, l; split1(a, h, l);
-                    hi[n * ld_out + k] = h;
-                    lo[n * ld_out + k] = l;
-                }
-            }
-        }
-        __syncthreads();
-    }
-}
-
 /* Vectorised form for 16-byte aligned input with a pitch that is a multiple of 4: 128-bit
  * loads along n into the tile, 128-bit stores along k out of it.  A thread of the store phase
  * owns 4 consecutive k of one n, so a 16-thread group writes one 256-byte run of an output
@@ -192,6 +167,7 @@ struct SplitTransposeArgs {
     const float* in; int64_t K, N, ld_in;
     float *hi, *lo; int64_t ld_out; int raw;
     int64_t tiles_n, nbatch, in_batch_stride, out_batch_rows;
+    decxb_bounds bnd;
 };
 
 __device__ __forceinline__ void split_transpose_vec_body(const SplitTransposeArgs& a, float (*tile)[65], int64_t bid, int64_t nblocks)
@@ -213,11 +189,11 @@ __device__ __forceinline__ void split_transpose_vec_body(const SplitTransposeArg
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (k < a.K) {
                 const float* p = in + k * a.ld_in + n;
-                if (n + 3 < a.N) v = __ldg(reinterpret_cast<const float4*>(p));
+                if (n + 3 < a.N) { if (DECXB_OK_IN(a.bnd, p, 16)) v = __ldg(reinterpret_cast<const float4*>(p)); }
                 else {
-                    if (n < a.N) v.x = __ldg(p);
-                    if (n + 1 < a.N) v.y = __ldg(p + 1);
-                    if (n + 2 < a.N) v.z = __ldg(p + 2);
+                    if (n < a.N && DECXB_OK_IN(a.bnd, p, 4)) v.x = __ldg(p);
+                    if (n + 1 < a.N && DECXB_OK_IN(a.bnd, p + 1, 4)) v.y = __ldg(p + 1);
+                    if (n + 2 < a.N && DECXB_OK_IN(a.bnd, p + 2, 4)) v.z = __ldg(p + 2);
                 }
             }
             tile[kr][n4] = v.x; tile[kr][n4 + 1] = v.y; tile[kr][n4 + 2] = v.z; tile[kr][n4 + 3] = v.w;
@@ -233,8 +209,47 @@ __device__ __forceinline__ void split_transpose_vec_body(const SplitTransposeArg
                 float4 h, l;
                 if (a.raw) { h = make_float4(a0, a1, a2, a3); }
                 else { split1(a0, h.x, l.x); split1(a1, h.y, l.y); split1(a2, h.z, l.z); split1(a3, h.w, l.w); }
-                *reinterpret_cast<float4*>(hi + n * a.ld_out + k) = h;
-                if (!a.raw) *reinterpret_cast<float4*>(lo + n * a.ld_out + k) = l;
+                if (DECXB_OK_OUT0(a.bnd, hi + n * a.ld_out + k, 16)) *reinterpret_cast<float4*>(hi + n * a.ld_out + k) = h;
+                if (!a.raw && DECXB_OK_OUT1(a.bnd, lo + n * a.ld_out + k, 16)) *reinterpret_cast<float4*>(lo + n * a.ld_out + k) = l;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+/* The same for inputs that do not allow 128-bit accesses: one word per thread and step. */
+__global__ void __launch_bounds__(256)
+decxb_split_transpose_kernel(const SplitTransposeArgs a)
+{
+    __shared__ float tile[64][65];
+    allow_dependent_launch();
+    const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;   /* 64 x 4 */
+    const int64_t tiles_k = (a.ld_out + 63) / 64;
+    const int64_t n_tiles = tiles_k * a.tiles_n;
+    for (int64_t tt = blockIdx.x; tt < n_tiles * a.nbatch; tt += gridDim.x) {
+        const int64_t bb = tt / n_tiles, t = tt - bb * n_tiles;
+        const float* in = a.in + bb * a.in_batch_stride;
+        float* hi = a.hi + bb * a.out_batch_rows * a.ld_out;
+        float* lo = a.lo ? a.lo + bb * a.out_batch_rows * a.ld_out : nullptr;
+        const int64_t k0 = (t / a.tiles_n) * 64, n0 = (t % a.tiles_n) * 64;
+#pragma unroll 4
+        for (int j = ty; j < 64; j += 4) {
+            const int64_t k = k0 + j, n = n0 + tx;
+            tile[j][tx] = (k < a.K && n < a.N && DECXB_OK_IN(a.bnd, in + k * a.ld_in + n, 4)) ? __ldg(in + k * a.ld_in + n) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int j = ty; j < 64; j += 4) {
+            const int64_t n = n0 + j, k = k0 + tx;
+            if (n < a.N && k < a.ld_out) {
+                const float v = tile[tx][j];
+                if (a.raw) {
+                    if (DECXB_OK_OUT0(a.bnd, hi + n * a.ld_out + k, 4)) hi[n * a.ld_out + k] = v;
+                } else {
+                    float h, l; split1(v, h, l);
+                    if (DECXB_OK_OUT0(a.bnd, hi + n * a.ld_out + k, 4)) hi[n * a.ld_out + k] = h;
+                    if (DECXB_OK_OUT1(a.bnd, lo + n * a.ld_out + k, 4)) lo[n * a.ld_out + k] = l;
+                }
             }
         }
         __syncthreads();
@@ -261,6 +276,15 @@ decxb_split_ab_kernel(const SplitRowsArgs ra, const SplitTransposeArgs ta, int b
     else split_transpose_vec_body(ta, tile, (int64_t)blockIdx.x - blocks_rows, (int64_t)gridDim.x - blocks_rows);
 }
 
+static decxb_bounds split_transpose_bounds(decxb_ctx* ctx, const float* in, int64_t K, int64_t N, int64_t ld_in, float* hi, float* lo,
+                                           int64_t ld_out, int64_t nbatch, int64_t in_batch_stride, int64_t out_batch_rows)
+{
+    const size_t in_elems = (size_t)((nbatch - 1) * in_batch_stride + (K - 1) * ld_in + N);
+    const size_t out_elems = (size_t)(((nbatch - 1) * out_batch_rows + N) * ld_out);
+    return decxb_bounds{ctx->d_status, decxb_make_extent(in, in_elems * 4), decxb_make_extent(hi, out_elems * 4),
+                        decxb_make_extent(lo, out_elems * 4), DECXB_BK_SPLIT_TRANSPOSE};
+}
+
 bool decxb_split_ab_possible(const float* B, int64_t ldb, const float* b_hi, const float* b_lo)
 {
     return ((uintptr_t)B % 16 == 0) && (ldb % 4 == 0) && ((uintptr_t)b_hi % 16 == 0) && ((uintptr_t)b_lo % 16 == 0);
@@ -277,8 +301,10 @@ int decxb_launch_split_ab(decxb_ctx* ctx, const float* A, int64_t M, int64_t K, 
     if (blocks_rows > cap) blocks_rows = cap;
     if (blocks_t > cap) blocks_t = cap;
     const int vec_ok = ((uintptr_t)A % 16 == 0) && (lda % 4 == 0);
-    const SplitRowsArgs ra = {A, M, K, lda, a_hi, a_lo, ld_out, M, vec_ok, 1, 0, 0};
-    const SplitTransposeArgs ta = {B, K, N, ldb, b_hi, b_lo, ld_out, 0, tiles_n, 1, 0, 0};
+    const SplitRowsArgs ra = {A, M, K, lda, a_hi, a_lo, ld_out, M, vec_ok, 1, 0, 0,
+                              split_rows_bounds(ctx, A, M, K, lda, a_hi, a_lo, ld_out, M, 1, 0)};
+    const SplitTransposeArgs ta = {B, K, N, ldb, b_hi, b_lo, ld_out, 0, tiles_n, 1, 0, 0,
+                                   split_transpose_bounds(ctx, B, K, N, ldb, b_hi, b_lo, ld_out, 1, 0, 0)};
     {
         decxb_launch_scope scope(ctx, s, DECXB_K_SPLIT);
         decxb_split_ab_kernel<<<(int)(blocks_rows + blocks_t), 256, 0, s>>>(ra, ta, (int)blocks_rows);
@@ -297,18 +323,18 @@ int decxb_launch_split_transpose(decxb_ctx* ctx, const float* in, int64_t K, int
     int64_t blocks = tiles_n * tiles_k * nbatch;
     if (blocks == 0) return DECXB_OK;
     if (blocks > (int64_t)ctx->sm_count * 16) blocks = (int64_t)ctx->sm_count * 16;
+    const SplitTransposeArgs a = {in, K, N, ld_in, hi, lo, ld_out, raw, tiles_n, nbatch, in_batch_stride, out_batch_rows,
+                                  split_transpose_bounds(ctx, in, K, N, ld_in, hi, lo, ld_out, nbatch, in_batch_stride, out_batch_rows)};
     if (((uintptr_t)in % 16 == 0) && (ld_in % 4 == 0) && (in_batch_stride % 4 == 0) && ((uintptr_t)hi % 16 == 0) &&
         (raw || (uintptr_t)lo % 16 == 0)) {
         decxb_launch_scope scope(ctx, s, DECXB_K_SPLIT);
-        const SplitTransposeArgs a = {in, K, N, ld_in, hi, lo, ld_out, raw, tiles_n, nbatch, in_batch_stride, out_batch_rows};
         decxb_split_transpose_vec_kernel<<<(int)blocks, 256, 0, s>>>(a);
         DECXB_CUDA_TRY(ctx, cudaGetLastError());
         return DECXB_OK;
     }
     {
         decxb_launch_scope scope(ctx, s, DECXB_K_SPLIT);
-        decxb_split_transpose_kernel<<<(int)blocks, 256, 0, s>>>(in, K, N, ld_in, hi, lo, ld_out, raw, tiles_n,
-                                                                 nbatch, in_batch_stride, out_batch_rows);
+        decxb_split_transpose_kernel<<<(int)blocks, 256, 0, s>>>(a);
     }
     DECXB_CUDA_TRY(ctx, cudaGetLastError());
     return DECXB_OK;
@@ -320,7 +346,8 @@ int decxb_launch_split_transpose(decxb_ctx* ctx, const float* in, int64_t K, int
  * c >= dp and columns >= kW*kH*cp are zero. */
 __global__ void __launch_bounds__(256)
 decxb_filter_matrix_kernel(const float* __restrict__ filters, int kW, int kH, int dp, int cp, int64_t N,
-                           float* __restrict__ hi, float* __restrict__ lo, int64_t rows_out, int64_t ld_out, int raw)
+                           float* __restrict__ hi, float* __restrict__ lo, int64_t rows_out, int64_t ld_out, int raw,
+                           const decxb_bounds bnd)
 {
     allow_dependent_launch();
     const int64_t Kp = (int64_t)kW * kH * cp;
@@ -334,10 +361,14 @@ decxb_filter_matrix_kernel(const float* __restrict__ filters, int kW, int kH, in
         if (n < N && k < Kp) {
             const int64_t tap = k / cp, c = k - tap * cp;
             const int64_t ky = tap / kW, kx = tap - ky * kW;
-            if (c < dp) a = __ldg(filters + n * gap + (ky * kwp + kx) * dp + c);
+            if (c < dp && DECXB_OK_IN(bnd, filters + n * gap + (ky * kwp + kx) * dp + c, 4)) a = __ldg(filters + n * gap + (ky * kwp + kx) * dp + c);
         }
-        if (raw) { hi[i] = a; }
-        else { float h, l; split1(a, h, l); hi[i] = h; lo[i] = l; }
+        if (raw) { if (DECXB_OK_OUT0(bnd, hi + i, 4)) hi[i] = a; }
+        else {
+            float h, l; split1(a, h, l);
+            if (DECXB_OK_OUT0(bnd, hi + i, 4)) hi[i] = h;
+            if (DECXB_OK_OUT1(bnd, lo + i, 4)) lo[i] = l;
+        }
     }
 }
 
@@ -353,7 +384,10 @@ int decxb_launch_filter_matrix(decxb_ctx* ctx, const float* filters, int64_t kW,
     if (blocks > (int64_t)ctx->sm_count * 16) blocks = (int64_t)ctx->sm_count * 16;
     {
         decxb_launch_scope scope(ctx, s, DECXB_K_SPLIT);
-        decxb_filter_matrix_kernel<<<(int)blocks, 256, 0, s>>>(filters, (int)kW, (int)kH, (int)dp, (int)cp, N, hi, lo, rows_out, ld_out, raw);
+        const size_t bank = (size_t)N * (size_t)(dp * decxb_ceil_to(kW, 4) * kH) * 4;
+        const decxb_bounds bnd = {ctx->d_status, decxb_make_extent(filters, bank), decxb_make_extent(hi, (size_t)total * 4),
+                                  decxb_make_extent(lo, (size_t)total * 4), DECXB_BK_FILTER_MATRIX};
+        decxb_filter_matrix_kernel<<<(int)blocks, 256, 0, s>>>(filters, (int)kW, (int)kH, (int)dp, (int)cp, N, hi, lo, rows_out, ld_out, raw, bnd);
     }
     DECXB_CUDA_TRY(ctx, cudaGetLastError());
     return DECXB_OK;
@@ -363,7 +397,7 @@ int decxb_launch_filter_matrix(decxb_ctx* ctx, const float* filters, int64_t kW,
  * 16-bit words through shared memory; output columns k >= K (up to ld_out) are zero. */
 __global__ void __launch_bounds__(256)
 decxb_transpose_f16_kernel(const unsigned short* __restrict__ in, int64_t K, int64_t N, int64_t ld_in,
-                           unsigned short* __restrict__ out, int64_t ld_out, int64_t tiles_n)
+                           unsigned short* __restrict__ out, int64_t ld_out, int64_t tiles_n, const decxb_bounds bnd)
 {
     __shared__ unsigned short tile[64][66];
     const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
@@ -374,13 +408,13 @@ decxb_transpose_f16_kernel(const unsigned short* __restrict__ in, int64_t K, int
 #pragma unroll 4
         for (int j = ty; j < 64; j += 4) {
             const int64_t k = k0 + j, n = n0 + tx;
-            tile[j][tx] = (k < K && n < N) ? in[k * ld_in + n] : (unsigned short)0;
+            tile[j][tx] = (k < K && n < N && DECXB_OK_IN(bnd, in + k * ld_in + n, 2)) ? in[k * ld_in + n] : (unsigned short)0;
         }
         __syncthreads();
 #pragma unroll 4
         for (int j = ty; j < 64; j += 4) {
             const int64_t n = n0 + j, k = k0 + tx;
-            if (n < N && k < ld_out) out[n * ld_out + k] = tile[tx][j];
+            if (n < N && k < ld_out && DECXB_OK_OUT0(bnd, out + n * ld_out + k, 2)) out[n * ld_out + k] = tile[tx][j];
         }
         __syncthreads();
     }
@@ -396,9 +430,38 @@ int decxb_launch_transpose_f16(decxb_ctx* ctx, const void* in, int64_t K, int64_
     if (blocks > (int64_t)ctx->sm_count * 16) blocks = (int64_t)ctx->sm_count * 16;
     {
         decxb_launch_scope scope(ctx, s, DECXB_K_SPLIT);
+        const decxb_bounds bnd = {ctx->d_status, decxb_make_extent(in, (size_t)((K - 1) * ld_in + N) * 2),
+                                  decxb_make_extent(out, (size_t)(N * ld_out) * 2), {}, DECXB_BK_TRANSPOSE_F16};
         decxb_transpose_f16_kernel<<<(int)blocks, 256, 0, s>>>(static_cast<const unsigned short*>(in), K, N, ld_in,
-                                                               static_cast<unsigned short*>(out), ld_out, tiles_n);
+                                                               static_cast<unsigned short*>(out), ld_out, tiles_n, bnd);
     }
     DECXB_CUDA_TRY(ctx, cudaGetLastError());
     return DECXB_OK;
+}
+
+/* Self-test of the debug bounds build: splits a small matrix while the launcher is told that the
+ * input array is one row shorter than it is.  The memory IS there (nothing can fault); the check
+ * must trip, skip the accesses to that row and leave DECXB_ERR_BOUNDS for the host. */
+extern "C" int decxb_selftest_bounds(decxb_ctx* ctx)
+{
+    int rc = decxb_bind(ctx);
+    if (rc) return rc;
+    if (!decxb_bounds_build()) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "this library was built without DECXB_BOUNDS");
+    const int64_t rows = 64, cols = 128;
+    float *in = nullptr, *hi = nullptr, *lo = nullptr;
+    if ((rc = decxb_malloc(ctx, rows * cols * 4, (void**)&in)) || (rc = decxb_malloc(ctx, rows * cols * 4, (void**)&hi)) ||
+        (rc = decxb_malloc(ctx, rows * cols * 4, (void**)&lo))) return rc;
+    cudaStream_t s = ctx->stream;
+    DECXB_CUDA_TRY(ctx, cudaMemsetAsync(in, 0, rows * cols * 4, s));
+    {
+        SplitRowsArgs a = {in, rows, cols, cols, hi, lo, cols, rows, 1, 1, 0, 0,
+                           split_rows_bounds(ctx, in, rows - 1, cols, cols, hi, lo, cols, rows, 1, 0)};   /* declared one row short */
+        decxb_launch_scope scope(ctx, s, DECXB_K_SPLIT);
+        decxb_split_rows_kernel<<<32, 256, 0, s>>>(a);
+    }
+    DECXB_CUDA_TRY(ctx, cudaGetLastError());
+    DECXB_CUDA_TRY(ctx, cudaStreamSynchronize(s));
+    rc = decxb_check_dev_status(ctx);
+    decxb_free(ctx, in); decxb_free(ctx, hi); decxb_free(ctx, lo);
+    return rc;
 }

@@ -21,7 +21,11 @@ class DecxbError(RuntimeError):
 
 
 def library_path() -> Path:
-    return _PKG / "libdecxb.so"
+    """The CUDA library; DECXB_LIBRARY may name another build of it (the debug bounds build libdecxb_bounds.so)."""
+    import os
+
+    alt = os.environ.get("DECXB_LIBRARY")
+    return Path(alt) if alt else _PKG / "libdecxb.so"
 
 
 class ConvGeom(C.Structure):
@@ -110,6 +114,8 @@ SIGNATURES = {
     "decxb_gemm_f32_rowshard_gather": (_i, [_vp, _vp, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i, _vp]),
     "decxb_comm_selftest_handshake": (_i, [C.c_char_p, _i, _i, _vp, _i, C.c_char_p, _sz]),
     "decxb_probe_tensor_peak": (_i, [_vp, _i, C.c_double, C.POINTER(TensorProbe)]),
+    "decxb_bounds_build": (_i, []),
+    "decxb_selftest_bounds": (_i, [_vp]),
     "decxb_version": (C.c_char_p, []),
 }
 

@@ -325,6 +325,16 @@ class Bench:
                 def step():  # noqa: F811
                     ctx.gemm_f16(M_rank, N, K, dA, K, dB, N, dD, N, stream=self.st)
             w["step"] = step
+            if mode_name != "f16":
+                def prepare():
+                    w["pb"] = ctx.prepare_b(K, N, dB, N, mode=mode, stream=self.st)
+
+                def step_prepared():
+                    ctx.gemm_prepared(M_rank, dA, K, w["pb"], dD, N, tile=args.tile, stream=self.st)
+
+                def release():
+                    ctx.release_b(w.pop("pb"), stream=self.st)
+                w.update(prepare=prepare, step_prepared=step_prepared, release=release)
             if host_leg:
                 hA = torch.empty((M_rank, K), pin_memory=True, dtype=dA.dtype); hB = torch.empty((K, N), pin_memory=True, dtype=dA.dtype)
                 hD = torch.empty((M_rank, N), pin_memory=True, dtype=dA.dtype)
@@ -368,6 +378,17 @@ class Bench:
                 if nb:
                     ctx.conv2_im2col(dS, W, H, C, dF, kW, kH, F, dO, flag=1, batch=nb, mode=mode, algo=algo, stream=self.st)
             w["step"] = step
+
+            def prepare():
+                w["pf"] = ctx.conv_prepare_filters(dF, kW, kH, C, F, mode=mode, algo=algo, stream=self.st)
+
+            def step_prepared():
+                if nb:
+                    ctx.conv2_im2col_prepared(dS, W, H, w["pf"], dO, flag=1, batch=nb, stream=self.st)
+
+            def release():
+                ctx.conv_release_filters(w.pop("pf"), stream=self.st)
+            w.update(prepare=prepare, step_prepared=step_prepared, release=release)
             if host_leg:
                 hS = torch.empty(dS.shape, pin_memory=True); hF = torch.empty(dF.shape, pin_memory=True)
                 hO = torch.empty(dO.shape, pin_memory=True)
@@ -452,6 +473,37 @@ class Bench:
         ctx.profile_enable(False)
         res["prof"], res["prof_steps"] = prof, psteps
         return res
+
+    def measure_prepared(self, w, steps):
+        """The same step with the weights (B / the filter bank) prepared once outside the timed region
+        (decxb_gemm_prepare_b / decxb_conv_prepare_filters): ms per step, max over ranks."""
+        if "prepare" not in w:
+            return None
+        torch = self.torch
+        w["prepare"]()
+        for _ in range(3):
+            w["step_prepared"]()
+        self.ctx.synchronize()
+        self.barrier()
+        ms = 0.0
+        if w["flush"]:
+            evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+            for e0, e1 in evs:
+                self.flush_l2()
+                e0.record(self.ts); w["step_prepared"](); e1.record(self.ts)
+            self.barrier()
+            ms = sum(e0.elapsed_time(e1) for e0, e1 in evs)
+        else:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(self.ts)
+            for _ in range(steps):
+                w["step_prepared"]()
+            e1.record(self.ts)
+            self.barrier()
+            ms = e0.elapsed_time(e1)
+        w["release"]()
+        self.ctx.synchronize()
+        return self.max_over_ranks(ms) / steps
 
     def roofline(self, w, res):
         peaks, wl, mode, args = self.peaks, w["wl"], w["mode"], self.args
@@ -621,6 +673,7 @@ def main():
     big = w["flops"] >= 1e13
     res = bench.measure(w, args.steps, args.warmup, profile_steps=min(args.steps, 5) if big else None)
     roofline = bench.roofline(w, res)
+    ms_prepared = bench.measure_prepared(w, min(args.steps, 5) if big else args.steps)
     err = bench.check(w)
     err = bench.max_over_ranks(err) if err is not None else None
 
@@ -724,8 +777,10 @@ def main():
                 w2 = bench.build(name, wl2, args.mode, host_leg=False)
                 r2 = bench.measure(w2, steps, 3, sample_clocks=False)
                 rf2 = bench.roofline(w2, r2)
+                mp2 = bench.measure_prepared(w2, steps)
                 e2 = bench.check(w2)
                 also.append({"workload": name, "value": r2["value"], "ms_per_step": r2["ms_per_step"], "steps": steps,
+                             "ms_per_step_prepared_weights": mp2,
                              "kernel": rf2["kernel"], "kernel_tflops_or_gbs": rf2["achieved"], "kernel_frac": rf2["frac"],
                              "kernel_avg_launch_ms": rf2["avg_launch_ms"], "time_shares": rf2["time_shares"],
                              "max_norm_err": bench.max_over_ranks(e2) if e2 is not None else None,
@@ -770,6 +825,9 @@ def main():
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "ms_per_step": t_e2e / e2e_steps * 1e3},
+            "ms_per_step_prepared_weights": ms_prepared,
+            "prepared_weights_note": ("the same step with B / the filter bank split and laid out once outside the timed region "
+                                      "(decxb_gemm_prepare_b, decxb_conv_prepare_filters); `value` uses the plain entry, which prepares them on every call"),
             "gpu_launches": res["launches"], "clocks": clocks, "per_rank_ms_per_step": per_rank_ms, "also": also,
         }
         if gather:

@@ -47,7 +47,8 @@ typedef enum decxb_status {
     DECXB_ERR_ARCH         = 102, /* device is not compute capability 10.x                              */
     DECXB_ERR_TIMEOUT      = 103, /* a bounded device-side wait expired; the context stays usable       */
     DECXB_ERR_TOO_LARGE    = 104, /* request exceeds a documented fixed limit                           */
-    DECXB_ERR_COMM         = 105  /* the communication library failed or could not be loaded            */
+    DECXB_ERR_COMM         = 105, /* the communication library failed or could not be loaded            */
+    DECXB_ERR_BOUNDS       = 106  /* debug bounds build only: an access outside its array was caught    */
 } decxb_status;
 
 /* Precision of the tensor-core GEMM.  3xTF32 (default) splits every fp32 operand into a
@@ -452,6 +453,18 @@ DECXB_API int decxb_gemm_f32_rowshard_gather(decxb_ctx* ctx, decxb_comm* comm, i
  * which never arrives can be played by a stand-in library on a machine without a GPU. */
 DECXB_API int decxb_comm_selftest_handshake(const char* nccl_path, int world, int rank, const void* id128, int timeout_ms,
                                             char* err, size_t err_len);
+
+/* Debug bounds build.  `make -C backup_1_b200/csrc bounds` builds libdecxb_bounds.so, the same library
+ * compiled with -DDECXB_BOUNDS: every global load and store made by the threads of the
+ * memory-bound kernels (operand split, transposes, filter matrix, pack, fill) is checked against
+ * the extent of its array; the first violation is recorded in the status word and the access
+ * skipped (nothing faults), and the next status check (decxb_synchronize, the blocking entries)
+ * returns DECXB_ERR_BOUNDS.  decxb_bounds_build tells which library is loaded;
+ * decxb_selftest_bounds provokes one caught violation (valid memory, an extent declared one row
+ * short).  The reference has no such facility (its kernels are unchecked); it stands in for a
+ * memory checker where none can be run. */
+DECXB_API int decxb_bounds_build(void);
+DECXB_API int decxb_selftest_bounds(decxb_ctx* ctx);
 
 /* Number of kernels this library has launched on the context since it was created. */
 DECXB_API uint64_t decxb_kernel_launch_count(decxb_ctx* ctx);
