@@ -135,8 +135,12 @@ int comm_handshake(decxb_comm* c, const void* id128)
     memcpy(&id, id128, sizeof id);
     ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
     cfg.blocking = 0;
-    /* NCCL's kernels run beside the persistent GEMM kernel, whose blocks fill whole SMs: keep them few */
-    cfg.maxCTAs = c->reserve_sms;
+    /* NCCL's kernels run beside the persistent GEMM kernel, whose blocks fill whole SMs: keep them few
+     * (DECXB_COMM_MAX_CTAS overrides the default of 16 thread blocks per NCCL kernel) */
+    const char* env = getenv("DECXB_COMM_MAX_CTAS");
+    const int ctas = env && atoi(env) > 0 && atoi(env) <= 64 ? atoi(env) : c->reserve_sms;
+    cfg.maxCTAs = ctas;
+    c->reserve_sms = ctas;
     ncclResult_t rc = c->api->CommInitRankConfig(&c->comm, c->world, id, c->rank, &cfg);
     if (!c->comm && rc != ncclSuccess && rc != ncclInProgress)
         return comm_fail(c, DECXB_ERR_COMM, std::string("ncclCommInitRankConfig: ") + c->api->GetErrorString(rc));
@@ -169,15 +173,17 @@ int comm_drain(decxb_comm* c)
     }
 }
 
-/* Rows [a, b) of the `rows`-row block of one rank that belong to panel group g of G: boundaries are
- * multiples of 256 rows (whole tiles), the last group takes the rest.  A pure function of its
- * arguments, so sender and receivers agree on every panel without talking. */
+/* Rows [a, b) of the `rows`-row block of one rank that belong to panel group g of G.  The transfer of
+ * the LAST group is the only one nothing overlaps, so the last group is small (a third of an even
+ * share) and the others share the rest evenly; boundaries are multiples of 256 rows (whole tiles).
+ * A pure function of its arguments, so sender and receivers agree on every panel without talking. */
 void panel_range(int64_t rows, int g, int G, int64_t* a, int64_t* b)
 {
     auto cut = [&](int k) -> int64_t {
         if (k <= 0) return 0;
         if (k >= G) return rows;
-        int64_t c = rows * k / G / 256 * 256;
+        const int64_t last = rows / (3 * (int64_t)G);
+        int64_t c = (rows - last) * k / (G - 1) / 256 * 256;
         return c > rows ? rows : c;
     };
     *a = cut(g); *b = cut(g + 1);
@@ -370,8 +376,15 @@ extern "C" int decxb_gemm_f32_rowshard_gather(decxb_ctx* ctx, decxb_comm* c, int
         if (cudaEventRecord(ev, s) != cudaSuccess || cudaStreamWaitEvent(c->stream, ev, 0) != cudaSuccess) {
             cudaGetLastError(); rc = comm_fail(c, DECXB_ERR_CUDA, "event on the compute stream"); break;
         }
-        rc = exchange(c, reinterpret_cast<char*>(D_full), row_bytes, M,
-                      [&](int64_t n, int64_t* pa, int64_t* pbb) { panel_range(n, g, groups, pa, pbb); }, c->stream);
+        if (groups == 1 && M % c->world == 0) {
+            /* one group of equal blocks: NCCL's own all-gather, in place */
+            ncclResult_t r = c->api->AllGather(reinterpret_cast<char*>(D_full) + (size_t)f * row_bytes, D_full, (size_t)rows * row_bytes,
+                                               ncclChar, c->comm, c->stream);
+            rc = comm_settle(c, r, "ncclAllGather");
+        } else {
+            rc = exchange(c, reinterpret_cast<char*>(D_full), row_bytes, M,
+                          [&](int64_t n, int64_t* pa, int64_t* pbb) { panel_range(n, g, groups, pa, pbb); }, c->stream);
+        }
     }
     if (pb) decxb_gemm_release_b(ctx, pb, s);
     if (rc) return rc;

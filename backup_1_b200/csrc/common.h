@@ -28,6 +28,7 @@ struct decxb_dev_status {
 /* Per-device tables (kernel attributes set once per device) are sized by this; decxb_init
  * refuses device indices beyond it. */
 #define DECXB_MAX_DEVICES 64
+#define DECXB_WAVE_SLOTS 32
 
 enum {
     DECXB_DEVERR_NONE = 0,
@@ -113,6 +114,15 @@ struct decxb_ctx {
     std::mutex map_mtx;
     decxb_map_entry map_cache[16];
     uint64_t map_clock = 0;
+    /* wave alignment of the GEMM kernel: one monotonic counter per launching stream (so that launches on
+     * different streams, whose order on the GPU is not the host's, never share one), and what it will read
+     * when the launches queued so far have run */
+    unsigned long long* wave_counters = nullptr;      /* device, DECXB_WAVE_SLOTS words, zero at start */
+    std::mutex wave_mtx;
+    struct WaveSlot { cudaStream_t stream; unsigned long long base; bool used; } wave_slots[DECXB_WAVE_SLOTS] = {};
+    int wave_align = 1;                               /* decxb_set_wave_align */
+    unsigned long long* trace = nullptr;   /* decxb_set_tile_trace: device buffer [clusters][trace_tiles] of tile start times */
+    int trace_tiles = 0;
     int tile_group = 8;                 /* tile-rows per group of the GEMM kernel's tile order (decxb_set_tile_group) */
     int reserved_sms = 0;               /* SMs the next GEMM launches leave free (a transfer kernel runs beside them) */
     int inject_countdown = -1;          /* >= 0: that many pipeline CUDA calls from now, one reports a failure (tests) */
@@ -150,6 +160,12 @@ int decxb_bind(decxb_ctx* ctx);
  * the release is still running; a taker on another stream waits for it on the device. */
 int decxb_malloc_on_stream(decxb_ctx* ctx, size_t bytes, void** dptr, cudaStream_t s);
 int decxb_free_on_stream(decxb_ctx* ctx, void* dptr, cudaStream_t s);
+/* Wave alignment bookkeeping: the counter of stream `s` and its value before a launch that will add `arrivals`
+ * to it (false: no slot free, launch without alignment); _unslot takes the arrivals of a launch that was not made
+ * back; _reset zeroes everything after a launch gave up (device idle). */
+bool decxb_wave_slot(decxb_ctx* ctx, cudaStream_t s, unsigned long long arrivals, unsigned long long** counter, unsigned long long* base);
+void decxb_wave_unslot(decxb_ctx* ctx, cudaStream_t s, unsigned long long arrivals);
+void decxb_wave_reset(decxb_ctx* ctx);
 /* Reads (and clears) the device status word after a synchronisation. */
 int decxb_check_dev_status(decxb_ctx* ctx);
 

@@ -79,7 +79,9 @@ extern "C" int decxb_init(int device, decxb_ctx** out)
            && cudaStreamCreateWithFlags(&ctx->copy_stream[1], cudaStreamNonBlocking) == cudaSuccess
            && cudaMalloc((void**)&ctx->d_status, sizeof(decxb_dev_status)) == cudaSuccess
            && cudaMemset(ctx->d_status, 0, sizeof(decxb_dev_status)) == cudaSuccess
-           && cudaHostAlloc((void**)&ctx->h_status, sizeof(decxb_dev_status), cudaHostAllocDefault) == cudaSuccess;
+           && cudaHostAlloc((void**)&ctx->h_status, sizeof(decxb_dev_status), cudaHostAllocDefault) == cudaSuccess
+           && cudaMalloc((void**)&ctx->wave_counters, DECXB_WAVE_SLOTS * sizeof(unsigned long long)) == cudaSuccess
+           && cudaMemset(ctx->wave_counters, 0, DECXB_WAVE_SLOTS * sizeof(unsigned long long)) == cudaSuccess;
     if (!ok) { cudaGetLastError(); delete ctx; return DECXB_ERR_CUDA; }
     memset(ctx->h_status, 0, sizeof(decxb_dev_status));
     *out = ctx;
@@ -95,6 +97,7 @@ extern "C" int decxb_destroy(decxb_ctx* ctx)
         for (auto& kv : ctx->arena.live) cudaFree(kv.first);
         for (cudaEvent_t e : ctx->arena.ev_pool) cudaEventDestroy(e);
         cudaFree(ctx->d_status);
+        cudaFree(ctx->wave_counters);
         cudaFreeHost(ctx->h_status);
         cudaStreamDestroy(ctx->stream);
         cudaStreamDestroy(ctx->copy_stream[0]);
@@ -122,6 +125,52 @@ extern "C" int decxb_set_tile_group(decxb_ctx* ctx, int tile_rows)
     return DECXB_OK;
 }
 
+bool decxb_wave_slot(decxb_ctx* ctx, cudaStream_t s, unsigned long long arrivals, unsigned long long** counter, unsigned long long* base)
+{
+    std::lock_guard<std::mutex> lock(ctx->wave_mtx);
+    int free_slot = -1;
+    for (int i = 0; i < DECXB_WAVE_SLOTS; ++i) {
+        auto& w = ctx->wave_slots[i];
+        if (w.used && w.stream == s) { *counter = ctx->wave_counters + i; *base = w.base; w.base += arrivals; return true; }
+        if (!w.used && free_slot < 0) free_slot = i;
+    }
+    if (free_slot < 0) return false;
+    auto& w = ctx->wave_slots[free_slot];
+    w.used = true; w.stream = s; w.base = arrivals;
+    *counter = ctx->wave_counters + free_slot; *base = 0;
+    return true;
+}
+
+void decxb_wave_unslot(decxb_ctx* ctx, cudaStream_t s, unsigned long long arrivals)
+{
+    std::lock_guard<std::mutex> lock(ctx->wave_mtx);
+    for (auto& w : ctx->wave_slots) if (w.used && w.stream == s) { w.base -= arrivals; return; }
+}
+
+void decxb_wave_reset(decxb_ctx* ctx)
+{
+    std::lock_guard<std::mutex> lock(ctx->wave_mtx);
+    cudaDeviceSynchronize();
+    cudaMemset(ctx->wave_counters, 0, DECXB_WAVE_SLOTS * sizeof(unsigned long long));
+    for (auto& w : ctx->wave_slots) w = {};
+    cudaGetLastError();
+}
+
+extern "C" int decxb_set_wave_align(decxb_ctx* ctx, int on)
+{
+    if (!ctx) return DECXB_ERR_BAD_PARAM;
+    ctx->wave_align = on == 2 ? 2 : on ? 1 : 0;
+    return DECXB_OK;
+}
+
+extern "C" int decxb_set_tile_trace(decxb_ctx* ctx, unsigned long long* dbuf, int tiles_per_cluster)
+{
+    if (!ctx || tiles_per_cluster < 0) return DECXB_ERR_BAD_PARAM;
+    ctx->trace = tiles_per_cluster > 0 ? dbuf : nullptr;
+    ctx->trace_tiles = dbuf ? tiles_per_cluster : 0;
+    return DECXB_OK;
+}
+
 extern "C" int decxb_set_pack_variant(decxb_ctx* ctx, int variant)
 {
     if (!ctx || variant < 0 || variant > 2) return DECXB_ERR_BAD_PARAM;
@@ -142,6 +191,7 @@ int decxb_check_dev_status(decxb_ctx* ctx)
             snprintf(buf, sizeof buf, "device wait gave up: code %d at role/barrier %d, block %d, detail %d",
                      ctx->h_status->code, ctx->h_status->where, ctx->h_status->block, ctx->h_status->detail);
         cudaMemset(ctx->d_status, 0, sizeof(decxb_dev_status));
+        if (!bounds) decxb_wave_reset(ctx);       /* a launch that gave up left its wave counter short */
         return decxb_fail(ctx, bounds ? DECXB_ERR_BOUNDS : DECXB_ERR_TIMEOUT, buf);
     }
     return DECXB_OK;

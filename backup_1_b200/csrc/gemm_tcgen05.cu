@@ -79,6 +79,11 @@ struct GemmParams {
     int act;                    /* DECXB_ACT_*                                                    */
     int tma_store;              /* 1 = results leave through shared memory and TMA stores (map_d)   */
     int tile_group;             /* tile-rows per group of the tile order                            */
+    /* wave alignment (see align_wave): counter shared by all blocks of the launch, value it had before the launch */
+    unsigned long long* wave_counter;
+    unsigned long long wave_base;
+    unsigned long long* trace;  /* measurement: global-timer value at the start of every tile of every cluster, or NULL */
+    int trace_tiles;            /* entries per cluster in `trace`                                   */
 };
 
 /* Activations with the reference's formulas (srcs/nn/operators/ReLU.h:48-75 keeps x when its
@@ -106,6 +111,41 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, cons
             if ((long long)(globaltimer_ns() - t0) > p.wait_limit_ns) {
                 if (atomicCAS(&p.status->code, 0, DECXB_DEVERR_WAIT_EXPIRED) == 0) {
                     p.status->where = where; p.status->block = (int)blockIdx.x; p.status->detail = detail;
+                    __threadfence_system();
+                }
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+/* Wave alignment.  All block pairs walk the tile list in lock step (pair c takes tiles c, c + P, c + 2P, ...),
+ * and the pairs of one wave share operand panels: the L2 serves a panel's k-block to every pair that asks for
+ * it while it is still resident.  Left alone the pairs drift apart (some SMs are a percent or two slower;
+ * measured: 400 us of spread after 50 tiles of 540 us at 16384^3), the same k-block is then fetched from HBM
+ * once per pair instead of once per wave, and the DRAM traffic grows to 20 times the operands.  So before the
+ * first load of its tile i >= 1 the leading producer announces itself on a counter in global memory and waits,
+ * with the usual time limit, until every pair that has a tile i has done the same.  The slowest pair sets the
+ * pace either way (the launch ends when it ends); the others now wait at tile starts instead of at the end.
+ * The launch is made cooperative, so all blocks are resident together and the wait can always be satisfied. */
+__device__ __forceinline__ bool align_wave(const GemmParams& p, int local_tile, int num_clusters, int num_tiles, int t)
+{
+    const int with_tile = min(num_clusters, num_tiles - local_tile * num_clusters);
+    const unsigned long long target = p.wave_base + (unsigned long long)(local_tile - 1) * (unsigned long long)num_clusters +
+                                      (unsigned long long)with_tile;
+    atomicAdd(p.wave_counter, 1ULL);
+    volatile unsigned long long* c = p.wave_counter;
+    if (*c >= target) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (*c < target) {
+        __nanosleep(100);
+        if ((++spins & 63u) == 0) {
+            if (*reinterpret_cast<volatile int*>(&p.status->code) != 0) return false;
+            if ((long long)(globaltimer_ns() - t0) > p.wait_limit_ns) {
+                if (atomicCAS(&p.status->code, 0, DECXB_DEVERR_WAIT_EXPIRED) == 0) {
+                    p.status->where = 500; p.status->block = (int)blockIdx.x; p.status->detail = t;
                     __threadfence_system();
                 }
                 return false;
@@ -332,8 +372,12 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
             int stage = 0; uint32_t phase = 0;
             uint32_t armed = 0, armed_parity = 0;     /* per stage: loads issued at least once / parity of the latest */
             bool alive = true;
-            for (int t = cluster_id; t < num_tiles && alive; t += num_clusters) {
+            int local_tile = 0;
+            for (int t = cluster_id; t < num_tiles && alive; t += num_clusters, ++local_tile) {
                 int tm, tn; tile_coords(t, p.tiles_m, p.tiles_n, p.tile_group, tm, tn);
+                if (p.wave_counter && is_leader && local_tile > 0 && !align_wave(p, local_tile, num_clusters, num_tiles, t)) { alive = false; break; }
+                if (p.trace && is_leader && local_tile < p.trace_tiles)
+                    p.trace[(size_t)cluster_id * p.trace_tiles + local_tile] = globaltimer_ns();
                 const int row_a = tm * C::UMMA_M + (int)cta_rank * BM_CTA;
                 int row_b = tn * C::UMMA_N + (int)cta_rank * BN;
                 if (!CONV && p.tiles_m_per) row_b += (tm / p.tiles_m_per) * (int)p.b_batch_rows;   /* matrix of the batch */
@@ -774,11 +818,35 @@ int launch_kernel(decxb_ctx* ctx, const CUtensorMap& ma_hi, const CUtensorMap& m
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CTAS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 2;
     GemmParams pp = p;
     pp.tile_group = ctx->tile_group > 0 ? ctx->tile_group : 8;
+    pp.trace = ctx->trace; pp.trace_tiles = ctx->trace_tiles;
+    /* Several waves of a long-K product: keep the block pairs of a wave aligned (align_wave).  Such a launch is
+     * cooperative (all blocks resident together); if the device refuses that, the launch is repeated without. */
+    const bool want_align = !CONV && ctx->wave_align && ctx->wave_counters && (ctx->reserved_sms == 0 || ctx->wave_align == 2) &&
+                            p.tiles_m_per == 0 && tiles >= 2 * clusters &&
+                            (int64_t)p.num_kb * 128 >= 4096;
+    if (want_align) {
+        unsigned long long* counter = nullptr; unsigned long long base = 0;
+        if (decxb_wave_slot(ctx, s, (unsigned long long)(tiles - clusters), &counter, &base)) {
+            pp.wave_counter = counter; pp.wave_base = base;
+            attr[1].id = cudaLaunchAttributeCooperative;
+            attr[1].val.cooperative = ctx->wave_align == 2 ? 0 : 1;      /* 2: plain launch (see decxb_set_wave_align) */
+            cudaError_t e;
+            {
+                decxb_launch_scope scope(ctx, s, DECXB_K_GEMM);
+                e = cudaLaunchKernelEx(&cfg, kernel, ma_hi, ma_lo, mb_hi, mb_lo, md, pp);
+            }
+            if (e == cudaSuccess) return DECXB_OK;
+            cudaGetLastError();
+            decxb_wave_unslot(ctx, s, (unsigned long long)(tiles - clusters));     /* nothing was counted */
+            ctx->wave_align = 0;                                                    /* not on this device: stop asking */
+            pp.wave_counter = nullptr; pp.wave_base = 0;
+        }
+    }
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     {
         decxb_launch_scope scope(ctx, s, DECXB_K_GEMM);
         DECXB_CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kernel, ma_hi, ma_lo, mb_hi, mb_lo, md, pp));

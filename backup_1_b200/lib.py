@@ -85,6 +85,8 @@ SIGNATURES = {
     "decxb_im2col_pack_f32": (_i, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _i, _vp, _i64, _i64, _i64, _vp]),
     "decxb_set_pack_variant": (_i, [_vp, _i]),
     "decxb_set_tile_group": (_i, [_vp, _i]),
+    "decxb_set_tile_trace": (_i, [_vp, _vp, _i]),
+    "decxb_set_wave_align": (_i, [_vp, _i]),
     "decxb_conv2_im2col_f32": (_i, [_vp, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp]),
     "decxb_conv2_im2col_f32_act": (_i, [_vp, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i, _vp, _i64, _i64, _i64, _vp]),
     "decxb_conv2_im2col_f32_host": (_i, [_vp, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64]),
@@ -202,6 +204,10 @@ class Context:
 
     def set_tile_group(self, tile_rows: int):
         self._chk(self.L.decxb_set_tile_group(self.h, tile_rows))
+
+    def set_wave_align(self, mode: int):
+        """0 off, 1 on (cooperative launches), 2 on with plain launches."""
+        self._chk(self.L.decxb_set_wave_align(self.h, int(mode)))
 
     def launches(self) -> int:
         return int(self.L.decxb_kernel_launch_count(self.h))

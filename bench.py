@@ -641,6 +641,7 @@ def main():
     ap.add_argument("--pack-variant", type=int, default=0, help="0 copy-engine pack, 1 staged, 2 direct (explicit convolution)")
     ap.add_argument("--batch", type=int, default=0, help="override the image count of a convolution workload")
     ap.add_argument("--no-gather", action="store_true", help="skip the all-gather of the result blocks (N > 1)")
+    ap.add_argument("--comm-ctas", type=int, default=0, help="thread blocks per NCCL kernel of the gather layer (0 = its default, 16)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="skip the other BASELINE configurations")
     ap.add_argument("--no-probe", action="store_true", help="skip the tensor-ceiling probes")
@@ -696,6 +697,8 @@ def main():
     if world > 1 and not args.no_gather and wl["scaling"] == "strong" and "full" in w:
         from backup_1_b200 import shard
 
+        if args.comm_ctas > 0:
+            os.environ["DECXB_COMM_MAX_CTAS"] = str(args.comm_ctas)
         uid = [bench.b.Comm.unique_id() if rank == 0 else None]
         dist.broadcast_object_list(uid, src=0)
         comm = bench.b.Comm(ctx, world, rank, uid[0], timeout_ms=120000)
@@ -718,11 +721,12 @@ def main():
 
         gms = timed(lambda: comm.allgather_blocks(full, unit_bytes, total_units, stream=bench.st), 2)
         gather = {"ms": gms, "bytes_per_rank": mine, "busbw_gbs": mine * (world - 1) / (gms * 1e-3) / 1e9,
+                  "nccl_thread_blocks": args.comm_ctas or 16,
                   "how": "decxb_comm_allgather_blocks (NCCL, in place in the whole-result array) after the step, timed alone"}
         if wl["kind"] == "gemm":
             mode = {"3xtf32": bench.b.GEMM_3XTF32, "1xtf32": bench.b.GEMM_1XTF32, "strict": bench.b.GEMM_3XTF32_STRICT}[args.mode]
             A_rows, Bm = w["dA"], w["dB"]
-            for groups in (1, 4, 8):
+            for groups in (1, 3, 4, 6):
                 ms = timed(lambda: comm.gemm_rowshard_gather(wl["M"], wl["N"], wl["K"], A_rows, wl["K"], Bm, wl["N"], full, groups=groups,
                                                              mode=mode, tile=args.tile, stream=bench.st), max(2, min(args.steps, 5)))
                 gather[f"step_with_gather_ms_groups{groups}"] = ms
@@ -737,7 +741,7 @@ def main():
             cols = torch.arange(0, 256, device=bench.dev)
             ref = a.double() @ Bm[:, cols].double()
             gather["gathered_rows_max_norm_err"] = bench.max_over_ranks(float((full[rows][:, cols].double() - ref).abs().max()) / wl["K"])
-            best = min((gather[f"step_with_gather_ms_groups{g}"], g) for g in (4, 8))
+            best = min((gather[f"step_with_gather_ms_groups{g}"], g) for g in (3, 4, 6))
             gather["overlapped_groups"] = best[1]
             gather["step_with_overlapped_gather_ms"] = best[0]
             gather["how_overlapped"] = ("decxb_gemm_f32_rowshard_gather: the rank's rows in row-panel groups, each group sent to the peers "

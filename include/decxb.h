@@ -349,6 +349,21 @@ DECXB_API int decxb_conv2_im2col_f32_host(decxb_ctx* ctx, int mode, int algo, in
  * column inside a group, so that the blocks running at the same time share A row-panels and B
  * column-panels in L2 (1..64, default 8).  Results do not depend on it.  For measurement. */
 DECXB_API int decxb_set_tile_group(decxb_ctx* ctx, int tile_rows);
+/* Wave alignment of the GEMM kernel (on by default): in launches of several waves of a long-K product
+ * the block pairs wait for one another at tile starts, so that the pairs sharing an operand panel
+ * read it from L2 together instead of each fetching it from HBM (the slowest pair sets the pace
+ * either way).  Results do not depend on it.  1 (default): such launches are cooperative, so all
+ * blocks are resident together; not used while decxb_gemm_f32_rowshard_gather has left SMs to a
+ * transfer.  2: the same waits in a plain launch (a profiler that cannot capture cooperative
+ * launches; also used beside a transfer): the blocks are resident together only as long as nothing
+ * else holds SMs, and a wait that cannot be met ends in DECXB_ERR_TIMEOUT after the limit.  0: the
+ * pairs run free.  For measurement. */
+DECXB_API int decxb_set_wave_align(decxb_ctx* ctx, int on);
+/* Measurement: while `dbuf` (device memory, sm_count x tiles_per_cluster 64-bit words) is set, the
+ * producer of every block (pair) of the GEMM kernel stores the GPU's global timer at the start of
+ * each of its tiles at dbuf[block_pair * tiles_per_cluster + i], which shows how far the blocks
+ * that share operand panels in L2 drift apart.  NULL or 0 switches it off. */
+DECXB_API int decxb_set_tile_trace(decxb_ctx* ctx, unsigned long long* dbuf, int tiles_per_cluster);
 /* Per-kernel device timing.  While enabled, every kernel the library launches is bracketed
  * by CUDA events on its own stream; decxb_profile_read synchronises the device, adds the
  * elapsed times to the totals below and returns them (decxb_profile_enable(ctx, 1) also
@@ -432,8 +447,11 @@ DECXB_API int decxb_inject_pipeline_error(decxb_ctx* ctx, int nth_call);
  *   groups (1..64) straight into D_full[M][N] (dense, leading dimension N), each group sent to
  *   the peers while the next is multiplied; on return everything is queued, and `stream`
  *   continues only after all rows of D_full have arrived.  groups = 1 computes, then gathers.
- *   While transfers run, the GEMM leaves decxb_comm_set_reserved_sms SMs (default 16) to
- *   NCCL's kernels.  A_rows points at the rank's first row; B is the whole matrix.
+ *   The last group, whose transfer nothing overlaps, is a third of an even share.  While
+ *   transfers run, the GEMM leaves decxb_comm_set_reserved_sms SMs to NCCL's kernels (default: the
+ *   communicator's limit of thread blocks per NCCL kernel, 16, or what the environment variable
+ *   DECXB_COMM_MAX_CTAS said when the communicator was made).  A_rows points at the rank's first
+ *   row; B is the whole matrix.
  * decxb_comm_synchronize: waits (bounded) until the transfers queued so far have finished. */
 #define DECXB_COMM_ID_BYTES 128
 typedef struct decxb_comm decxb_comm;

@@ -383,6 +383,34 @@ def test_gemm_batched_single_launch_many_small(ctx, mode, tile):
         assert np.all(Di[:, N:] == 7.0) and np.all(D[i, M * ldd:] == 7.0)
 
 
+@pytest.mark.parametrize("mode", [b.GEMM_DEFAULT, b.GEMM_3XTF32, b.GEMM_1XTF32])
+def test_wave_alignment_does_not_change_results(ctx, mode):
+    """A product of several waves with the block pairs waiting for one another at tile starts (cooperative
+    launch, the default), with the same waits in a plain launch, and with the pairs running free: same bits;
+    and the counters survive many launches in a row on two streams."""
+    M, N, K = 4096, 3072, 1100
+    dA = torch.empty((M, K), device=DEV); dB = torch.empty((K, N), device=DEV)
+    ctx.fill_uniform(dA, M, K, K, 1); ctx.fill_uniform(dB, K, N, N, 2)
+    outs = []
+    other = torch.cuda.Stream(device=DEV)
+    try:
+        for align in (1, 2, 0, 1):
+            ctx.set_wave_align(align)
+            D = torch.full((M, N), float("nan"), device=DEV)
+            for i in range(6):
+                ctx.gemm(M, N, K, dA, K, dB, N, D, N, mode=mode, tile=b.TILE_2CTA_256x256,
+                         stream=other.cuda_stream if i % 2 else None)
+            ctx.synchronize()
+            outs.append(D)
+    finally:
+        ctx.set_wave_align(1)
+    for D in outs[1:]:
+        assert torch.equal(D, outs[0])
+    rows = np.array([0, 255, 2048, 4095])
+    R = o.gemm_fmaf(dA[rows].cpu().numpy(), dB.cpu().numpy())
+    assert o.norm_err(outs[0][rows].cpu().numpy(), R, K, 1.0, 1.0) <= (TOL_3X if mode != b.GEMM_1XTF32 else 2e-3)
+
+
 def test_gemm_argument_errors(ctx):
     t = torch.zeros(64, device=DEV)
     with pytest.raises(b.DecxbError) as e:
