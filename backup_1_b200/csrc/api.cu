@@ -344,6 +344,11 @@ extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M
     if (rows > M) rows = M;
     /* first row-block: about K rows; column blocks of B: about 1/8 of N, at least 1024 columns */
     int64_t rows0 = decxb_ceil_to(K, 256);
+    /* ... but no more rows than the GPU needs to stay busy while B comes up: multiplying rows0 rows with a column
+     * block takes 2 rows0 ncol K / F, uploading the block 4 K ncol / BW, equal at rows0 = 2 F / BW, about 10 000 rows
+     * at 250 TFLOP/s and 50 GB/s, whatever the sizes.  (With K = 32768 the first block was the whole of A: 80 ms of
+     * upload with the GPU idle.) */
+    if (rows0 > 10240) rows0 = 10240;
     if (rows0 < rows) rows0 = rows;
     if (rows0 > M) rows0 = M;
     int64_t ncol = decxb_ceil_to(decxb_ceil_div(N, 8), 256);

@@ -51,7 +51,10 @@ ALSO = [("gemm16k", 5), ("cfg2", 40), ("cfg4", 8), ("cfg3", 60), ("cfg1", 60)]  
 NCU_TRAFFIC_BYTES = {("cfg2", "3xtf32", "gemm"): 727.8e6, ("cfg2", "strict", "gemm"): 731.1e6,
                      ("cfg3", "3xtf32", "pack"): 70.7e6, ("cfg3", "strict", "pack"): 70.7e6,
                      ("cfg4", "strict", "gemm"): 2594e6, ("cfg4", "3xtf32", "gemm"): 2515e6}
-NCU_TRAFFIC_PER_FLOP = {}     # filled from profiles/gemm_tf32_kernel_16384.md: bytes per algorithmic flop of the 256x256-tile GEMM
+# DRAM bytes per algorithmic flop of the 256 x 256-tile GEMM with the block pairs aligned, from the single-pass capture at
+# 16384^3 in profiles/gemm_tf32_kernel_16384.md (35.44 GB read + 1.10 GB written per 2 * 16384^3 flop).  A wave of 74
+# tiles reads 17.25 operand panels whatever K and N are, so the traffic of a larger product grows with its flops.
+NCU_TRAFFIC_PER_FLOP = {("strict", "gemm"): (35.44e9 + 1.10e9) / (2.0 * 16384 ** 3)}
 
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
@@ -139,7 +142,7 @@ def config_for(args, wl, name, world):
     if wl["kind"] == "pcie":
         return {"workload": name, "desc": wl["desc"]}
     t = touched_bytes(wl, args.mode, world)
-    return {"workload": name, "desc": wl["desc"], "mode": args.mode, "tile": args.tile,
+    return {"workload": name, "desc": wl["desc"], "mode": args.mode, "tile": args.tile, "wave_align": args.wave_align,
             "algo": args.algo if wl["kind"] == "conv" else None,
             "l2": (f"each step touches {t / 1e6:.0f} MB per GPU (operands, split scratch, result): "
                    + ("larger than the 126 MB L2, steps run back to back" if t > 2 * L2_BYTES else
@@ -243,6 +246,7 @@ class Bench:
         self.dev = torch.device(f"cuda:{self.local}")
         self.ctx = b.Context(self.local)
         self.ctx.set_pack_variant(args.pack_variant)
+        self.ctx.set_wave_align(args.wave_align)
         self.ts = torch.cuda.Stream(device=self.dev)
         self.st = self.ts.cuda_stream
         self.peaks = load_peaks()
@@ -523,8 +527,11 @@ class Bench:
             traffic = NCU_TRAFFIC_BYTES.get((w["name"], mode, "gemm")) if args.tile == 0 else None
             if traffic is not None and wl["kind"] == "conv":
                 traffic = traffic * w["nb"] / wl["batch"] if (args.algo == "implicit" and not args.batch) else None
-            if traffic is None and args.tile == 0 and wl["kind"] == "gemm" and (mode, "gemm") in NCU_TRAFFIC_PER_FLOP and w["M_rank"] >= 4096:
+            traffic_note = None
+            if (traffic is None and args.tile == 0 and args.wave_align != 0 and wl["kind"] == "gemm" and (mode, "gemm") in NCU_TRAFFIC_PER_FLOP
+                    and w["M_rank"] >= 4096 and wl["N"] >= 4096 and wl["K"] >= 4096):
                 traffic = NCU_TRAFFIC_PER_FLOP[(mode, "gemm")] * flops_launch
+                traffic_note = "scaled by flops from the single-pass ncu capture of one 16384^3 launch (profiles/gemm_tf32_kernel_16384.md)"
             r = {"bound": "tensor", "kernel": "decxb_gemm_tf32_kernel", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
                  "frac": ach / peak, "traffic": traffic,
                  "peak_basis": (f"{peaks['basis']} bf16 dense {'sustained' if long_step else 'burst'} {bf16} TFLOP/s"
@@ -533,6 +540,8 @@ class Bench:
                                 + (": steps of >= 100 ms run under the power cap" if long_step else ": a step is shorter than 100 ms")),
                  "frac_burst_basis": ach / (peaks["bf16_tflops"] / div), "frac_sustained_basis": ach / (peaks["bf16_sustained"] / div),
                  "avg_launch_ms": avg_ms, "time_shares": shares}
+            if traffic_note:
+                r["traffic_basis"] = traffic_note
             if r["frac"] > 1.0:
                 r["note"] = ("frac > 1: the denominator is derived from a cuBLAS bf16 run, not a TF32 measurement; "
                              "frac_of_probe compares with this library's own tcgen05 kind::tf32 probe on the same GPU")
@@ -641,6 +650,8 @@ def main():
     ap.add_argument("--pack-variant", type=int, default=0, help="0 copy-engine pack, 1 staged, 2 direct (explicit convolution)")
     ap.add_argument("--batch", type=int, default=0, help="override the image count of a convolution workload")
     ap.add_argument("--no-gather", action="store_true", help="skip the all-gather of the result blocks (N > 1)")
+    ap.add_argument("--wave-align", type=int, default=1, choices=[0, 1, 2],
+                    help="GEMM wave alignment: 1 cooperative launches (default), 2 plain launches (profilers; also beside a transfer), 0 off")
     ap.add_argument("--comm-ctas", type=int, default=0, help="thread blocks per NCCL kernel of the gather layer (0 = its default, 16)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="skip the other BASELINE configurations")
