@@ -824,15 +824,17 @@ int launch_kernel(decxb_ctx* ctx, const CUtensorMap& ma_hi, const CUtensorMap& m
     pp.trace = ctx->trace; pp.trace_tiles = ctx->trace_tiles;
     /* Several waves of a long-K product: keep the block pairs of a wave aligned (align_wave).  Such a launch is
      * cooperative (all blocks resident together); if the device refuses that, the launch is repeated without. */
-    const bool want_align = !CONV && ctx->wave_align && ctx->wave_counters && (ctx->reserved_sms == 0 || ctx->wave_align == 2) &&
-                            p.tiles_m_per == 0 && tiles >= 2 * clusters &&
-                            (int64_t)p.num_kb * 128 >= 4096;
+    const bool want_align = !CONV && ctx->wave_align && ctx->wave_counters && p.tiles_m_per == 0 && tiles >= 2 * clusters &&
+                            p.num_kb >= 32;   /* 32 k-blocks: K >= 1024 floats */
+    /* Beside a transfer kernel (SMs left to it) the launch stays a plain one: a cooperative launch might be held back
+     * until the transfer's blocks have gone.  The waits are then met as soon as all blocks have been placed. */
+    const bool cooperative = ctx->wave_align == 1 && ctx->reserved_sms == 0;
     if (want_align) {
         unsigned long long* counter = nullptr; unsigned long long base = 0;
         if (decxb_wave_slot(ctx, s, (unsigned long long)(tiles - clusters), &counter, &base)) {
             pp.wave_counter = counter; pp.wave_base = base;
             attr[1].id = cudaLaunchAttributeCooperative;
-            attr[1].val.cooperative = ctx->wave_align == 2 ? 0 : 1;      /* 2: plain launch (see decxb_set_wave_align) */
+            attr[1].val.cooperative = cooperative ? 1 : 0;
             cudaError_t e;
             {
                 decxb_launch_scope scope(ctx, s, DECXB_K_GEMM);
@@ -840,6 +842,7 @@ int launch_kernel(decxb_ctx* ctx, const CUtensorMap& ma_hi, const CUtensorMap& m
             }
             if (e == cudaSuccess) return DECXB_OK;
             cudaGetLastError();
+            ctx->launches--;                                                        /* that one did not happen */
             decxb_wave_unslot(ctx, s, (unsigned long long)(tiles - clusters));     /* nothing was counted */
             ctx->wave_align = 0;                                                    /* not on this device: stop asking */
             pp.wave_counter = nullptr; pp.wave_base = 0;

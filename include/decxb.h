@@ -353,11 +353,12 @@ DECXB_API int decxb_set_tile_group(decxb_ctx* ctx, int tile_rows);
  * the block pairs wait for one another at tile starts, so that the pairs sharing an operand panel
  * read it from L2 together instead of each fetching it from HBM (the slowest pair sets the pace
  * either way).  Results do not depend on it.  1 (default): such launches are cooperative, so all
- * blocks are resident together; not used while decxb_gemm_f32_rowshard_gather has left SMs to a
- * transfer.  2: the same waits in a plain launch (a profiler that cannot capture cooperative
- * launches; also used beside a transfer): the blocks are resident together only as long as nothing
- * else holds SMs, and a wait that cannot be met ends in DECXB_ERR_TIMEOUT after the limit.  0: the
- * pairs run free.  For measurement. */
+ * blocks are resident together; only the launches that decxb_gemm_f32_rowshard_gather makes beside
+ * a running transfer are plain ones with the same waits (a cooperative launch could be held back
+ * until the transfer's blocks have gone).  2: the waits in plain launches throughout (a profiler
+ * that cannot capture cooperative launches): the blocks are resident together only as long as
+ * nothing else holds SMs, and a wait that cannot be met ends in DECXB_ERR_TIMEOUT after the limit.
+ * 0: the pairs run free.  For measurement. */
 DECXB_API int decxb_set_wave_align(decxb_ctx* ctx, int on);
 /* Measurement: while `dbuf` (device memory, sm_count x tiles_per_cluster 64-bit words) is set, the
  * producer of every block (pair) of the GEMM kernel stores the GPU's global timer at the start of
