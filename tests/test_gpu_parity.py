@@ -791,6 +791,15 @@ def test_bounded_wait_expires_and_context_survives(ctx):
     A = o.fill_uniform(256 * 64, 1).reshape(256, 64)
     B = o.fill_uniform(64 * 256, 2).reshape(64, 256)
     assert o.norm_err(run_gemm(ctx, A, B), o.gemm_fmaf(A, B), 64, 1.0, 1.0) <= TOL_3X
+    # a product of several waves (its block pairs wait for one another on counters that the failed launch caused to be reset)
+    M, N, K = 4096, 3072, 1100
+    dA = torch.empty((M, K), device=DEV); dB = torch.empty((K, N), device=DEV); dD = torch.full((M, N), float("nan"), device=DEV)
+    ctx.fill_uniform(dA, M, K, K, 1); ctx.fill_uniform(dB, K, N, N, 2)
+    for _ in range(3):
+        ctx.gemm(M, N, K, dA, K, dB, N, dD, N)
+    ctx.synchronize()
+    rows = np.array([0, 2047, 4095])
+    assert o.norm_err(dD[rows].cpu().numpy(), o.gemm_fmaf(dA[rows].cpu().numpy(), dB.cpu().numpy()), K, 1.0, 1.0) <= TOL_3X
 
 
 @pytest.mark.parametrize("nth", [0, 2, 3])      # the shortest pipeline (fp16) makes four CUDA calls
