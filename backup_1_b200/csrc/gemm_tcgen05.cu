@@ -64,8 +64,12 @@ struct GemmParams {
     decxb_dev_status* status;
     /* implicit-GEMM convolution only: an M tile of one CTA is a BX x BY patch of output
      * pixels of one image; a k-block is 32 channels of one filter tap */
-    int bx, by;                 /* patch size, bx * by = 128                                    */
-    int tiles_x, tiles_y;       /* patches per image row / CTA-group patches per image column    */
+    int bx, by;                 /* patch of output pixels that one TMA box covers, bx * by = 128 / nbox  */
+    int nbox;                   /* patches (boxes) per CTA tile: 1, 2 or 4; patch s of the launch is patch
+                                   s % (tiles_x * tiles_y) of image s / (tiles_x * tiles_y), x fastest, and
+                                   CTA c of tile t owns patches ((t * CTAS + c) * nbox + j), j < nbox   */
+    int tiles_x, tiles_y;       /* patches per image row / per image column                      */
+    int batch;                  /* images                                                        */
     int out_h, eq_w;            /* output rows, pixels per output row (= wpitch of destination)  */
     int kw, off_x, off_y;       /* filter width, source offset of tap (0,0)                      */
     int cblocks;                /* 32-channel blocks per tap                                     */
@@ -129,23 +133,22 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, cons
  * with the usual time limit, until every pair that has a tile i has done the same.  The slowest pair sets the
  * pace either way (the launch ends when it ends); the others now wait at tile starts instead of at the end.
  * The launch is made cooperative, so all blocks are resident together and the wait can always be satisfied. */
-__device__ __forceinline__ bool align_wave(const GemmParams& p, int local_tile, int num_clusters, int num_tiles, int t)
+__device__ __noinline__ bool align_wave_wait(unsigned long long* counter, unsigned long long target, long long limit_ns,
+                                            decxb_dev_status* status, int detail)
 {
-    const int with_tile = min(num_clusters, num_tiles - local_tile * num_clusters);
-    const unsigned long long target = p.wave_base + (unsigned long long)(local_tile - 1) * (unsigned long long)num_clusters +
-                                      (unsigned long long)with_tile;
-    atomicAdd(p.wave_counter, 1ULL);
-    volatile unsigned long long* c = p.wave_counter;
+    /* (not inlined: the producer that calls it lives on 56 registers in the chunked kernels) */
+    atomicAdd(counter, 1ULL);
+    volatile unsigned long long* c = counter;
     if (*c >= target) return true;
     const unsigned long long t0 = globaltimer_ns();
     uint32_t spins = 0;
     while (*c < target) {
         __nanosleep(100);
         if ((++spins & 63u) == 0) {
-            if (*reinterpret_cast<volatile int*>(&p.status->code) != 0) return false;
-            if ((long long)(globaltimer_ns() - t0) > p.wait_limit_ns) {
-                if (atomicCAS(&p.status->code, 0, DECXB_DEVERR_WAIT_EXPIRED) == 0) {
-                    p.status->where = 500; p.status->block = (int)blockIdx.x; p.status->detail = t;
+            if (*reinterpret_cast<volatile int*>(&status->code) != 0) return false;
+            if ((long long)(globaltimer_ns() - t0) > limit_ns) {
+                if (atomicCAS(&status->code, 0, DECXB_DEVERR_WAIT_EXPIRED) == 0) {
+                    status->where = 500; status->block = (int)blockIdx.x; status->detail = detail;
                     __threadfence_system();
                 }
                 return false;
@@ -153,6 +156,14 @@ __device__ __forceinline__ bool align_wave(const GemmParams& p, int local_tile, 
         }
     }
     return true;
+}
+
+__device__ __forceinline__ bool align_wave(const GemmParams& p, int local_tile, int num_clusters, int num_tiles, int t)
+{
+    const int with_tile = min(num_clusters, num_tiles - local_tile * num_clusters);
+    const unsigned long long target = p.wave_base + (unsigned long long)(local_tile - 1) * (unsigned long long)num_clusters +
+                                      (unsigned long long)with_tile;
+    return align_wave_wait(p.wave_counter, target, p.wait_limit_ns, p.status, t);
 }
 
 /* Writes 32 consecutive result columns of one row, first column `col_first`:
@@ -381,44 +392,61 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
                 const int row_a = tm * C::UMMA_M + (int)cta_rank * BM_CTA;
                 int row_b = tn * C::UMMA_N + (int)cta_rank * BN;
                 if (!CONV && p.tiles_m_per) row_b += (tm / p.tiles_m_per) * (int)p.b_batch_rows;   /* matrix of the batch */
-                /* convolution: this CTA's patch of output pixels */
-                int img = 0, px0 = 0, py0 = 0;
+                /* convolution: this CTA's patches of output pixels (up to four boxes of 128 / nbox pixels each,
+                 * consecutive in the launch's patch order, possibly of different images) */
+                int s_img[4] = {0, 0, 0, 0}, s_px[4] = {0, 0, 0, 0}, s_py[4] = {0, 0, 0, 0};
                 if (CONV) {
                     const int per_img = p.tiles_x * p.tiles_y;
-                    img = tm / per_img;
-                    const int r = tm - img * per_img;
-                    py0 = ((r / p.tiles_x) * CTAS + (int)cta_rank) * p.by;
-                    px0 = (r % p.tiles_x) * p.bx;
+                    const long long s0 = ((long long)tm * CTAS + (long long)cta_rank) * p.nbox;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const long long sj = s0 + j;
+                        const int im = (int)(sj / per_img), r = (int)(sj - (long long)im * per_img);
+                        s_img[j] = im; s_py[j] = (r / p.tiles_x) * p.by; s_px[j] = (r % p.tiles_x) * p.bx;
+                    }
                 }
+                const uint32_t sub_bytes = CONV ? (uint32_t)(BM_CTA / p.nbox) * 128u : 0u;   /* rows of one box x 128 bytes */
                 int tap = 0, cb = 0;       /* convolution: filter tap and channel block of this k-block */
                 for (int kb = 0; kb < p.num_kb; ++kb) {
                     if (!wait_bounded(empty_bar(stage), phase ^ 1u, p, 100 + stage, t)) { alive = false; break; }
                     const int kx = kb * (NSPLIT == 16 ? 64 : BK);       /* elements per 128-byte k-block */
                     const int ky_t = CONV ? tap / p.kw : 0;
-                    const int cc = cb * BK, xx = px0 + (tap - ky_t * p.kw) + p.off_x, yy = py0 + ky_t + p.off_y;
+                    const int cc = cb * BK, dx = (tap - ky_t * p.kw) + p.off_x, dy = ky_t + p.off_y;
                     if (CTAS == 1) {
                         const uint32_t fb = full_bar(stage);
                         mbar_arrive_expect_tx(fb, C::STAGE_BYTES);
-                        if (CONV) tma_load_4d(stage_a(stage, 0), &map_a_hi, fb, cc, xx, yy, img);
-                        else      tma_load_2d(stage_a(stage, 0), &map_a_hi, fb, kx, row_a);
-                        tma_load_2d(stage_b(stage, 0), &map_b_hi, fb, kx, row_b);
-                        if (NSPLIT == 3) {
-                            if (CONV) tma_load_4d(stage_a(stage, 1), &map_a_lo, fb, cc, xx, yy, img);
-                            else      tma_load_2d(stage_a(stage, 1), &map_a_lo, fb, kx, row_a);
-                            tma_load_2d(stage_b(stage, 1), &map_b_lo, fb, kx, row_b);
+                        if (CONV) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                if (j < p.nbox) {
+                                    tma_load_4d(stage_a(stage, 0) + j * sub_bytes, &map_a_hi, fb, cc, s_px[j] + dx, s_py[j] + dy, s_img[j]);
+                                    if (NSPLIT == 3)
+                                        tma_load_4d(stage_a(stage, 1) + j * sub_bytes, &map_a_lo, fb, cc, s_px[j] + dx, s_py[j] + dy, s_img[j]);
+                                }
+                        } else {
+                            tma_load_2d(stage_a(stage, 0), &map_a_hi, fb, kx, row_a);
+                            if (NSPLIT == 3) tma_load_2d(stage_a(stage, 1), &map_a_lo, fb, kx, row_a);
                         }
+                        tma_load_2d(stage_b(stage, 0), &map_b_hi, fb, kx, row_b);
+                        if (NSPLIT == 3) tma_load_2d(stage_b(stage, 1), &map_b_lo, fb, kx, row_b);
                     } else {
                         /* Both CTAs' bytes are counted on the leader's barrier. */
                         if (is_leader) mbar_arrive_expect_tx(full_bar(stage), 2 * C::STAGE_BYTES);
                         const uint32_t fb = mapa(full_bar(stage), 0);
-                        if (CONV) tma_load_4d_pair(stage_a(stage, 0), &map_a_hi, fb, cc, xx, yy, img);
-                        else      tma_load_2d_pair(stage_a(stage, 0), &map_a_hi, fb, kx, row_a);
-                        tma_load_2d_pair(stage_b(stage, 0), &map_b_hi, fb, kx, row_b);
-                        if (NSPLIT == 3) {
-                            if (CONV) tma_load_4d_pair(stage_a(stage, 1), &map_a_lo, fb, cc, xx, yy, img);
-                            else      tma_load_2d_pair(stage_a(stage, 1), &map_a_lo, fb, kx, row_a);
-                            tma_load_2d_pair(stage_b(stage, 1), &map_b_lo, fb, kx, row_b);
+                        if (CONV) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                if (j < p.nbox) {
+                                    tma_load_4d_pair(stage_a(stage, 0) + j * sub_bytes, &map_a_hi, fb, cc, s_px[j] + dx, s_py[j] + dy, s_img[j]);
+                                    if (NSPLIT == 3)
+                                        tma_load_4d_pair(stage_a(stage, 1) + j * sub_bytes, &map_a_lo, fb, cc, s_px[j] + dx, s_py[j] + dy, s_img[j]);
+                                }
+                        } else {
+                            tma_load_2d_pair(stage_a(stage, 0), &map_a_hi, fb, kx, row_a);
+                            if (NSPLIT == 3) tma_load_2d_pair(stage_a(stage, 1), &map_a_lo, fb, kx, row_a);
                         }
+                        tma_load_2d_pair(stage_b(stage, 0), &map_b_hi, fb, kx, row_b);
+                        if (NSPLIT == 3) tma_load_2d_pair(stage_b(stage, 1), &map_b_lo, fb, kx, row_b);
                     }
                     armed |= 1u << stage;
                     armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
@@ -509,17 +537,19 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
             float* __restrict__ drow = p.D + bidx * p.d_batch_stride + row * p.ldd;
             int box_x = 0, box_y = 0, box_img = 0;    /* convolution: first pixel of the warp's 32 tile rows */
             if (CONV) {
-                /* tile row i is pixel (px0 + i % bx, py0 + i / bx) of image img */
-                const int per_img = p.tiles_x * p.tiles_y;
-                const int img = tm / per_img;
-                const int r = tm - img * per_img;
-                const int i = q * 32 + lane;
-                const int py0 = ((r / p.tiles_x) * CTAS + (int)cta_rank) * p.by, px0 = (r % p.tiles_x) * p.bx;
-                const int y = py0 + i / p.bx;
-                const int x = px0 + i % p.bx;
-                row_ok = (x < p.eq_w) && (y < p.out_h);
+                /* tile row i lies in the CTA's patch i / (bx * by), at pixel (li % bx, li / bx) of it, li = i % (bx * by);
+                 * a warp's 32 rows always lie in one patch (a patch has at least 32 pixels) */
+                const int per_img = p.tiles_x * p.tiles_y, rpb = BM_CTA / p.nbox;
+                const int i0 = q * 32, j = i0 / rpb, li0 = i0 - j * rpb;
+                const long long sj = ((long long)tm * CTAS + (long long)cta_rank) * p.nbox + j;
+                const int img = (int)(sj / per_img), r = (int)(sj - (long long)img * per_img);
+                const int py0 = (r / p.tiles_x) * p.by, px0 = (r % p.tiles_x) * p.bx;
+                const int li = li0 + lane;
+                const int y = py0 + li / p.bx;
+                const int x = px0 + li % p.bx;
+                row_ok = (x < p.eq_w) && (y < p.out_h) && (img < p.batch);
                 drow = p.D + (int64_t)img * p.dst_img_stride + ((int64_t)y * p.eq_w + x) * p.ldd;
-                box_x = px0 + (q * 32) % p.bx; box_y = py0 + (q * 32) / p.bx; box_img = img;
+                box_x = px0 + li0 % p.bx; box_y = py0 + li0 / p.bx; box_img = img;
             }
             const float* __restrict__ crow = (p.C && !CONV) ? p.C + bidx * p.c_batch_stride + row * p.ldc : nullptr;
             const bool vec = d_vec && (!crow || c_vec);
@@ -861,14 +891,19 @@ template <int CTAS, int BN, int NSPLIT, int KCH = 0>
 int launch_conv_cfg(decxb_ctx* ctx, const decxb_conv_gemm_args& a, cudaStream_t s)
 {
     using C = Cfg<CTAS, BN, NSPLIT>;
-    /* patch shape: bx * by = 128, the one that wastes the fewest rows on ragged edges */
-    int best_bx = 128; int64_t best_area = -1;
-    for (int bx = 128; bx >= 1; bx >>= 1) {
-        const int by = 128 / bx;
-        const int64_t area = decxb_ceil_to(a.eq_w, bx) * decxb_ceil_to(a.out_h, (int64_t)by * CTAS);
-        if (best_area < 0 || area < best_area) { best_area = area; best_bx = bx; }
+    /* A CTA's 128 tile rows are nbox patches of bx x by output pixels (one TMA box each): the choice that covers
+     * the image with the fewest wasted pixels (56 x 56 cannot be tiled by 128-pixel rectangles with power-of-two
+     * sides, 8 x 8 patches tile it exactly), fewer boxes on a tie. */
+    int best_bx = 128, best_nbox = 1; int64_t best_area = -1;
+    for (int nbox = 1; nbox <= 4; nbox <<= 1) {
+        const int P = 128 / nbox;
+        for (int bx = P; bx >= 1; bx >>= 1) {
+            const int by = P / bx;
+            const int64_t area = decxb_ceil_to(a.eq_w, bx) * decxb_ceil_to(a.out_h, by);
+            if (best_area < 0 || area < best_area) { best_area = area; best_bx = bx; best_nbox = nbox; }
+        }
     }
-    const int bx = best_bx, by = 128 / best_bx;
+    const int nbox = best_nbox, bx = best_bx, by = 128 / nbox / best_bx;
     const int64_t dp = a.dp, cblocks = decxb_ceil_div(dp, BK);
     CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
     int rc;
@@ -879,17 +914,18 @@ int launch_conv_cfg(decxb_ctx* ctx, const decxb_conv_gemm_args& a, cudaStream_t 
         if ((rc = make_map(ctx, &mb_lo, a.k_lo, a.k_rows, a.k_cols, a.ldk, BN))) return rc;
     } else { ma_lo = ma_hi; mb_lo = mb_hi; }
     GemmParams p = {};
-    p.bx = bx; p.by = by;
+    p.bx = bx; p.by = by; p.nbox = nbox; p.batch = (int)a.batch;
     p.tiles_x = (int)decxb_ceil_div(a.eq_w, bx);
-    p.tiles_y = (int)decxb_ceil_div(a.out_h, (int64_t)by * CTAS);
+    p.tiles_y = (int)decxb_ceil_div(a.out_h, by);
     p.out_h = (int)a.out_h; p.eq_w = (int)a.eq_w; p.kw = (int)a.kW; p.off_x = a.off_x; p.off_y = a.off_y;
     p.cblocks = (int)cblocks;
     p.dst_img_stride = a.dst_img_stride;
-    p.M = (int64_t)a.batch * p.tiles_x * p.tiles_y * C::UMMA_M;   /* rows of the tiled problem; real bounds are per pixel */
+    const int64_t patches = (int64_t)a.batch * p.tiles_x * p.tiles_y;
+    const int64_t tiles_m = decxb_ceil_div(patches, (int64_t)nbox * CTAS);
+    p.M = tiles_m * C::UMMA_M;                                     /* rows of the tiled problem; real bounds are per pixel */
     p.N = a.Np; p.K = a.k_cols;
     p.C = nullptr; p.ldc = 0; p.D = a.dst; p.ldd = a.Np;
     p.bias = a.bias; p.act = a.act;
-    const int64_t tiles_m = (int64_t)a.batch * p.tiles_x * p.tiles_y;
     if (tiles_m > 0x7fffffffLL) return decxb_fail(ctx, DECXB_ERR_TOO_LARGE, "convolution tiles");
     p.tiles_m = (int)tiles_m;
     p.tiles_n = (int)decxb_ceil_div(a.Np, C::UMMA_N);

@@ -738,6 +738,7 @@ def test_conv_with_prepared_filters_gives_the_bits_of_the_plain_entry(ctx, algo,
     want = torch.full((nb, oh, eq, o.ceil4(F)), float("nan"), device=DEV); got = torch.full_like(want, float("nan"))
     ctx.conv2_im2col_act(dS, W, H, C, dF, kW, kW, F, want, bias=dB, act=b.ACT_TANH, batch=nb, mode=mode, algo=algo)
     pf = ctx.conv_prepare_filters(dF, kW, kW, C, F, mode=mode, algo=algo)
+    ctx.synchronize()                            # the preparation runs on the context's stream
     dF.zero_()                                   # the bank itself is no longer needed once prepared
     for _ in range(2):
         ctx.conv2_im2col_prepared(dS, W, H, pf, got, batch=nb, bias=dB, act=b.ACT_TANH)

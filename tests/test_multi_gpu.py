@@ -48,8 +48,9 @@ def test_prepared_b_gives_the_bits_of_the_plain_entry(ctx):
         want = torch.empty((M, N), device="cuda:0"); got = torch.full((M, N), float("nan"), device="cuda:0")
         ctx.gemm_act(M, N, K, dA, K, dB, N, want, N, Cin=dC, ldc=N, bias=dbias, act=b.ACT_RELU, mode=mode)
         pb = ctx.prepare_b(K, N, dB, N, mode=mode)
+        ctx.synchronize()                                 # the preparation runs on the context's stream
         dB_saved = dB.clone(); dB.zero_()                 # B itself is no longer needed once prepared
-        ctx.synchronize()
+        torch.cuda.synchronize()
         for _ in range(2):
             ctx.gemm_prepared(M, dA, K, pb, got, N, Cin=dC, ldc=N, bias=dbias, act=b.ACT_RELU)
         ctx.synchronize()
