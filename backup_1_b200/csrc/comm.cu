@@ -8,7 +8,9 @@
  * do the blocks travel, and then the transfer is overlapped with the arithmetic: the rank's rows
  * are computed in a few row-panel groups, and while group g+1 is multiplied the finished rows of
  * group g are already on their way to the peers (NCCL send/receive on a side stream, into their
- * final place in the peers' result arrays).  Only the last group's transfer is exposed.
+ * final place in the peers' result arrays, through a communicator limited to a few thread blocks so
+ * that the GEMM beside it keeps its SMs).  Only the last, small group's transfer is exposed, and it
+ * goes through a communicator with many thread blocks.
  *
  * NCCL is loaded at run time (dlopen of libnccl.so.2, or the file DECXB_NCCL_LIB names), so
  * the library has no link-time dependency on it and single-GPU users never load it.  The
@@ -36,6 +38,7 @@ struct NcclApi {
     ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;
     ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*CommSplit)(ncclComm_t, int, int, ncclComm_t*, ncclConfig_t*) = nullptr;
     ncclResult_t (*GroupStart)() = nullptr;
     ncclResult_t (*GroupEnd)() = nullptr;
     ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
@@ -66,6 +69,7 @@ NcclApi* load_nccl(const char* path_or_null, std::string* err)
     a->CommGetAsyncError = reinterpret_cast<decltype(a->CommGetAsyncError)>(sym("ncclCommGetAsyncError"));
     a->CommAbort = reinterpret_cast<decltype(a->CommAbort)>(sym("ncclCommAbort"));
     a->CommDestroy = reinterpret_cast<decltype(a->CommDestroy)>(sym("ncclCommDestroy"));
+    a->CommSplit = reinterpret_cast<decltype(a->CommSplit)>(sym("ncclCommSplit"));
     a->GroupStart = reinterpret_cast<decltype(a->GroupStart)>(sym("ncclGroupStart"));
     a->GroupEnd = reinterpret_cast<decltype(a->GroupEnd)>(sym("ncclGroupEnd"));
     a->Send = reinterpret_cast<decltype(a->Send)>(sym("ncclSend"));
@@ -81,11 +85,13 @@ NcclApi* load_nccl(const char* path_or_null, std::string* err)
 
 struct decxb_comm {
     NcclApi* api = nullptr;
-    ncclComm_t comm = nullptr;
+    ncclComm_t comm = nullptr;          /* wide: many thread blocks per NCCL kernel, for transfers that run alone */
+    ncclComm_t narrow = nullptr;        /* few thread blocks, for transfers that run beside a GEMM (split off `comm`) */
+    int wide_ctas = 32;
     decxb_ctx* ctx = nullptr;           /* may be NULL in the host-side self-test */
     int world = 0, rank = 0;
     int timeout_ms = 30000;
-    int reserve_sms = 16;               /* SMs left to NCCL's kernels while a transfer overlaps a GEMM */
+    int reserve_sms = 8;                /* SMs left to NCCL's kernels while a transfer overlaps a GEMM = blocks of `narrow` */
     bool aborted = false;
     cudaStream_t stream = nullptr;      /* side stream the transfers run on */
     cudaEvent_t ev_ready = nullptr, ev_done = nullptr;
@@ -104,21 +110,27 @@ int comm_fail(decxb_comm* c, int status, const std::string& msg)
 
 /* Polls the communicator until the last NCCL call has left the "in progress" state; aborts the
  * communicator when the time limit passes or NCCL reports an asynchronous error. */
-int comm_settle(decxb_comm* c, ncclResult_t call_rc, const char* what)
+void comm_abort_all(decxb_comm* c)
+{
+    if (c->narrow) { c->api->CommAbort(c->narrow); c->narrow = nullptr; }
+    if (c->comm) { c->api->CommAbort(c->comm); c->comm = nullptr; }
+    c->aborted = true;
+}
+
+int comm_settle(decxb_comm* c, ncclResult_t call_rc, const char* what, ncclComm_t which = nullptr)
 {
     if (call_rc != ncclSuccess && call_rc != ncclInProgress)
         return comm_fail(c, DECXB_ERR_COMM, std::string(what) + ": " + c->api->GetErrorString(call_rc));
+    if (!which) which = c->comm;
     const auto t0 = std::chrono::steady_clock::now();
     for (;;) {
         ncclResult_t st = ncclSuccess;
-        ncclResult_t q = c->api->CommGetAsyncError(c->comm, &st);
+        ncclResult_t q = c->api->CommGetAsyncError(which, &st);
         if (q != ncclSuccess) st = q;
         if (st == ncclSuccess) return DECXB_OK;
         const bool late = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count() > c->timeout_ms;
         if (st != ncclInProgress || late) {
-            c->api->CommAbort(c->comm);
-            c->comm = nullptr;
-            c->aborted = true;
+            comm_abort_all(c);
             if (st == ncclInProgress)
                 return comm_fail(c, DECXB_ERR_TIMEOUT, std::string(what) + " did not complete within " + std::to_string(c->timeout_ms) +
                                                        " ms (a rank that never arrived?); communicator aborted");
@@ -135,16 +147,36 @@ int comm_handshake(decxb_comm* c, const void* id128)
     memcpy(&id, id128, sizeof id);
     ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
     cfg.blocking = 0;
-    /* NCCL's kernels run beside the persistent GEMM kernel, whose blocks fill whole SMs: keep them few
-     * (DECXB_COMM_MAX_CTAS overrides the default of 16 thread blocks per NCCL kernel) */
-    const char* env = getenv("DECXB_COMM_MAX_CTAS");
-    const int ctas = env && atoi(env) > 0 && atoi(env) <= 64 ? atoi(env) : c->reserve_sms;
-    cfg.maxCTAs = ctas;
-    c->reserve_sms = ctas;
+    /* Two communicators over the same ranks.  The wide one (DECXB_COMM_WIDE_CTAS thread blocks per NCCL kernel,
+     * default 32) serves transfers that run alone.  The narrow one (DECXB_COMM_MAX_CTAS, default 2 per rank, 4 to 16) serves transfers
+     * that run beside the persistent GEMM kernel, whose blocks fill whole SMs: every block NCCL takes is an SM the
+     * GEMM does without, and a transfer hidden behind a row-panel group has time to spare. */
+    const char* envw = getenv("DECXB_COMM_WIDE_CTAS");
+    const char* envn = getenv("DECXB_COMM_MAX_CTAS");
+    c->wide_ctas = envw && atoi(envw) > 0 && atoi(envw) <= 64 ? atoi(envw) : 32;
+    /* measured on config 5: 4 blocks are too slow to hide a group's transfer at 4 ranks, 8 are best there, 16 cost the
+     * GEMM more than they save; with twice the ranks a group's GEMM is half as long for about the same bytes */
+    int narrow_default = 2 * c->world;
+    if (narrow_default < 4) narrow_default = 4;
+    if (narrow_default > 16) narrow_default = 16;
+    c->reserve_sms = envn && atoi(envn) > 0 && atoi(envn) <= 64 ? atoi(envn) : narrow_default;
+    cfg.maxCTAs = c->wide_ctas;
     ncclResult_t rc = c->api->CommInitRankConfig(&c->comm, c->world, id, c->rank, &cfg);
     if (!c->comm && rc != ncclSuccess && rc != ncclInProgress)
         return comm_fail(c, DECXB_ERR_COMM, std::string("ncclCommInitRankConfig: ") + c->api->GetErrorString(rc));
-    return comm_settle(c, rc, "ncclCommInitRankConfig");
+    int st = comm_settle(c, rc, "ncclCommInitRankConfig");
+    if (st || c->world == 1) return st;
+    ncclConfig_t cfgn = NCCL_CONFIG_INITIALIZER;
+    cfgn.blocking = 0;
+    cfgn.minCTAs = 1;
+    cfgn.maxCTAs = c->reserve_sms;
+    rc = c->api->CommSplit(c->comm, 0, c->rank, &c->narrow, &cfgn);
+    if (rc != ncclSuccess && rc != ncclInProgress) {
+        comm_abort_all(c);
+        return comm_fail(c, DECXB_ERR_COMM, std::string("ncclCommSplit: ") + c->api->GetErrorString(rc));
+    }
+    if ((st = comm_settle(c, rc, "ncclCommSplit"))) return st;              /* the parent reports the split's progress */
+    return c->narrow ? comm_settle(c, ncclSuccess, "ncclCommSplit (new communicator)", c->narrow) : DECXB_OK;
 }
 
 /* Bounded wait for everything queued on the side stream; aborts the communicator when the limit passes. */
@@ -161,12 +193,12 @@ int comm_drain(decxb_comm* c)
             ncclResult_t st = ncclSuccess;
             c->api->CommGetAsyncError(c->comm, &st);
             if (st != ncclSuccess && st != ncclInProgress) {
-                c->api->CommAbort(c->comm); c->comm = nullptr; c->aborted = true;
+                comm_abort_all(c);
                 return comm_fail(c, DECXB_ERR_COMM, std::string("asynchronous NCCL error: ") + c->api->GetErrorString(st) + "; communicator aborted");
             }
         }
         if (std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count() > c->timeout_ms) {
-            if (c->comm) { c->api->CommAbort(c->comm); c->comm = nullptr; c->aborted = true; }
+            if (c->comm) comm_abort_all(c);
             return comm_fail(c, DECXB_ERR_TIMEOUT, "transfers did not finish within " + std::to_string(c->timeout_ms) + " ms; communicator aborted");
         }
         std::this_thread::sleep_for(std::chrono::microseconds(50));
@@ -192,7 +224,7 @@ void panel_range(int64_t rows, int g, int G, int64_t* a, int64_t* b)
 /* One exchange: every rank sends units [ua_r, ub_r) of its own block to all peers and receives theirs
  * into place.  `base` is the whole array (same layout on every rank), unit_bytes the size of a unit. */
 template <typename RangeFn>
-int exchange(decxb_comm* c, char* base, size_t unit_bytes, int64_t total_units, RangeFn range, cudaStream_t s)
+int exchange(decxb_comm* c, ncclComm_t comm, char* base, size_t unit_bytes, int64_t total_units, RangeFn range, cudaStream_t s)
 {
     NcclApi* n = c->api;
     int64_t my_f = 0, my_l = 0;
@@ -206,13 +238,13 @@ int exchange(decxb_comm* c, char* base, size_t unit_bytes, int64_t total_units, 
         int64_t f = 0, l = 0, a = 0, b = 0;
         decxb_shard_range(total_units, c->world, p, &f, &l);
         range(l - f, &a, &b);
-        if (mb > ma) rc = n->Send(base + (size_t)(my_f + ma) * unit_bytes, (size_t)(mb - ma) * unit_bytes, ncclChar, p, c->comm, s);
+        if (mb > ma) rc = n->Send(base + (size_t)(my_f + ma) * unit_bytes, (size_t)(mb - ma) * unit_bytes, ncclChar, p, comm, s);
         if (b > a && (rc == ncclSuccess || rc == ncclInProgress))
-            rc = n->Recv(base + (size_t)(f + a) * unit_bytes, (size_t)(b - a) * unit_bytes, ncclChar, p, c->comm, s);
+            rc = n->Recv(base + (size_t)(f + a) * unit_bytes, (size_t)(b - a) * unit_bytes, ncclChar, p, comm, s);
     }
     ncclResult_t rc2 = n->GroupEnd();
-    if (rc != ncclSuccess && rc != ncclInProgress) return comm_settle(c, rc, "ncclSend/ncclRecv");
-    return comm_settle(c, rc2, "ncclGroupEnd");
+    if (rc != ncclSuccess && rc != ncclInProgress) return comm_settle(c, rc, "ncclSend/ncclRecv", comm);
+    return comm_settle(c, rc2, "ncclGroupEnd", comm);
 }
 
 int comm_usable(decxb_comm* c)
@@ -267,6 +299,7 @@ extern "C" int decxb_comm_destroy(decxb_comm* c)
     if (!c) return DECXB_OK;
     if (c->ctx) decxb_bind(c->ctx);
     if (c->stream) (void)comm_drain(c);
+    if (c->narrow) { c->api->CommDestroy(c->narrow); c->narrow = nullptr; }
     if (c->comm) { c->api->CommDestroy(c->comm); c->comm = nullptr; }
     if (c->ev_ready) cudaEventDestroy(c->ev_ready);
     if (c->ev_done) cudaEventDestroy(c->ev_done);
@@ -333,7 +366,7 @@ extern "C" int decxb_comm_allgather_blocks(decxb_comm* c, void* base, size_t uni
         ncclResult_t r = c->api->AllGather(static_cast<char*>(base) + (size_t)f * unit_bytes, base, count, ncclChar, c->comm, c->stream);
         rc = comm_settle(c, r, "ncclAllGather");
     } else if (c->world > 1) {
-        rc = exchange(c, static_cast<char*>(base), unit_bytes, total_units, [](int64_t n, int64_t* a, int64_t* b) { *a = 0; *b = n; }, c->stream);
+        rc = exchange(c, c->comm, static_cast<char*>(base), unit_bytes, total_units, [](int64_t n, int64_t* a, int64_t* b) { *a = 0; *b = n; }, c->stream);
     }
     if (rc) return rc;
     if (cudaEventRecord(c->ev_done, c->stream) != cudaSuccess || cudaStreamWaitEvent(s, c->ev_done, 0) != cudaSuccess) {
@@ -382,7 +415,8 @@ extern "C" int decxb_gemm_f32_rowshard_gather(decxb_ctx* ctx, decxb_comm* c, int
                                                ncclChar, c->comm, c->stream);
             rc = comm_settle(c, r, "ncclAllGather");
         } else {
-            rc = exchange(c, reinterpret_cast<char*>(D_full), row_bytes, M,
+            /* the last group's transfer runs alone: the wide communicator; the others run beside the next GEMM */
+            rc = exchange(c, (g == groups - 1 || !c->narrow) ? c->comm : c->narrow, reinterpret_cast<char*>(D_full), row_bytes, M,
                           [&](int64_t n, int64_t* pa, int64_t* pbb) { panel_range(n, g, groups, pa, pbb); }, c->stream);
         }
     }

@@ -652,7 +652,8 @@ def main():
     ap.add_argument("--no-gather", action="store_true", help="skip the all-gather of the result blocks (N > 1)")
     ap.add_argument("--wave-align", type=int, default=1, choices=[0, 1, 2],
                     help="GEMM wave alignment: 1 cooperative launches (default), 2 plain launches (profilers; also beside a transfer), 0 off")
-    ap.add_argument("--comm-ctas", type=int, default=0, help="thread blocks per NCCL kernel of the gather layer (0 = its default, 16)")
+    ap.add_argument("--comm-ctas", type=int, default=0,
+                    help="thread blocks per NCCL kernel for the transfers that overlap a GEMM (0 = the library's default, two per rank)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="skip the other BASELINE configurations")
     ap.add_argument("--no-probe", action="store_true", help="skip the tensor-ceiling probes")
@@ -732,7 +733,7 @@ def main():
 
         gms = timed(lambda: comm.allgather_blocks(full, unit_bytes, total_units, stream=bench.st), 2)
         gather = {"ms": gms, "bytes_per_rank": mine, "busbw_gbs": mine * (world - 1) / (gms * 1e-3) / 1e9,
-                  "nccl_thread_blocks": args.comm_ctas or 16,
+                  "nccl_thread_blocks": {"alone": 32, "beside_a_gemm": args.comm_ctas or min(16, max(4, 2 * world))},
                   "how": "decxb_comm_allgather_blocks (NCCL, in place in the whole-result array) after the step, timed alone"}
         if wl["kind"] == "gemm":
             mode = {"3xtf32": bench.b.GEMM_3XTF32, "1xtf32": bench.b.GEMM_1XTF32, "strict": bench.b.GEMM_3XTF32_STRICT}[args.mode]

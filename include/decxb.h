@@ -448,11 +448,12 @@ DECXB_API int decxb_inject_pipeline_error(decxb_ctx* ctx, int nth_call);
  *   groups (1..64) straight into D_full[M][N] (dense, leading dimension N), each group sent to
  *   the peers while the next is multiplied; on return everything is queued, and `stream`
  *   continues only after all rows of D_full have arrived.  groups = 1 computes, then gathers.
- *   The last group, whose transfer nothing overlaps, is a third of an even share.  While
- *   transfers run, the GEMM leaves decxb_comm_set_reserved_sms SMs to NCCL's kernels (default: the
- *   communicator's limit of thread blocks per NCCL kernel, 16, or what the environment variable
- *   DECXB_COMM_MAX_CTAS said when the communicator was made).  A_rows points at the rank's first
- *   row; B is the whole matrix.
+ *   The last group, whose transfer nothing overlaps, is a third of an even share and travels
+ *   through a communicator with many thread blocks per NCCL kernel (32, environment variable
+ *   DECXB_COMM_WIDE_CTAS; decxb_comm_allgather_blocks uses the same one); the groups that travel
+ *   beside a GEMM use a second communicator limited to a few (two per rank, 4 to 16; DECXB_COMM_MAX_CTAS), and the GEMM
+ *   leaves that many SMs free (decxb_comm_set_reserved_sms changes the number of SMs).  A_rows
+ *   points at the rank's first row; B is the whole matrix.
  * decxb_comm_synchronize: waits (bounded) until the transfers queued so far have finished. */
 #define DECXB_COMM_ID_BYTES 128
 typedef struct decxb_comm decxb_comm;
