@@ -13,6 +13,7 @@ from .lib import (  # noqa: F401
     GEMM_1XTF32,
     GEMM_3XTF32,
     GEMM_3XTF32_STRICT,
+    GEMM_TF32_2XBF16,
     GEMM_DEFAULT,
     ACT_NONE,
     ACT_RELU,

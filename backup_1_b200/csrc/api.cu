@@ -85,7 +85,7 @@ int gemm_device(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_
                 const float* C, int64_t ldc, float* D, int64_t ldd, cudaStream_t s,
                 const float* bias = nullptr, int act = DECXB_ACT_NONE)
 {
-    if (mode != DECXB_GEMM_3XTF32 && mode != DECXB_GEMM_1XTF32 && mode != DECXB_GEMM_3XTF32_STRICT)
+    if (mode != DECXB_GEMM_3XTF32 && mode != DECXB_GEMM_1XTF32 && mode != DECXB_GEMM_3XTF32_STRICT && mode != DECXB_GEMM_TF32_2XBF16)
         return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "gemm mode");
     if (act < DECXB_ACT_NONE || act > DECXB_ACT_TANH) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "activation");
     if (M <= 0 || N <= 0 || K <= 0) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "gemm dims must be positive");
@@ -93,6 +93,27 @@ int gemm_device(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_
     if (lda < K || ldb < (b_is_nt ? K : N) || ldd < N || (C && ldc < N))
         return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
     Scratch scratch(ctx, s);
+    if (mode == DECXB_GEMM_TF32_2XBF16) {
+        /* hi * hi in TF32, a_lo * b and a * b_lo in bf16: three arrays per operand, 8 bytes per element as in 3xTF32 */
+        if (b_is_nt) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "the TF32 + 2 x bf16 mode takes B as [K][N]");
+        const int64_t Kp = decxb_split_pitch(K), K16 = decxb_ceil_to(K, 8);
+        float *a_hi = nullptr, *b_hi = nullptr; void *a_lo16 = nullptr, *a_16 = nullptr, *b_lo16 = nullptr, *b_16 = nullptr;
+        int rc2;
+        if ((rc2 = scratch.get((size_t)M * Kp * 4, (void**)&a_hi)) || (rc2 = scratch.get((size_t)M * K16 * 2, &a_lo16)) ||
+            (rc2 = scratch.get((size_t)M * K16 * 2, &a_16)) || (rc2 = scratch.get((size_t)N * Kp * 4, (void**)&b_hi)) ||
+            (rc2 = scratch.get((size_t)N * K16 * 2, &b_lo16)) || (rc2 = scratch.get((size_t)N * K16 * 2, &b_16))) return rc2;
+        if ((rc2 = decxb_launch_split_rows_bf16(ctx, A, M, K, lda, a_hi, a_lo16, a_16, Kp, K16, s))) return rc2;
+        if ((rc2 = decxb_launch_split_transpose_bf16(ctx, B, K, N, ldb, b_hi, b_lo16, b_16, Kp, K16, s))) return rc2;
+        decxb_gemm_args g = {};
+        g.chunked = 1;
+        g.M = M; g.N = N; g.K = K; g.C = C; g.ldc = ldc; g.D = D; g.ldd = ldd; g.tile = tile; g.b_rows = N;
+        g.a_hi = a_hi; g.lda = Kp; g.b_hi = b_hi; g.ldb = Kp;
+        g.a_16 = a_16; g.a_lo16 = a_lo16; g.b_16 = b_16; g.b_lo16 = b_lo16; g.ld16 = K16;
+        g.bias = bias; g.act = act;
+        rc2 = decxb_launch_gemm_tn(ctx, g, s);
+        scratch.release();
+        return rc2;
+    }
     /* the strict mode is the 3xTF32 product with K accumulated in chunks (see gemm_tcgen05.cu) */
     const bool strict = mode == DECXB_GEMM_3XTF32_STRICT;
     const bool x3 = mode == DECXB_GEMM_3XTF32 || strict;

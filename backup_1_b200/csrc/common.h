@@ -193,6 +193,12 @@ bool decxb_split_ab_possible(const float* B, int64_t ldb, const float* b_hi, con
 int decxb_launch_split_ab(decxb_ctx* ctx, const float* A, int64_t M, int64_t K, int64_t lda, float* a_hi, float* a_lo,
                           const float* B, int64_t N, int64_t ldb, float* b_hi, float* b_lo, int64_t ld_out, cudaStream_t s);
 
+/* Operands of the TF32 + 2 x bf16 mode: hi = tf32(a) [rows][ld_hi], lo16 = bf16(a - hi) and a16 = bf16(a) [rows][ld16]. */
+int decxb_launch_split_rows_bf16(decxb_ctx* ctx, const float* in, int64_t rows, int64_t cols, int64_t ld_in,
+                                 float* hi, void* lo16, void* a16, int64_t ld_hi, int64_t ld16, cudaStream_t s);
+int decxb_launch_split_transpose_bf16(decxb_ctx* ctx, const float* in, int64_t K, int64_t N, int64_t ld_in,
+                                      float* hi, void* lo16, void* b16, int64_t ld_hi, int64_t ld16, cudaStream_t s);
+
 /* The tensor-core GEMM on K-contiguous operands.  a_hi/a_lo: [M][lda], b_hi/b_lo: [N][ldb]
  * (lo pointers NULL for plain TF32).  C optional addend, D output. */
 struct decxb_gemm_args {
@@ -205,6 +211,8 @@ struct decxb_gemm_args {
     int tile;
     const float* bias; int act;      /* fused epilogue (NULL / DECXB_ACT_NONE = off) */
     int chunked;                     /* 1 = accumulate K in chunks of 128 added in IEEE fp32 (3xTF32 only) */
+    /* TF32 + 2 x bf16 mode (a_16 != NULL): bf16(a), bf16(a_lo), bf16(b), bf16(b_lo), [rows][ld16] with K contiguous */
+    const void *a_16, *a_lo16, *b_16, *b_lo16; int64_t ld16;
     /* batched: nbatch > 1 stacked matrices; A holds m_pad rows per matrix, B n_pad rows per matrix
      * (both multiples of the tile chosen by `tile`, which must then be explicit) */
     int64_t nbatch, m_pad, n_pad, d_batch_stride, c_batch_stride;

@@ -284,6 +284,9 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
  * CTAS   : 1 or 2 CTAs per tile (cta_group)
  * BN     : rows of the B operand (columns of D) loaded per CTA; UMMA N = BN * CTAS
  * NSPLIT : 3 = 3xTF32 (hi and lo parts of both operands), 1 = plain TF32,
+ *          2 = the hi * hi product in TF32 and the two cross products a_lo * b and a * b_lo in bf16 (kind::f16 with
+ *          bf16 operands, twice the TF32 rate): the stage holds the TF32 hi tile and, in the space of the lo tile,
+ *          two bf16 tiles of 64-byte rows (64-byte swizzle); 4 + 4 MMAs per k-block instead of 12,
  *          16 = fp16 operands and fp16 result with fp32 accumulation (kind::f16); a k-block is
  *          then 64 halves, still one 128-byte row, and a k-step 16 halves, still 32 bytes
  * KCH    : 0 = the tensor core accumulates over all of K.  > 0 = chunked accumulation: the
@@ -295,7 +298,7 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
  * ------------------------------------------------------------------------------------ */
 template <int CTAS, int BN, int NSPLIT, int KCH = 0>
 struct Cfg {
-    static constexpr int PARTS = NSPLIT == 3 ? 2 : 1;
+    static constexpr int PARTS = (NSPLIT == 3 || NSPLIT == 2) ? 2 : 1;
     static constexpr int EPI_WARPS = NSPLIT == 16 ? 4 : 8;
     static constexpr int THREADS = KCH ? NUM_THREADS_CHUNKED : NSPLIT == 16 ? NUM_THREADS_F16 : NUM_THREADS;
     /* one 32 x 32 fp32 box (4 KiB, 128-byte swizzled) per epilogue warp for the TMA result stores */
@@ -323,8 +326,10 @@ template <int CTAS, int BN, int NSPLIT, bool CONV, int KCH>
 __global__ void __launch_bounds__((Cfg<CTAS, BN, NSPLIT, KCH>::THREADS), 1)
 decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                        const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
-                       const __grid_constant__ CUtensorMap map_d, const GemmParams p)
+                       const __grid_constant__ CUtensorMap map_d, const GemmParams p,
+                       const __grid_constant__ CUtensorMap map_a_x, const __grid_constant__ CUtensorMap map_b_x)
 {
+    /* NSPLIT == 2: map_a_lo = bf16(a_lo), map_a_x = bf16(a), map_b_lo = bf16(b_lo), map_b_x = bf16(b); unused otherwise */
     using C = Cfg<CTAS, BN, NSPLIT, KCH>;
     extern __shared__ uint8_t smem_raw[];
     /* 1024-byte alignment: the 128-byte swizzle pattern is a function of address bits 4-9. */
@@ -348,7 +353,8 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
 
     if (threadIdx.x == 0) {
         prefetch_tensormap(&map_a_hi); prefetch_tensormap(&map_b_hi);
-        if (NSPLIT == 3) { prefetch_tensormap(&map_a_lo); prefetch_tensormap(&map_b_lo); }
+        if (NSPLIT == 3 || NSPLIT == 2) { prefetch_tensormap(&map_a_lo); prefetch_tensormap(&map_b_lo); }
+        if (NSPLIT == 2) { prefetch_tensormap(&map_a_x); prefetch_tensormap(&map_b_x); }
         if (p.tma_store) prefetch_tensormap(&map_d);
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), C::EPI_WARPS * CTAS); }
@@ -426,9 +432,17 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
                         } else {
                             tma_load_2d(stage_a(stage, 0), &map_a_hi, fb, kx, row_a);
                             if (NSPLIT == 3) tma_load_2d(stage_a(stage, 1), &map_a_lo, fb, kx, row_a);
+                            if (NSPLIT == 2) {
+                                tma_load_2d(stage_a(stage, 1), &map_a_lo, fb, kx, row_a);
+                                tma_load_2d(stage_a(stage, 1) + C::A_BYTES / 2, &map_a_x, fb, kx, row_a);
+                            }
                         }
                         tma_load_2d(stage_b(stage, 0), &map_b_hi, fb, kx, row_b);
                         if (NSPLIT == 3) tma_load_2d(stage_b(stage, 1), &map_b_lo, fb, kx, row_b);
+                        if (NSPLIT == 2) {
+                            tma_load_2d(stage_b(stage, 1), &map_b_x, fb, kx, row_b);
+                            tma_load_2d(stage_b(stage, 1) + C::B_BYTES / 2, &map_b_lo, fb, kx, row_b);
+                        }
                     } else {
                         /* Both CTAs' bytes are counted on the leader's barrier. */
                         if (is_leader) mbar_arrive_expect_tx(full_bar(stage), 2 * C::STAGE_BYTES);
@@ -444,9 +458,17 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
                         } else {
                             tma_load_2d_pair(stage_a(stage, 0), &map_a_hi, fb, kx, row_a);
                             if (NSPLIT == 3) tma_load_2d_pair(stage_a(stage, 1), &map_a_lo, fb, kx, row_a);
+                            if (NSPLIT == 2) {
+                                tma_load_2d_pair(stage_a(stage, 1), &map_a_lo, fb, kx, row_a);
+                                tma_load_2d_pair(stage_a(stage, 1) + C::A_BYTES / 2, &map_a_x, fb, kx, row_a);
+                            }
                         }
                         tma_load_2d_pair(stage_b(stage, 0), &map_b_hi, fb, kx, row_b);
                         if (NSPLIT == 3) tma_load_2d_pair(stage_b(stage, 1), &map_b_lo, fb, kx, row_b);
+                        if (NSPLIT == 2) {
+                            tma_load_2d_pair(stage_b(stage, 1), &map_b_x, fb, kx, row_b);
+                            tma_load_2d_pair(stage_b(stage, 1) + C::B_BYTES / 2, &map_b_lo, fb, kx, row_b);
+                        }
                     }
                     armed |= 1u << stage;
                     armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
@@ -490,6 +512,23 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
                         const uint64_t db_hi = make_smem_desc(stage_b(stage, 0));
                         const uint64_t da_lo = make_smem_desc(stage_a(stage, C::PARTS - 1));
                         const uint64_t db_lo = make_smem_desc(stage_b(stage, C::PARTS - 1));
+                        if constexpr (NSPLIT == 2) {
+                            /* per 16 values of K: a_lo * b and a * b_lo in bf16 (one MMA each, 32 bytes of a 64-byte row),
+                             * then hi * hi in TF32 (two MMAs of 8); the small terms first */
+                            constexpr uint32_t idesc_bf = make_idesc_bf16(C::UMMA_M, C::UMMA_N);
+                            const uint64_t da_lb = make_smem_desc_sw64(stage_a(stage, 1));
+                            const uint64_t da_ab = make_smem_desc_sw64(stage_a(stage, 1) + C::A_BYTES / 2);
+                            const uint64_t db_bb = make_smem_desc_sw64(stage_b(stage, 1));
+                            const uint64_t db_lb = make_smem_desc_sw64(stage_b(stage, 1) + C::B_BYTES / 2);
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                const uint32_t first = ((kb - kb0) | h) != 0 ? 1u : 0u;
+                                umma_f16<CTAS>(tmem_d, da_lb + (uint64_t)(2 * h), db_bb + (uint64_t)(2 * h), idesc_bf, first);
+                                umma_f16<CTAS>(tmem_d, da_ab + (uint64_t)(2 * h), db_lb + (uint64_t)(2 * h), idesc_bf, 1u);
+                                umma_tf32<CTAS>(tmem_d, da_hi + (uint64_t)(4 * h), db_hi + (uint64_t)(4 * h), idesc, 1u);
+                                umma_tf32<CTAS>(tmem_d, da_hi + (uint64_t)(4 * h + 2), db_hi + (uint64_t)(4 * h + 2), idesc, 1u);
+                            }
+                        } else {
 #pragma unroll
                         for (int kk = 0; kk < BK / UMMA_K; ++kk) {
                             /* advance 8 floats = 32 bytes inside the 128-byte swizzled row */
@@ -506,6 +545,7 @@ decxb_gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
                             } else {
                                 umma_tf32<CTAS>(tmem_d, da_hi + koff, db_hi + koff, idesc, first);
                             }
+                        }
                         }
                         umma_commit<CTAS>(empty_bar(stage));     /* stage reusable once these MMAs have read it */
                         if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
@@ -798,16 +838,16 @@ int make_map_conv_dst(decxb_ctx* ctx, CUtensorMap* map, const float* base, int64
  * groups (setmaxnreg) and count on exactly 168 registers per thread at launch.  Whether the
  * toolkit compiled them that way is asked once per device; when it did not, the callers take
  * the 128 x 128 tile, whose chunked kernel needs no register hand-over and gives the same bits. */
-template <int CTAS, int BN, bool CONV>
+template <int CTAS, int BN, bool CONV, int NSPLIT = 3>
 bool chunked_regs_ok(decxb_ctx* ctx)
 {
-    using C = Cfg<CTAS, BN, 3, KCHUNK>;
+    using C = Cfg<CTAS, BN, NSPLIT, KCHUNK>;
     if (C::UMMA_N / 2 <= 64) return true;
     static std::atomic<int> regs[DECXB_MAX_DEVICES];
     int r = regs[ctx->device].load();
     if (r == 0) {
         cudaFuncAttributes fa;
-        if (cudaFuncGetAttributes(&fa, decxb_gemm_tf32_kernel<CTAS, BN, 3, CONV, KCHUNK>) != cudaSuccess) { cudaGetLastError(); return false; }
+        if (cudaFuncGetAttributes(&fa, decxb_gemm_tf32_kernel<CTAS, BN, NSPLIT, CONV, KCHUNK>) != cudaSuccess) { cudaGetLastError(); return false; }
         r = fa.numRegs;
         regs[ctx->device].store(r);
     }
@@ -819,8 +859,11 @@ bool chunked_regs_ok(decxb_ctx* ctx)
 
 template <int CTAS, int BN, int NSPLIT, bool CONV, int KCH = 0>
 int launch_kernel(decxb_ctx* ctx, const CUtensorMap& ma_hi, const CUtensorMap& ma_lo, const CUtensorMap& mb_hi,
-                  const CUtensorMap& mb_lo, const CUtensorMap& md, const GemmParams& p, cudaStream_t s)
+                  const CUtensorMap& mb_lo, const CUtensorMap& md, const GemmParams& p, cudaStream_t s,
+                  const CUtensorMap* ma_x_or_null = nullptr, const CUtensorMap* mb_x_or_null = nullptr)
 {
+    const CUtensorMap& ma_x = ma_x_or_null ? *ma_x_or_null : ma_hi;
+    const CUtensorMap& mb_x = mb_x_or_null ? *mb_x_or_null : mb_hi;
     using C = Cfg<CTAS, BN, NSPLIT, KCH>;
     auto kernel = decxb_gemm_tf32_kernel<CTAS, BN, NSPLIT, CONV, KCH>;
     static std::once_flag once[DECXB_MAX_DEVICES];
@@ -832,8 +875,8 @@ int launch_kernel(decxb_ctx* ctx, const CUtensorMap& ma_hi, const CUtensorMap& m
     if (attr_err[dev] != cudaSuccess)
         return decxb_fail(ctx, DECXB_ERR_CUDA, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(attr_err[dev]));
     /* never launch a register-moving kernel whose register count does not add up: its epilogue would wait forever */
-    if constexpr (KCH > 0 && NSPLIT == 3) {
-        if (!chunked_regs_ok<CTAS, BN, CONV>(ctx))
+    if constexpr (KCH > 0 && (NSPLIT == 3 || NSPLIT == 2)) {
+        if (!chunked_regs_ok<CTAS, BN, CONV, NSPLIT>(ctx))
             return decxb_fail(ctx, DECXB_ERR_CUDA, "chunked GEMM kernel was not compiled to 168 registers");
     }
     const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
@@ -868,7 +911,7 @@ int launch_kernel(decxb_ctx* ctx, const CUtensorMap& ma_hi, const CUtensorMap& m
             cudaError_t e;
             {
                 decxb_launch_scope scope(ctx, s, DECXB_K_GEMM);
-                e = cudaLaunchKernelEx(&cfg, kernel, ma_hi, ma_lo, mb_hi, mb_lo, md, pp);
+                e = cudaLaunchKernelEx(&cfg, kernel, ma_hi, ma_lo, mb_hi, mb_lo, md, pp, ma_x, mb_x);
             }
             if (e == cudaSuccess) return DECXB_OK;
             cudaGetLastError();
@@ -882,7 +925,7 @@ int launch_kernel(decxb_ctx* ctx, const CUtensorMap& ma_hi, const CUtensorMap& m
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     {
         decxb_launch_scope scope(ctx, s, DECXB_K_GEMM);
-        DECXB_CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kernel, ma_hi, ma_lo, mb_hi, mb_lo, md, pp));
+        DECXB_CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kernel, ma_hi, ma_lo, mb_hi, mb_lo, md, pp, ma_x, mb_x));
     }
     return DECXB_OK;
 }
@@ -941,11 +984,29 @@ int launch_conv_cfg(decxb_ctx* ctx, const decxb_conv_gemm_args& a, cudaStream_t 
     return launch_kernel<CTAS, BN, NSPLIT, true, KCH>(ctx, ma_hi, ma_lo, mb_hi, mb_lo, md, p, s);
 }
 
+/* rows x K bf16 array with K contiguous and a row pitch of `ld` values; box = 32 values (64 bytes) x box_rows, 64-byte swizzle. */
+int make_map_bf16(decxb_ctx* ctx, CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64_t ld, int box_rows)
+{
+    auto fn = get_encode_fn();
+    if (!fn) return decxb_fail(ctx, DECXB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
+    if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld % 8))
+        return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "TMA bf16 operand must be 16-byte aligned with a pitch that is a multiple of 8 values");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return decxb_fail(ctx, DECXB_ERR_CUDA, "cuTensorMapEncodeTiled (bf16) failed: " + std::to_string((int)r));
+    return DECXB_OK;
+}
+
 template <int CTAS, int BN, int NSPLIT, int KCH = 0>
 int launch_cfg(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s)
 {
     using C = Cfg<CTAS, BN, NSPLIT>;
-    CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
+    CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo, ma_x, mb_x;
     int rc;
     const int64_t a_rows = a.nbatch > 1 ? a.m_pad * a.nbatch : a.M;
     const int64_t b_rows = a.nbatch > 1 ? a.n_pad * a.nbatch : a.b_rows;
@@ -954,6 +1015,11 @@ int launch_cfg(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s)
     if (NSPLIT == 3) {
         if ((rc = make_map(ctx, &ma_lo, a.a_lo, a_rows, a.K, a.lda, BM_CTA))) return rc;
         if ((rc = make_map(ctx, &mb_lo, a.b_lo, b_rows, a.K, a.ldb, BN))) return rc;
+    } else if (NSPLIT == 2) {
+        if ((rc = make_map_bf16(ctx, &ma_lo, a.a_lo16, a_rows, a.K, a.ld16, BM_CTA))) return rc;
+        if ((rc = make_map_bf16(ctx, &ma_x, a.a_16, a_rows, a.K, a.ld16, BM_CTA))) return rc;
+        if ((rc = make_map_bf16(ctx, &mb_lo, a.b_lo16, b_rows, a.K, a.ld16, BN))) return rc;
+        if ((rc = make_map_bf16(ctx, &mb_x, a.b_16, b_rows, a.K, a.ld16, BN))) return rc;
     } else { ma_lo = ma_hi; mb_lo = mb_hi; }
 
     GemmParams p = {};
@@ -982,6 +1048,7 @@ int launch_cfg(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t s)
         if ((rc = make_map(ctx, &md, a.D, a.M, a.N, a.ldd, 32))) return rc;
         p.tma_store = 1;
     }
+    if (NSPLIT == 2) return launch_kernel<CTAS, BN, NSPLIT, false, KCH>(ctx, ma_hi, ma_lo, mb_hi, mb_lo, md, p, s, &ma_x, &mb_x);
     return launch_kernel<CTAS, BN, NSPLIT, false, KCH>(ctx, ma_hi, ma_lo, mb_hi, mb_lo, md, p, s);
 }
 
@@ -1056,6 +1123,12 @@ int decxb_launch_gemm_tn(decxb_ctx* ctx, const decxb_gemm_args& a, cudaStream_t 
     const bool x3 = a.a_lo != nullptr;
     int tile = a.tile;
     if (tile == DECXB_TILE_AUTO) tile = decxb_pick_tile(ctx, a.M, a.N, a.nbatch);
+    if (a.a_16) {
+        /* TF32 hi * hi plus two bf16 cross products, K accumulated in chunks; two tile shapes */
+        if (a.nbatch > 1 || !a.a_lo16 || !a.b_16 || !a.b_lo16) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "bf16 cross-term operands");
+        if (tile != DECXB_TILE_2CTA_256x256 || !chunked_regs_ok<2, 128, false, 2>(ctx)) return launch_cfg<1, 128, 2, KCHUNK>(ctx, a, s);
+        return launch_cfg<2, 128, 2, KCHUNK>(ctx, a, s);
+    }
     /* a K that fits the first chunk gives the same bits either way: take the kernel with fewer threads */
     const bool chunked = a.chunked && decxb_ceil_div(a.K, BK) > 2 * KCHUNK;
     if (a.chunked && !x3) return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "chunked accumulation needs the 3xTF32 operands");

@@ -10,6 +10,8 @@
  */
 #include "common.h"
 
+#include <cuda_bf16.h>
+
 /* ------------------------------------------------------------------------------------ */
 __device__ __forceinline__ uint32_t fmix32(uint32_t h)
 {
@@ -434,6 +436,121 @@ int decxb_launch_transpose_f16(decxb_ctx* ctx, const void* in, int64_t K, int64_
                                   decxb_make_extent(out, (size_t)(N * ld_out) * 2), {}, DECXB_BK_TRANSPOSE_F16};
         decxb_transpose_f16_kernel<<<(int)blocks, 256, 0, s>>>(static_cast<const unsigned short*>(in), K, N, ld_in,
                                                                static_cast<unsigned short*>(out), ld_out, tiles_n, bnd);
+    }
+    DECXB_CUDA_TRY(ctx, cudaGetLastError());
+    return DECXB_OK;
+}
+
+/* ------------------------------------------------------------------------------------
+ * Operands of the TF32 + 2 x bf16 mode: hi = tf32(a) as above, and two bf16 arrays for the cross
+ * products, lo16 = bf16(a - hi) and a16 = bf16(a) (round to nearest even).  One thread per 8
+ * consecutive k, so that the bf16 stores are 16 bytes.  Row pitches: hi `ld_hi` floats (a multiple of
+ * 4), bf16 arrays `ld16` values (a multiple of 8); pad columns are written as zero.
+ * ---------------------------------------------------------------------------------- */
+__device__ __forceinline__ uint32_t pack_bf16x2(float x, float y)
+{
+    const __nv_bfloat162 v = __floats2bfloat162_rn(x, y);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__device__ __forceinline__ void split8_store(const float* v, float* hi_row, unsigned short* lo16_row, unsigned short* a16_row,
+                                             int64_t k, int64_t ld_hi)
+{
+    float h[8], l[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { h[j] = tf32_rna(v[j]); l[j] = __fsub_rn(v[j], h[j]); }
+    *reinterpret_cast<float4*>(hi_row + k) = make_float4(h[0], h[1], h[2], h[3]);
+    if (k + 4 < ld_hi) *reinterpret_cast<float4*>(hi_row + k + 4) = make_float4(h[4], h[5], h[6], h[7]);
+    *reinterpret_cast<uint4*>(lo16_row + k) = make_uint4(pack_bf16x2(l[0], l[1]), pack_bf16x2(l[2], l[3]), pack_bf16x2(l[4], l[5]), pack_bf16x2(l[6], l[7]));
+    *reinterpret_cast<uint4*>(a16_row + k) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+}
+
+__global__ void __launch_bounds__(256)
+decxb_split_rows_bf16_kernel(const float* __restrict__ in, int64_t rows, int64_t cols, int64_t ld_in,
+                             float* __restrict__ hi, unsigned short* __restrict__ lo16, unsigned short* __restrict__ a16,
+                             int64_t ld_hi, int64_t ld16, int in_vec_ok)
+{
+    allow_dependent_launch();
+    const int64_t o_per_row = ld16 >> 3;
+    const int64_t total = rows * o_per_row;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / o_per_row, k = (i - r * o_per_row) << 3;
+        float v[8];
+        if (in_vec_ok && k + 7 < cols) {
+            const float4 t0 = __ldg(reinterpret_cast<const float4*>(in + r * ld_in + k));
+            const float4 t1 = __ldg(reinterpret_cast<const float4*>(in + r * ld_in + k + 4));
+            v[0] = t0.x; v[1] = t0.y; v[2] = t0.z; v[3] = t0.w; v[4] = t1.x; v[5] = t1.y; v[6] = t1.z; v[7] = t1.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = (k + j < cols) ? __ldg(in + r * ld_in + k + j) : 0.0f;
+        }
+        split8_store(v, hi + r * ld_hi, lo16 + r * ld16, a16 + r * ld16, k, ld_hi);
+    }
+}
+
+/* in[K][ld_in] (K rows, N columns) -> the same three arrays of the transposed operand, [N][...] with K contiguous. */
+__global__ void __launch_bounds__(256)
+decxb_split_transpose_bf16_kernel(const float* __restrict__ in, int64_t K, int64_t N, int64_t ld_in,
+                                  float* __restrict__ hi, unsigned short* __restrict__ lo16, unsigned short* __restrict__ b16,
+                                  int64_t ld_hi, int64_t ld16, int64_t tiles_n)
+{
+    __shared__ float tile[64][65];
+    allow_dependent_launch();
+    const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+    const int64_t tiles_k = (ld16 + 63) / 64;
+    for (int64_t t = blockIdx.x; t < tiles_k * tiles_n; t += gridDim.x) {
+        const int64_t k0 = (t / tiles_n) * 64, n0 = (t % tiles_n) * 64;
+#pragma unroll 4
+        for (int j = ty; j < 64; j += 4) {
+            const int64_t k = k0 + j, n = n0 + tx;
+            tile[j][tx] = (k < K && n < N) ? __ldg(in + k * ld_in + n) : 0.0f;
+        }
+        __syncthreads();
+        /* 64 n-rows x 8 runs of 8 consecutive k */
+        for (int i = threadIdx.x; i < 512; i += 256) {
+            const int nr = i >> 3, k8 = (i & 7) << 3;
+            const int64_t n = n0 + nr, k = k0 + k8;
+            if (n < N && k < ld16) {
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = tile[k8 + j][nr];
+                split8_store(v, hi + n * ld_hi, lo16 + n * ld16, b16 + n * ld16, k, ld_hi);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+int decxb_launch_split_rows_bf16(decxb_ctx* ctx, const float* in, int64_t rows, int64_t cols, int64_t ld_in,
+                                 float* hi, void* lo16, void* a16, int64_t ld_hi, int64_t ld16, cudaStream_t s)
+{
+    if (ld16 % 8 || ld16 < cols || ld_hi % 4 || ld_hi < cols || ld_hi > ld16) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "bf16 split pitch");
+    const int64_t total = rows * (ld16 / 8);
+    if (total == 0) return DECXB_OK;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > (int64_t)ctx->sm_count * 32) blocks = (int64_t)ctx->sm_count * 32;
+    {
+        decxb_launch_scope scope(ctx, s, DECXB_K_SPLIT);
+        const int vec_ok = ((uintptr_t)in % 16 == 0) && (ld_in % 4 == 0);
+        decxb_split_rows_bf16_kernel<<<(int)blocks, 256, 0, s>>>(in, rows, cols, ld_in, hi, static_cast<unsigned short*>(lo16),
+                                                                 static_cast<unsigned short*>(a16), ld_hi, ld16, vec_ok);
+    }
+    DECXB_CUDA_TRY(ctx, cudaGetLastError());
+    return DECXB_OK;
+}
+
+int decxb_launch_split_transpose_bf16(decxb_ctx* ctx, const float* in, int64_t K, int64_t N, int64_t ld_in,
+                                      float* hi, void* lo16, void* b16, int64_t ld_hi, int64_t ld16, cudaStream_t s)
+{
+    if (ld16 % 8 || ld16 < K || ld_hi % 4 || ld_hi < K || ld_hi > ld16) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "bf16 split pitch");
+    const int64_t tiles_n = (N + 63) / 64, tiles_k = (ld16 + 63) / 64;
+    int64_t blocks = tiles_n * tiles_k;
+    if (blocks == 0) return DECXB_OK;
+    if (blocks > (int64_t)ctx->sm_count * 16) blocks = (int64_t)ctx->sm_count * 16;
+    {
+        decxb_launch_scope scope(ctx, s, DECXB_K_SPLIT);
+        decxb_split_transpose_bf16_kernel<<<(int)blocks, 256, 0, s>>>(in, K, N, ld_in, hi, static_cast<unsigned short*>(lo16),
+                                                                      static_cast<unsigned short*>(b16), ld_hi, ld16, tiles_n);
     }
     DECXB_CUDA_TRY(ctx, cudaGetLastError());
     return DECXB_OK;

@@ -236,12 +236,31 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr)
     return d;
 }
 
+/* The same for a K-contiguous tile whose rows are 64 bytes (32 bf16 values), written by TMA with the
+ * 64-byte swizzle: 8-row groups lie 512 bytes apart, layout type 4 (64-byte swizzle). */
+__device__ __forceinline__ uint64_t make_smem_desc_sw64(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(512 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)4 << 61;
+    return d;
+}
+
 /* Instruction descriptor: D fp32 (bits 4-5 = 1), A and B TF32 (bits 7-9, 10-12 = 2), both
  * K-major (bits 15, 16 = 0), N>>3 at bits 17-22, M>>4 at bits 24-28. */
 /* Same with fp16 operands (format code 0 at bits 7-9 and 10-12), fp32 accumulator. */
 __host__ __device__ constexpr uint32_t make_idesc_f16(int umma_m, int umma_n)
 {
     return (1u << 4) | ((uint32_t)(umma_n >> 3) << 17) | ((uint32_t)(umma_m >> 4) << 24);
+}
+
+/* bf16 operands (format code 1), fp32 accumulator; issued with kind::f16 like fp16. */
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int umma_m, int umma_n)
+{
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(umma_n >> 3) << 17) | ((uint32_t)(umma_m >> 4) << 24);
 }
 
 __host__ __device__ constexpr uint32_t make_idesc(int umma_m, int umma_n)

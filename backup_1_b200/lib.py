@@ -4,7 +4,7 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
-GEMM_3XTF32, GEMM_1XTF32, GEMM_3XTF32_STRICT = 0, 1, 2
+GEMM_3XTF32, GEMM_1XTF32, GEMM_3XTF32_STRICT, GEMM_TF32_2XBF16 = 0, 1, 2, 3
 GEMM_DEFAULT = GEMM_3XTF32_STRICT   # what the DECX-facing host layer uses unless told otherwise
 TILE_AUTO, TILE_1CTA_128x128, TILE_2CTA_256x256, TILE_1CTA_128x256, TILE_1CTA_128x64 = 0, 1, 2, 3, 4
 CONV_NO_COMPENSATE, CONV_ZERO_COMPENSATE = 0, 1

@@ -128,7 +128,7 @@ def dist_env():
 
 def touched_bytes(wl, mode, world):
     """Bytes one step touches per rank (operands, split/column scratch, result): decides whether L2 must be flushed."""
-    parts = 3 if mode in ("3xtf32", "strict") else 2
+    parts = 3 if mode in ("3xtf32", "strict", "tf32bf16") else 2
     if wl["kind"] == "gemm":
         m = wl["M"] // world if wl["scaling"] == "strong" else wl["M"]
         esz = 2 if mode == "f16" else 4
@@ -299,7 +299,8 @@ class Bench:
         torch, b, ctx, dev, world, rank = self.torch, self.b, self.ctx, self.dev, self.world, self.rank
         from backup_1_b200 import shard
         args = self.args
-        mode = {"3xtf32": b.GEMM_3XTF32, "1xtf32": b.GEMM_1XTF32, "strict": b.GEMM_3XTF32_STRICT, "f16": b.GEMM_1XTF32}[mode_name]
+        mode = {"3xtf32": b.GEMM_3XTF32, "1xtf32": b.GEMM_1XTF32, "strict": b.GEMM_3XTF32_STRICT, "f16": b.GEMM_1XTF32,
+                "tf32bf16": b.GEMM_TF32_2XBF16}[mode_name]
         algo = b.CONV_EXPLICIT if args.algo == "explicit" else b.CONV_IMPLICIT
         w = {"name": name, "wl": wl, "mode": mode_name}
         if wl["kind"] == "gemm":
@@ -329,7 +330,7 @@ class Bench:
                 def step():  # noqa: F811
                     ctx.gemm_f16(M_rank, N, K, dA, K, dB, N, dD, N, stream=self.st)
             w["step"] = step
-            if mode_name != "f16":
+            if mode_name not in ("f16", "tf32bf16"):
                 def prepare():
                     w["pb"] = ctx.prepare_b(K, N, dB, N, mode=mode, stream=self.st)
 
@@ -350,7 +351,9 @@ class Bench:
                     if mode_name == "f16":
                         ctx.gemm_f16_host(M_rank, N, K, hA.data_ptr(), K, hB.data_ptr(), N, hD.data_ptr(), N)
                     else:
-                        ctx.gemm_host(M_rank, N, K, hA.data_ptr(), K, hB.data_ptr(), N, hD.data_ptr(), N, mode=mode, tile=args.tile)
+                        # the host-resident entry does not take the bf16 cross-product mode: its leg runs the default mode
+                        ctx.gemm_host(M_rank, N, K, hA.data_ptr(), K, hB.data_ptr(), N, hD.data_ptr(), N,
+                                      mode=b.GEMM_3XTF32_STRICT if mode_name == "tf32bf16" else mode, tile=args.tile)
                 w["step_host"] = step_host
         else:
             W, H, C, kW, kH, F, batch = (wl[k] for k in ("W", "H", "C", "kW", "kH", "F", "batch"))
@@ -520,7 +523,7 @@ class Bench:
             per_step = prof["gemm"]["launches"] / psteps
             flops_launch = w["flops"] / per_step
             ach = flops_launch / (avg_ms * 1e-3) / 1e12
-            div = {"3xtf32": 6.0, "strict": 6.0, "1xtf32": 2.0, "f16": 1.0}[mode]
+            div = {"3xtf32": 6.0, "strict": 6.0, "1xtf32": 2.0, "f16": 1.0, "tf32bf16": 4.0}[mode]
             long_step = avg_ms * per_step >= 100.0          # a kernel inside a seconds-long region runs under the power cap
             bf16 = peaks["bf16_sustained"] if long_step else peaks["bf16_tflops"]
             peak = bf16 / div
@@ -536,7 +539,8 @@ class Bench:
                  "frac": ach / peak, "traffic": traffic,
                  "peak_basis": (f"{peaks['basis']} bf16 dense {'sustained' if long_step else 'burst'} {bf16} TFLOP/s"
                                 + {"3xtf32": " / 2 (TF32) / 3 (3xTF32)", "strict": " / 2 (TF32) / 3 (3xTF32)", "1xtf32": " / 2 (TF32)",
-                                   "f16": " (fp16 runs at the bf16 rate)"}[mode]
+                                   "f16": " (fp16 runs at the bf16 rate)",
+                                   "tf32bf16": " / 4 (one TF32 product and two bf16 products at twice the TF32 rate = two TF32 products)"}[mode]
                                 + (": steps of >= 100 ms run under the power cap" if long_step else ": a step is shorter than 100 ms")),
                  "frac_burst_basis": ach / (peaks["bf16_tflops"] / div), "frac_sustained_basis": ach / (peaks["bf16_sustained"] / div),
                  "avg_launch_ms": avg_ms, "time_shares": shares}
@@ -641,9 +645,10 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="cfg5", choices=sorted(WORKLOADS))
-    ap.add_argument("--mode", default="strict", choices=["strict", "3xtf32", "1xtf32", "f16"],
+    ap.add_argument("--mode", default="strict", choices=["strict", "3xtf32", "1xtf32", "f16", "tf32bf16"],
                     help="strict = 3xTF32 with chunked IEEE accumulation (the default of the DECX-facing layer); "
-                         "3xtf32 = tensor core accumulates over all of K; 1xtf32 = plain TF32; f16 = the fp16 overloads")
+                         "3xtf32 = tensor core accumulates over all of K; 1xtf32 = plain TF32; f16 = the fp16 overloads; "
+                         "tf32bf16 = hi*hi in TF32 and the two cross products in bf16 (opt-in, GEMM workloads)")
     ap.add_argument("--tile", type=int, default=0)
     ap.add_argument("--algo", default="implicit", choices=["explicit", "implicit"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -669,8 +674,8 @@ def main():
             print(json.dumps({"impl": "reference", "unavailable": "the pcie workload measures this host's copies only"}))
             return
         return run_reference(args, wl, args.workload)
-    if args.mode == "f16" and wl["kind"] != "gemm":
-        raise SystemExit("--mode f16 applies to the GEMM workloads")
+    if args.mode in ("f16", "tf32bf16") and wl["kind"] != "gemm":
+        raise SystemExit(f"--mode {args.mode} applies to the GEMM workloads")
 
     bench = Bench(args)
     torch, dist, ctx, rank, world = bench.torch, bench.dist, bench.ctx, bench.rank, bench.world
@@ -736,7 +741,8 @@ def main():
                   "nccl_thread_blocks": {"alone": 32, "beside_a_gemm": args.comm_ctas or min(16, max(4, 2 * world))},
                   "how": "decxb_comm_allgather_blocks (NCCL, in place in the whole-result array) after the step, timed alone"}
         if wl["kind"] == "gemm":
-            mode = {"3xtf32": bench.b.GEMM_3XTF32, "1xtf32": bench.b.GEMM_1XTF32, "strict": bench.b.GEMM_3XTF32_STRICT}[args.mode]
+            mode = {"3xtf32": bench.b.GEMM_3XTF32, "1xtf32": bench.b.GEMM_1XTF32, "strict": bench.b.GEMM_3XTF32_STRICT,
+                    "tf32bf16": bench.b.GEMM_3XTF32_STRICT}[args.mode]
             A_rows, Bm = w["dA"], w["dB"]
             for groups in (1, 3, 4, 6):
                 ms = timed(lambda: comm.gemm_rowshard_gather(wl["M"], wl["N"], wl["K"], A_rows, wl["K"], Bm, wl["N"], full, groups=groups,
@@ -784,7 +790,7 @@ def main():
     also = []
     del w
     torch.cuda.empty_cache(); ctx.release_cached()
-    if not args.no_also and args.mode != "f16":
+    if not args.no_also and args.mode not in ("f16", "tf32bf16"):
         for name, steps in ALSO:
             if name == args.workload:
                 continue
@@ -805,6 +811,21 @@ def main():
             except Exception as ex:
                 also.append({"workload": name, "failed": str(ex)[:200]})
             torch.cuda.empty_cache(); ctx.release_cached()
+
+    if not args.no_also and args.mode == "strict":
+        try:     # the opt-in TF32 + 2 x bf16 mode on the north-star shape, for the record
+            w3 = bench.build("gemm16k", dict(WORKLOADS["gemm16k"]), "tf32bf16", host_leg=False)
+            r3 = bench.measure(w3, 5, 3, sample_clocks=False)
+            rf3 = bench.roofline(w3, r3)
+            e3 = bench.check(w3)
+            also.append({"workload": "gemm16k", "mode": "tf32bf16 (opt-in: TF32 hi*hi + two bf16 cross products)", "value": r3["value"],
+                         "ms_per_step": r3["ms_per_step"], "steps": 5, "kernel_tflops_or_gbs": rf3["achieved"],
+                         "kernel_avg_launch_ms": rf3["avg_launch_ms"], "time_shares": rf3["time_shares"],
+                         "max_norm_err": bench.max_over_ranks(e3) if e3 is not None else None})
+            del w3
+        except Exception as ex:
+            also.append({"workload": "gemm16k", "mode": "tf32bf16", "failed": str(ex)[:200]})
+        torch.cuda.empty_cache(); ctx.release_cached()
 
     # ---- CPU baseline (rank 0, N = 1 only) ------------------------------------------------------------
     cpu = None
@@ -834,7 +855,8 @@ def main():
             "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
             "scaling": wl["scaling"], "vs_baseline": None,
             "dtype": {"3xtf32": "f32 (3xTF32 tensor-core split, fp32 accumulate)", "strict": "f32 (3xTF32, K chunks added in IEEE fp32)",
-                      "1xtf32": "tf32", "f16": "f16 (fp32 accumulate)"}[args.mode],
+                      "1xtf32": "tf32", "f16": "f16 (fp32 accumulate)",
+                      "tf32bf16": "f32 (TF32 hi*hi + two bf16 cross products, K chunks added in IEEE fp32)"}[args.mode],
             "data": "synthetic (seeded uniform [-1,1), generated on device)",
             "config": config_for(args, wl, args.workload, world),
             "max_norm_err": err, "max_norm_err_basis": "sampled results against an fp64 product of the same operands, / (K max|a| max|b|)",

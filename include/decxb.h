@@ -65,7 +65,15 @@ typedef enum decxb_gemm_mode {
      * biases long sums of same-sign terms (the reference test program's all-positive matrices
      * reach 2.9e-6 of K max|a| max|b| at K = 2048); chunking brings such inputs to 3.3e-7.
      * Accepted by every fp32 GEMM and convolution entry point. */
-    DECXB_GEMM_3XTF32_STRICT = 2
+    DECXB_GEMM_3XTF32_STRICT = 2,
+    /* Opt-in, beyond the reference's arithmetic and beyond 3xTF32: the hi*hi product in TF32 and the
+     * two cross products a_lo*b and a*b_lo in bf16 on the tensor cores (bf16 runs at twice the TF32
+     * rate, so a k-block costs 8 MMA slots instead of 12), K accumulated in chunks like the strict
+     * mode.  The cross terms carry a relative error of about 2^-20 per product instead of 2^-22;
+     * rounding is to nearest, so the errors do not add up in one direction: on the seeded inputs the
+     * result stays within the 1e-6 bar with a wide margin (see the tests), adversarial inputs can
+     * come to about 2e-6.  Accepted by decxb_gemm_f32 and decxb_gemm_f32_act only. */
+    DECXB_GEMM_TF32_2XBF16 = 3
 } decxb_gemm_mode;
 
 /* Tile configuration of the GEMM kernel (0 = choose from the shape). */

@@ -55,20 +55,41 @@ def test_gemm_square_full_size_sampled_against_fma_chain(ctx, size):
     try:
         dA = torch.empty((M, K), device=DEV); dB = torch.empty((K, N), device=DEV)
         dD = torch.full((M, N), float("nan"), device=DEV)
+        torch.cuda.synchronize()                                # torch's stream and the context's are not ordered
         ctx.fill_uniform(dA, M, K, K, 1); ctx.fill_uniform(dB, K, N, N, 2)
         ctx.gemm(M, N, K, dA, K, dB, N, dD, N, mode=b.GEMM_3XTF32)
         ctx.synchronize()
         err_whole = _check_sampled(dA, dB, dD, K)
         dD.fill_(float("nan"))
+        torch.cuda.synchronize()
+        ctx.gemm(M, N, K, dA, K, dB, N, dD, N, mode=b.GEMM_TF32_2XBF16)     # opt-in: bf16 cross products
+        ctx.synchronize()
+        err_bf16 = _check_sampled(dA, dB, dD, K)
+        assert err_bf16 <= TOL_3X, err_bf16
+        dD.fill_(float("nan"))
+        torch.cuda.synchronize()
         ctx.gemm(M, N, K, dA, K, dB, N, dD, N)                  # default mode: chunked accumulation
         ctx.synchronize()
         err_default = _check_sampled(dA, dB, dD, K)
-        print(f"\n{size}^3: default mode {err_default:.3e}, whole-K mode {err_whole:.3e} of K max|a| max|b|")
+        print(f"\n{size}^3: default mode {err_default:.3e}, whole-K mode {err_whole:.3e}, TF32 + 2 x bf16 mode {err_bf16:.3e} of K max|a| max|b|")
         # The default mode holds the bar at every K.  The opt-in whole-K mode leaves all of K to the tensor
         # core's accumulator, which rounds toward zero: its error grows with K (1.2e-6 measured at K = 16384),
         # so it is held to the looser bound its documentation states.
         assert err_default <= TOL_3X
         assert err_whole <= 5e-6
+        # size-independent properties on the WHOLE result: scaling B by 2 scales every output by exactly 2 (binary
+        # floating point), and the row sums of D equal A times the row sums of B (checked in fp64, all rows)
+        if size == 16384:
+            dB2 = dB * 2.0
+            dD2 = torch.empty_like(dD)
+            ctx.gemm(M, N, K, dA, K, dB2, N, dD2, N)
+            ctx.synchronize()
+            assert torch.equal(dD2, dD * 2.0)
+            del dB2, dD2
+        want = dA.double() @ dB.double().sum(dim=1)
+        got = dD.double().sum(dim=1)
+        assert float((got - want).abs().max()) / (float(K) * N) <= 1e-7
+        del want, got
         if size == 32768:
             world = 8
             for rank in (0, 5):
@@ -100,6 +121,7 @@ def test_conv_config4_full_batch(ctx):
         dF = torch.zeros((F, kH, kwp, dp), device=DEV)
         dF[:, :, :kW, :] = tmpF
         dO = torch.full((nb, g.out_h, g.eq_w, g.Np), float("nan"), device=DEV)
+        torch.cuda.synchronize()
         ctx.conv2_im2col(dS, W, H, C, dF, kW, kH, F, dO, flag=1, batch=nb, algo=b.CONV_IMPLICIT)
         ctx.synchronize()
         assert not torch.isnan(dO).any()
@@ -117,6 +139,7 @@ def test_conv_config4_full_batch(ctx):
             ctx.synchronize()
             assert torch.equal(one, dO[i]), f"image {i}: batched and single-image results differ"
         dE = torch.full_like(dO, float("nan"))
+        torch.cuda.synchronize()
         ctx.conv2_im2col(dS, W, H, C, dF, kW, kH, F, dE, flag=1, batch=nb, algo=b.CONV_EXPLICIT)
         ctx.synchronize()
         assert float((dE - dO).abs().max()) / Kc <= TOL_3X

@@ -411,6 +411,46 @@ def test_wave_alignment_does_not_change_results(ctx, mode):
     assert o.norm_err(outs[0][rows].cpu().numpy(), R, K, 1.0, 1.0) <= (TOL_3X if mode != b.GEMM_1XTF32 else 2e-3)
 
 
+@pytest.mark.parametrize("tile", [b.TILE_AUTO, b.TILE_1CTA_128x128, b.TILE_2CTA_256x256])
+@pytest.mark.parametrize("shape", [(128, 128, 32), (256, 256, 256), (257, 129, 33), (300, 520, 777), (1024, 512, 2048), (64, 2100, 1000)])
+def test_gemm_tf32_plus_two_bf16_cross_products(ctx, shape, tile):
+    """The opt-in mode DECXB_GEMM_TF32_2XBF16 (hi*hi in TF32, a_lo*b and a*b_lo in bf16, K in chunks) against the
+    fma chain on the seeded inputs: inside the 1e-6 bar, with and without an addend, nothing written outside D."""
+    M, N, K = shape
+    A = o.fill_uniform(M * K, 1).reshape(M, K); B = o.fill_uniform(K * N, 2).reshape(K, N)
+    Cin = o.fill_uniform(M * N, 3).reshape(M, N)
+    R = o.gemm_fmaf(A, B)
+    assert o.norm_err(run_gemm(ctx, A, B, mode=b.GEMM_TF32_2XBF16, tile=tile), R, K, 1.0, 1.0) <= TOL_3X
+    ldd = N + 5
+    dD = torch.full((M, ldd), float("nan"), device=DEV)
+    torch.cuda.synchronize()
+    ctx.gemm(M, N, K, dev(A), K, dev(B), N, dD, ldd, Cin=dev(Cin), ldc=N, mode=b.GEMM_TF32_2XBF16, tile=tile)
+    ctx.synchronize()
+    X = dD.cpu().numpy()
+    assert np.isnan(X[:, N:]).all()
+    assert o.norm_err(X[:, :N], o.gemm_fmaf(A, B, Cin), K, 1.0, 1.0) <= TOL_3X
+
+
+def test_gemm_tf32_plus_two_bf16_on_same_sign_data_and_refusals(ctx):
+    """All-positive operands (the reference test program's known-answer matrices, test/test/CUDA_GEMM/CUDA_GEMM.cpp:24-42,
+    at 1024^3): the bf16 roundings of the cross terms are to nearest and do not add up in one direction.  The entries
+    that do not take the mode refuse it."""
+    n = 1024
+    A = np.tile((0.1 * np.arange(n, dtype=np.float32))[None, :], (n, 1)).astype(np.float32)
+    B = np.tile((0.1 * np.arange(n, dtype=np.float32))[:, None], (1, n)).astype(np.float32)
+    X = run_gemm(ctx, A, B, mode=b.GEMM_TF32_2XBF16)
+    R = A.astype(np.float64) @ B.astype(np.float64)
+    err = np.abs(X - R).max() / (n * A.max() * B.max())
+    assert err <= 1e-6, err
+    t = torch.zeros(64 * 64, device=DEV)
+    with pytest.raises(b.DecxbError) as e:
+        ctx.gemm_nt(64, 64, 64, t, 64, t, 64, t, 64, mode=b.GEMM_TF32_2XBF16)
+    assert e.value.status == 11
+    with pytest.raises(b.DecxbError) as e:
+        ctx.gemm_batched(2, 32, 32, 32, t, 32, 1024, t, 32, 1024, t, 32, 1024, mode=b.GEMM_TF32_2XBF16)
+    assert e.value.status == 11
+
+
 def test_gemm_argument_errors(ctx):
     t = torch.zeros(64, device=DEV)
     with pytest.raises(b.DecxbError) as e:
