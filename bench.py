@@ -48,9 +48,10 @@ ALSO = [("gemm16k", 5), ("cfg2", 40), ("cfg4", 8), ("cfg3", 60), ("cfg1", 60)]  
 
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel, from the ncu captures
 # summarised under profiles/; the per-flop figure below is scaled to a launch by the launch's flops
-NCU_TRAFFIC_BYTES = {("cfg2", "3xtf32", "gemm"): 727.8e6, ("cfg2", "strict", "gemm"): 731.1e6,
+NCU_TRAFFIC_BYTES = {("cfg2", "3xtf32", "gemm"): 727.8e6, ("cfg2", "strict", "gemm"): 737.8e6,
                      ("cfg3", "3xtf32", "pack"): 70.7e6, ("cfg3", "strict", "pack"): 70.7e6,
-                     ("cfg4", "strict", "gemm"): 2594e6, ("cfg4", "3xtf32", "gemm"): 2515e6}
+                     ("cfg4", "strict", "gemm"): 2530e6, ("cfg4", "3xtf32", "gemm"): 2515e6,
+                     ("cfg2", "tf32bf16", "gemm"): 738.0e6}
 # DRAM bytes per algorithmic flop of the 256 x 256-tile GEMM with the block pairs aligned, from the single-pass capture at
 # 16384^3 in profiles/gemm_tf32_kernel_16384.md (35.44 GB read + 1.10 GB written per 2 * 16384^3 flop).  A wave of 74
 # tiles reads 17.25 operand panels whatever K and N are, so the traffic of a larger product grows with its flops.
