@@ -350,6 +350,31 @@ class Context:
                                                      kW, kH, N, _ptr(dst), batch, src_stride, dst_stride))
 
 
+def _order_after_torch(fn):
+    """Device-resident entries called WITHOUT an explicit stream run on the context's own stream, which is not ordered
+    with torch's streams: if any argument is a torch CUDA tensor, wait for torch's current stream first, so that a
+    fill or copy torch has queued (a NaN sentinel, an upload) is complete before the library touches the tensor."""
+    import functools
+
+    @functools.wraps(fn)
+    def wrapper(self, *args, **kwargs):
+        if kwargs.get("stream") is None:
+            for a in list(args) + list(kwargs.values()):
+                if getattr(a, "is_cuda", False):
+                    import torch
+
+                    torch.cuda.current_stream(a.device).synchronize()
+                    break
+        return fn(self, *args, **kwargs)
+    return wrapper
+
+
+for _name in ("fill_uniform", "gemm", "gemm_act", "gemm_nt", "gemm_f16", "gemm_batched", "prepare_b", "gemm_prepared",
+              "im2col_pack", "conv2_im2col", "conv2_im2col_act", "conv2_im2col_prepared", "conv_prepare_filters",
+              "gemm_rowshard", "conv2_im2col_batchshard"):
+    setattr(Context, _name, _order_after_torch(getattr(Context, _name)))
+
+
 class Comm:
     """A communicator over NCCL for gathering the blocks of a sharded result (decxb_comm_*).
     Rank 0 makes the id with Comm.unique_id() and hands the 128 bytes to the other ranks."""
@@ -382,9 +407,17 @@ class Comm:
         self._chk(self.L.decxb_comm_synchronize(self.h))
 
     def allgather_blocks(self, base, unit_bytes: int, total_units: int, stream=None):
+        if stream is None and getattr(base, "is_cuda", False):
+            import torch
+
+            torch.cuda.current_stream(base.device).synchronize()
         self._chk(self.L.decxb_comm_allgather_blocks(self.h, _ptr(base), unit_bytes, total_units, stream))
 
     def gemm_rowshard_gather(self, M, N, K, A_rows, lda, B, ldb, D_full, groups=4, mode=GEMM_DEFAULT, tile=TILE_AUTO, stream=None):
+        if stream is None and getattr(D_full, "is_cuda", False):
+            import torch
+
+            torch.cuda.current_stream(D_full.device).synchronize()
         self._chk(self.L.decxb_gemm_f32_rowshard_gather(self.ctx.h, self.h, mode, tile, M, N, K, _ptr(A_rows), lda, _ptr(B), ldb,
                                                         _ptr(D_full), groups, stream))
 
