@@ -114,6 +114,7 @@ SIGNATURES = {
     "decxb_comm_synchronize": (_i, [_vp]),
     "decxb_comm_allgather_blocks": (_i, [_vp, _vp, _sz, _i64, _vp]),
     "decxb_gemm_f32_rowshard_gather": (_i, [_vp, _vp, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i, _vp]),
+    "decxb_gemm_f32_rowshard_host": (_i, [_vp, _vp, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64]),
     "decxb_comm_selftest_handshake": (_i, [C.c_char_p, _i, _i, _vp, _i, C.c_char_p, _sz]),
     "decxb_probe_tensor_peak": (_i, [_vp, _i, C.c_double, C.POINTER(TensorProbe)]),
     "decxb_bounds_build": (_i, []),
@@ -420,6 +421,11 @@ class Comm:
             torch.cuda.current_stream(D_full.device).synchronize()
         self._chk(self.L.decxb_gemm_f32_rowshard_gather(self.ctx.h, self.h, mode, tile, M, N, K, _ptr(A_rows), lda, _ptr(B), ldb,
                                                         _ptr(D_full), groups, stream))
+
+    def gemm_rowshard_host(self, M, N, K, hA_rows, lda, hB, ldb, hD_rows, ldd, mode=GEMM_DEFAULT, tile=TILE_AUTO):
+        """Host-resident operands: this rank's rows of D; B is uploaded in shares and all-gathered on the device."""
+        self._chk(self.L.decxb_gemm_f32_rowshard_host(self.ctx.h, self.h, mode, tile, M, N, K, _ptr(hA_rows), lda, _ptr(hB), ldb,
+                                                      _ptr(hD_rows), ldd))
 
     def close(self):
         if getattr(self, "h", None):

@@ -659,6 +659,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="skip the other BASELINE configurations")
     ap.add_argument("--no-probe", action="store_true", help="skip the tensor-ceiling probes")
+    ap.add_argument("--no-host-gather", action="store_true",
+                    help="N > 1: every rank uploads the whole B in the host-resident leg instead of a share that the ranks all-gather")
     ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the host-resident leg (default min(steps, 3) for the large workloads)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -692,7 +694,28 @@ def main():
     err = bench.check(w)
     err = bench.max_over_ranks(err) if err is not None else None
 
+    # ---- the NCCL layer (N > 1): B's shares in the host-resident leg, the result blocks after it ---------
+    comm = None
+    if world > 1 and wl["scaling"] == "strong" and not (args.no_gather and args.no_host_gather):
+        if args.comm_ctas > 0:
+            os.environ["DECXB_COMM_MAX_CTAS"] = str(args.comm_ctas)
+        uid = [bench.b.Comm.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        comm = bench.b.Comm(ctx, world, rank, uid[0], timeout_ms=120000)
+
     # ---- host-resident leg (e2e) ---------------------------------------------------------------------
+    e2e_how = "decxb_gemm_f32_host / decxb_conv2_im2col_f32_host per rank on its shard: every rank uploads all of the shared operand"
+    if comm is not None and wl["kind"] == "gemm" and args.mode != "f16" and not args.no_host_gather:
+        hA, hB, hD = w["host"]
+        M, N, K = wl["M"], wl["N"], wl["K"]
+        mode_h = {"3xtf32": bench.b.GEMM_3XTF32, "1xtf32": bench.b.GEMM_1XTF32, "strict": bench.b.GEMM_3XTF32_STRICT,
+                  "tf32bf16": bench.b.GEMM_3XTF32_STRICT}[args.mode]
+        w["step_host"] = lambda: comm.gemm_rowshard_host(M, N, K, hA.data_ptr(), K, hB.data_ptr(), N, hD.data_ptr(), N,
+                                                         mode=mode_h, tile=args.tile)
+        k0, k1 = bench.b.shard_range(K, world, rank)
+        w["h2d"] = (w["M_rank"] * K + (k1 - k0) * N) * 4
+        e2e_how = ("decxb_gemm_f32_rowshard_host: a rank uploads its rows of A and its 1/N of B's rows, the ranks all-gather B "
+                   "on the device (NCCL over NVLink), then each multiplies its rows and sends them home")
     e2e_steps = args.e2e_steps or (min(args.steps, 3) if big else min(args.steps, 10))
     for _ in range(1 if big else 2):
         w["step_host"]()
@@ -704,18 +727,20 @@ def main():
     t_e2e = bench.max_over_ranks(time.perf_counter() - t0)
     e2e_val = res["total_flops"] * e2e_steps / t_e2e / 1e12
     h2d, d2h = w["h2d"], w["d2h"]
+    e2e_err = None
+    if "rowshard_host" in e2e_how:
+        # the rows that came home equal the rows the device-resident leg left in HBM (same mode and shapes: bit for bit)
+        hD = w["host"][2]
+        if args.mode != "tf32bf16" and w["M_rank"] > 0:
+            same = all(torch.equal(hD[sl].to(bench.dev), w["dD"][sl]) for sl in (slice(0, 64), slice(-64, None)))
+            e2e_err = bench.max_over_ranks(0.0 if same else 1.0)
     w.pop("host", None); w.pop("step_host", None)
 
     # ---- gathering the result blocks over NCCL (N > 1): after the step, and overlapped with it ------------
     gather = None
-    if world > 1 and not args.no_gather and wl["scaling"] == "strong" and "full" in w:
+    if comm is not None and not args.no_gather and "full" in w:
         from backup_1_b200 import shard
 
-        if args.comm_ctas > 0:
-            os.environ["DECXB_COMM_MAX_CTAS"] = str(args.comm_ctas)
-        uid = [bench.b.Comm.unique_id() if rank == 0 else None]
-        dist.broadcast_object_list(uid, src=0)
-        comm = bench.b.Comm(ctx, world, rank, uid[0], timeout_ms=120000)
         full = w["full"]
         total_units = wl["M"] if wl["kind"] == "gemm" else wl["batch"]
         unit_bytes = full[0].numel() * 4
@@ -761,8 +786,9 @@ def main():
             gather["step_with_overlapped_gather_ms"] = best[0]
             gather["how_overlapped"] = ("decxb_gemm_f32_rowshard_gather: the rank's rows in row-panel groups, each group sent to the peers "
                                         "(NCCL send/receive on a side stream) while the next is multiplied")
-        comm.close()
         full = None
+    if comm is not None:
+        comm.close()
     per_rank_ms = bench.per_rank(res["ms_rank_per_step"])
     per_rank_mhz = bench.per_rank(res["clocks"]["sm_mhz"] if res["clocks"] else None)
 
@@ -860,7 +886,8 @@ def main():
             "max_norm_err": err, "max_norm_err_basis": "sampled results against an fp64 product of the same operands, / (K max|a| max|b|)",
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "steps": e2e_steps, "ms_per_step": t_e2e / e2e_steps * 1e3},
+                    "steps": e2e_steps, "ms_per_step": t_e2e / e2e_steps * 1e3, "how": e2e_how,
+                    **({"rows_differing_from_device_leg": e2e_err} if e2e_err is not None else {})},
             "ms_per_step_prepared_weights": ms_prepared[0] if ms_prepared else None,
             "ms_per_step_plain_alternating": ms_prepared[1] if ms_prepared else None,
             "prepared_weights_note": ("the same step with B / the filter bank split and laid out once outside the timed region "

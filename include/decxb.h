@@ -476,6 +476,17 @@ DECXB_API int decxb_gemm_f32_rowshard_gather(decxb_ctx* ctx, decxb_comm* comm, i
                                              int64_t M, int64_t N, int64_t K,
                                              const float* A_rows, int64_t lda, const float* B, int64_t ldb,
                                              float* D_full, int groups, void* stream);
+/* Host-resident operands on several GPUs: this rank's rows of D = A * B, with hA_rows / hD_rows pointing at the
+ * rank's first row in host memory and hB at the whole B (every rank can read it; pinned memory makes the copies fast).
+ * A rank uploads only its own 1/world of B's rows and the ranks all-gather B on the device over NVLink, because the
+ * host's copy bandwidth is shared by all ranks of a box and NVLink is not; the rank's rows of A go up in row blocks
+ * that overlap the arithmetic and the way back of the result.  Blocks until hD_rows is complete (bounded by the
+ * communicator's time limit).  The single-GPU counterpart in the reference is de::cuda::GEMM on Matrix
+ * (srcs/GEMM/CUDA/large_squares/GEMM.h:56-131); the sharding has none. */
+DECXB_API int decxb_gemm_f32_rowshard_host(decxb_ctx* ctx, decxb_comm* comm, int mode, int tile,
+                                           int64_t M, int64_t N, int64_t K,
+                                           const float* hA_rows, int64_t lda, const float* hB, int64_t ldb,
+                                           float* hD_rows, int64_t ldd);
 /* Failure-detection self-test on the host: the joining half of decxb_comm_init (load the library at
  * nccl_path, non-blocking init, bounded poll, abort on expiry) with no CUDA call, so that a rank
  * which never arrives can be played by a stand-in library on a machine without a GPU. */

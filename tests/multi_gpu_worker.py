@@ -57,6 +57,23 @@ def main():
                 # panel groups change the tile schedule of a rank's rows, not the arithmetic of an output
                 assert not torch.isnan(full).any()
                 assert torch.equal(full, want), f"rank {rank}: gathered product differs (M={M}, groups={groups})"
+        # host-resident operands: a rank uploads its share of B, the ranks all-gather it, the rank's rows come home
+        import numpy as np
+        for (M, N, K) in [(4099, 520, 300), (8192, 1024, 512), (5, 64, 3)]:
+            A = torch.empty((M, K), device=dev); Bm = torch.empty((K, N), device=dev)
+            ctx.fill_uniform(A, M, K, K, 3); ctx.fill_uniform(Bm, K, N, N, 4)
+            f, l = b.shard_range(M, world, rank)
+            want = torch.empty((max(l - f, 1), N), device=dev)
+            if l > f:
+                ctx.gemm_rowshard(world, rank, M, N, K, A[f:], K, Bm, N, want, N)
+            ctx.synchronize()
+            hA = np.ascontiguousarray(A.cpu().numpy()); hB = np.ascontiguousarray(Bm.cpu().numpy())
+            hD = np.full((M + 1, N + 3), np.nan, dtype=np.float32)            # a row pitch wider than the rows, one spare row
+            rows_a = hA[f:] if l > f else hA
+            comm.gemm_rowshard_host(M, N, K, rows_a.ctypes.data, K, hB.ctypes.data, N, hD[f:].ctypes.data, N + 3)
+            if l > f:
+                assert np.array_equal(hD[f:l, :N], want[:l - f].cpu().numpy()), f"rank {rank}: host-resident rows differ (M={M})"
+            assert np.isnan(hD[l:]).all() and np.isnan(hD[:f]).all() and np.isnan(hD[:, N:]).all(), "wrote outside the rank's rows"
         # blocks of unequal size (images of a sharded convolution result): 7 units of 3000 floats
         units, ub = 7, 3000
         base = torch.full((units, ub), float("nan"), device=dev)
