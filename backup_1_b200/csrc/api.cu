@@ -329,9 +329,19 @@ extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M
                                    const float* hA, int64_t lda, const float* hB, int64_t ldb,
                                    const float* hC, int64_t ldc, float* hD, int64_t ldd)
 {
+    return decxb_gemm_host_pipeline(ctx, mode, tile, M, N, K, hA, lda, hB, ldb, hC, ldc, hD, ldd, nullptr);
+}
+
+/* The host-resident product.  With `share` (several ranks, every one of which can read the whole B in host memory)
+ * a column block of B is kept contiguous on the device, this rank uploads only rows [k_first, k_last) of it and
+ * share->gather completes it from the peers; M may then be 0 (a rank without rows still contributes its rows of B). */
+int decxb_gemm_host_pipeline(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_t K,
+                             const float* hA, int64_t lda, const float* hB, int64_t ldb,
+                             const float* hC, int64_t ldc, float* hD, int64_t ldd, const decxb_b_share* share)
+{
     int rc = decxb_bind(ctx);
     if (rc) return rc;
-    if (M <= 0 || N <= 0 || K <= 0) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "gemm dims must be positive");
+    if (M < 0 || (M == 0 && !share) || N <= 0 || K <= 0) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "gemm dims must be positive");
     if (!hA || !hB || !hD) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null operand");
     if (lda < K || ldb < N || ldd < N || (hC && ldc < N))
         return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
@@ -352,10 +362,11 @@ extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M
     const bool x3 = mode == DECXB_GEMM_3XTF32 || strict;
     const int64_t Kp = decxb_split_pitch(K), Np = decxb_ceil_to(N, 4);
     float *dA, *dB, *dC = nullptr, *dD, *b_hi = nullptr, *b_lo = nullptr;
-    if ((rc = scratch.get((size_t)M * Kp * 4, (void**)&dA))) return rc;
+    const int64_t Ma = M > 0 ? M : 1;
+    if ((rc = scratch.get((size_t)Ma * Kp * 4, (void**)&dA))) return rc;
     if ((rc = scratch.get((size_t)K * Np * 4, (void**)&dB))) return rc;
-    if ((rc = scratch.get((size_t)M * Np * 4, (void**)&dD))) return rc;
-    if (hC && (rc = scratch.get((size_t)M * Np * 4, (void**)&dC))) return rc;
+    if ((rc = scratch.get((size_t)Ma * Np * 4, (void**)&dD))) return rc;
+    if (hC && (rc = scratch.get((size_t)Ma * Np * 4, (void**)&dC))) return rc;
     if ((rc = scratch.get((size_t)N * Kp * 4, (void**)&b_hi))) return rc;
     if (x3 && (rc = scratch.get((size_t)N * Kp * 4, (void**)&b_lo))) return rc;
     if ((rc = fence_copy_streams(ctx, evs))) return rc;
@@ -369,7 +380,11 @@ extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M
      * block takes 2 rows0 ncol K / F, uploading the block 4 K ncol / BW, equal at rows0 = 2 F / BW, about 10 000 rows
      * at 250 TFLOP/s and 50 GB/s, whatever the sizes.  (With K = 32768 the first block was the whole of A: 80 ms of
      * upload with the GPU idle.) */
-    if (rows0 > 10240) rows0 = 10240;
+    int64_t cap0 = 10240;
+    /* shares of B arrive `world` times as fast, over a host link that the ranks of the box share (about half the rate each) */
+    if (share && share->world > 1) cap0 = decxb_ceil_to(20480 / share->world, 256);
+    if (cap0 < 1024) cap0 = 1024;
+    if (rows0 > cap0) rows0 = cap0;
     if (rows0 < rows) rows0 = rows;
     if (rows0 > M) rows0 = M;
     int64_t ncol = decxb_ceil_to(decxb_ceil_div(N, 8), 256);
@@ -379,12 +394,12 @@ extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M
     auto fail = [&](int code) { drain_all_streams(ctx); return code; };
     cudaEvent_t e_a0 = evs.make();
     if (!e_a0) return decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate");
-    PIPE_TRY(cudaMemcpy2DAsync(dA, Kp * 4, hA, lda * 4, K * 4, rows0, cudaMemcpyHostToDevice, up));
-    if (hC) PIPE_TRY(cudaMemcpy2DAsync(dC, Np * 4, hC, ldc * 4, N * 4, rows0, cudaMemcpyHostToDevice, up));
+    if (rows0 > 0) PIPE_TRY(cudaMemcpy2DAsync(dA, Kp * 4, hA, lda * 4, K * 4, rows0, cudaMemcpyHostToDevice, up));
+    if (hC && rows0 > 0) PIPE_TRY(cudaMemcpy2DAsync(dC, Np * 4, hC, ldc * 4, N * 4, rows0, cudaMemcpyHostToDevice, up));
     PIPE_TRY(cudaEventRecord(e_a0, up));
     PIPE_TRY(cudaStreamWaitEvent(s, e_a0, 0));
     const float *a0_hi = dA, *a0_lo = nullptr;
-    if (x3) {
+    if (x3 && rows0 > 0) {
         float *hi = nullptr, *lo = nullptr;
         if ((rc = scratch.get((size_t)rows0 * Kp * 4, (void**)&hi)) || (rc = scratch.get((size_t)rows0 * Kp * 4, (void**)&lo))) return fail(rc);
         if ((rc = decxb_launch_split_rows(ctx, dA, rows0, K, Kp, hi, lo, Kp, rows0, s))) return fail(rc);
@@ -394,11 +409,20 @@ extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M
         const int64_t nc = N - c0 < ncol ? N - c0 : ncol;
         cudaEvent_t e_up = evs.make(), e_done = evs.make();
         if (!e_up || !e_done) return fail(decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"));
-        PIPE_TRY(cudaMemcpy2DAsync(dB + c0, Np * 4, hB + c0, ldb * 4, nc * 4, K, cudaMemcpyHostToDevice, up));
+        /* whole B: the column block in place in the K x Np array; shares: the block on its own, K rows of nc floats,
+         * so that the rows the peers send are contiguous */
+        float* blk = share ? dB + K * c0 : dB + c0;
+        const int64_t blk_ld = share ? decxb_ceil_to(nc, 4) : Np;
+        if (!share) PIPE_TRY(cudaMemcpy2DAsync(blk, blk_ld * 4, hB + c0, ldb * 4, nc * 4, K, cudaMemcpyHostToDevice, up));
+        else if (share->k_last > share->k_first)
+            PIPE_TRY(cudaMemcpy2DAsync(blk + share->k_first * blk_ld, blk_ld * 4, hB + share->k_first * ldb + c0, ldb * 4, nc * 4,
+                                       share->k_last - share->k_first, cudaMemcpyHostToDevice, up));
         PIPE_TRY(cudaEventRecord(e_up, up));
         PIPE_TRY(cudaStreamWaitEvent(s, e_up, 0));
+        if (share && (rc = share->gather(share->user, blk, (size_t)blk_ld * 4, K, s))) return fail(rc);
+        if (M == 0) continue;
         /* columns c0.. of B are rows c0.. of the prepared (K-contiguous) operand */
-        if ((rc = decxb_launch_split_transpose(ctx, dB + c0, K, nc, Np, b_hi + c0 * Kp, x3 ? b_lo + c0 * Kp : nullptr, Kp,
+        if ((rc = decxb_launch_split_transpose(ctx, blk, K, nc, blk_ld, b_hi + c0 * Kp, x3 ? b_lo + c0 * Kp : nullptr, Kp,
                                                x3 ? 0 : 1, s))) return fail(rc);
         decxb_gemm_args g = {};
         g.M = rows0; g.N = nc; g.K = K;

@@ -441,8 +441,9 @@ extern "C" int decxb_gemm_f32_rowshard_gather(decxb_ctx* ctx, decxb_comm* c, int
 
 /* Host-resident operands on several GPUs.  Every rank holds (or can read) the whole B in host memory, but the host's
  * copy bandwidth is shared by all ranks of the box (measured: 55 GB/s for one rank alone, 8 to 36 GB/s per rank when
- * eight copy at once), while NVLink is not: so a rank uploads only its own 1/world of B's rows and the ranks
- * all-gather B on the device, then each multiplies its rows of A (uploaded in row blocks) and sends its rows of D home. */
+ * eight copy at once), while NVLink is not: so a rank uploads only its own 1/world of the rows of each column block
+ * of B and the ranks all-gather the block on the device; the rest is the single-GPU pipeline (a first row block of A
+ * multiplied with the column blocks as they complete, then the other row blocks against the whole prepared B). */
 extern "C" int decxb_gemm_f32_rowshard_host(decxb_ctx* ctx, decxb_comm* c, int mode, int tile, int64_t M, int64_t N, int64_t K,
                                             const float* hA_rows, int64_t lda, const float* hB, int64_t ldb,
                                             float* hD_rows, int64_t ldd)
@@ -454,70 +455,21 @@ extern "C" int decxb_gemm_f32_rowshard_host(decxb_ctx* ctx, decxb_comm* c, int m
     if (lda < K || ldb < N || ldd < N) return comm_fail(c, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
     std::lock_guard<std::mutex> lock(c->mtx);
     if ((rc = decxb_bind(ctx))) return rc;
-    cudaStream_t s = ctx->stream, up = ctx->copy_stream[0], down = ctx->copy_stream[1];
-    int64_t f = 0, l = 0, kf = 0, kl = 0;
+    int64_t f = 0, l = 0;
     decxb_shard_range(M, c->world, c->rank, &f, &l);
-    decxb_shard_range(K, c->world, c->rank, &kf, &kl);
-    const int64_t rows = l - f;
-    float *dB = nullptr, *dA = nullptr, *dD = nullptr;
-    decxb_prepared_b* pb = nullptr;
-    std::vector<cudaEvent_t> evs;
-    auto event = [&]() -> cudaEvent_t {
-        cudaEvent_t e = nullptr;
-        if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); return nullptr; }
-        evs.push_back(e);
-        return e;
+    decxb_b_share share = {};
+    share.world = c->world;
+    decxb_shard_range(K, c->world, c->rank, &share.k_first, &share.k_last);
+    share.user = c;
+    share.gather = [](void* user, float* base, size_t unit_bytes, int64_t units, cudaStream_t s) {
+        return allgather_blocks_locked((decxb_comm*)user, base, unit_bytes, units, s);
     };
-    auto finish = [&](int code) {
-        /* whatever happened, nothing may still use the scratch or the caller's buffers when this returns */
-        cudaStreamSynchronize(up); cudaStreamSynchronize(s); cudaStreamSynchronize(down);
-        if (code == DECXB_OK) code = comm_drain(c); else cudaStreamSynchronize(c->stream);
+    rc = decxb_gemm_host_pipeline(ctx, mode, tile, l - f, N, K, hA_rows, lda, hB, ldb, nullptr, 0, hD_rows, ldd, &share);
+    if (rc) {                                      /* the pipeline drained its own streams; the transfer stream is this layer's */
+        cudaStreamSynchronize(c->stream);
         cudaGetLastError();
-        if (pb) decxb_gemm_release_b(ctx, pb, s);
-        if (dB) decxb_free_on_stream(ctx, dB, s);
-        if (dA) decxb_free_on_stream(ctx, dA, s);
-        if (dD) decxb_free_on_stream(ctx, dD, s);
-        for (cudaEvent_t e : evs) cudaEventDestroy(e);
-        return code == DECXB_OK ? decxb_check_dev_status(ctx) : code;
-    };
-#define HOST_TRY(expr)                                                                                  \
-    do {                                                                                               \
-        cudaError_t _e = (expr);                                                                       \
-        if (_e != cudaSuccess) return finish(comm_fail(c, DECXB_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(_e))); \
-    } while (0)
-    if ((rc = decxb_malloc_on_stream(ctx, (size_t)K * N * 4, (void**)&dB, s))) return finish(rc);
-    if (rows > 0) {
-        if ((rc = decxb_malloc_on_stream(ctx, (size_t)rows * K * 4, (void**)&dA, s))) return finish(rc);
-        if ((rc = decxb_malloc_on_stream(ctx, (size_t)rows * N * 4, (void**)&dD, s))) return finish(rc);
+        if (c->last_error.empty()) c->last_error = decxb_last_error(ctx);
+        return rc;
     }
-    cudaEvent_t e0 = event(), e_b = event();
-    if (!e0 || !e_b) return finish(comm_fail(c, DECXB_ERR_CUDA, "cudaEventCreate"));
-    HOST_TRY(cudaEventRecord(e0, s));
-    HOST_TRY(cudaStreamWaitEvent(up, e0, 0));
-    HOST_TRY(cudaStreamWaitEvent(down, e0, 0));
-    /* this rank's rows of B, then every rank's over NVLink */
-    if (kl > kf) HOST_TRY(cudaMemcpy2DAsync(dB + kf * N, (size_t)N * 4, hB + kf * ldb, (size_t)ldb * 4, (size_t)N * 4, (size_t)(kl - kf), cudaMemcpyHostToDevice, up));
-    HOST_TRY(cudaEventRecord(e_b, up));
-    HOST_TRY(cudaStreamWaitEvent(s, e_b, 0));
-    if ((rc = allgather_blocks_locked(c, dB, (size_t)N * 4, K, s))) return finish(rc);
-    if (rows > 0) {
-        if ((rc = decxb_gemm_prepare_b(ctx, mode, K, N, dB, N, s, &pb))) return finish(rc);
-        /* row blocks of about a quarter of the rank's rows: upload, multiply, download overlap */
-        int64_t rb = decxb_ceil_to(decxb_ceil_div(rows, 4), 256);
-        if (rb < 512) rb = 512;
-        for (int64_t r0 = 0; r0 < rows; r0 += rb) {
-            const int64_t nr = rows - r0 < rb ? rows - r0 : rb;
-            cudaEvent_t e_up = event(), e_done = event();
-            if (!e_up || !e_done) return finish(comm_fail(c, DECXB_ERR_CUDA, "cudaEventCreate"));
-            HOST_TRY(cudaMemcpy2DAsync(dA + r0 * K, (size_t)K * 4, hA_rows + r0 * lda, (size_t)lda * 4, (size_t)K * 4, (size_t)nr, cudaMemcpyHostToDevice, up));
-            HOST_TRY(cudaEventRecord(e_up, up));
-            HOST_TRY(cudaStreamWaitEvent(s, e_up, 0));
-            if ((rc = decxb_gemm_rows_prepared_b(ctx, mode, tile, nr, N, K, dA + r0 * K, K, pb, nullptr, 0, dD + r0 * N, N, s))) return finish(rc);
-            HOST_TRY(cudaEventRecord(e_done, s));
-            HOST_TRY(cudaStreamWaitEvent(down, e_done, 0));
-            HOST_TRY(cudaMemcpy2DAsync(hD_rows + r0 * ldd, (size_t)ldd * 4, dD + r0 * N, (size_t)N * 4, (size_t)N * 4, (size_t)nr, cudaMemcpyDeviceToHost, down));
-        }
-    }
-    return finish(DECXB_OK);
-#undef HOST_TRY
+    return comm_drain(c);
 }

@@ -253,6 +253,19 @@ struct decxb_conv_gemm_args {
 int decxb_launch_conv_implicit(decxb_ctx* ctx, const decxb_conv_gemm_args& a, cudaStream_t s);
 
 /* Rows of D = A * B (+C) (+bias, activation) with B prepared by decxb_gemm_prepare_b. */
+/* B of a host-resident product arriving in shares (several ranks): this rank uploads rows [k_first, k_last) of each
+ * column block; `gather` (ordered after `s`'s earlier work, and `s` waits for it) completes the block from the peers:
+ * `units` rows of unit_bytes each, partitioned over the ranks by decxb_shard_range. */
+struct decxb_b_share {
+    int world;
+    int64_t k_first, k_last;
+    int (*gather)(void* user, float* base, size_t unit_bytes, int64_t units, cudaStream_t s);
+    void* user;
+};
+int decxb_gemm_host_pipeline(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_t K,
+                             const float* hA, int64_t lda, const float* hB, int64_t ldb,
+                             const float* hC, int64_t ldc, float* hD, int64_t ldd, const decxb_b_share* share);
+
 int decxb_gemm_rows_prepared_b(decxb_ctx* ctx, int mode, int tile, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
                                const decxb_prepared_b* pb, const float* C, int64_t ldc, float* D, int64_t ldd, cudaStream_t s,
                                const float* bias = nullptr, int act = DECXB_ACT_NONE);

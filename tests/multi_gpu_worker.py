@@ -59,7 +59,8 @@ def main():
                 assert torch.equal(full, want), f"rank {rank}: gathered product differs (M={M}, groups={groups})"
         # host-resident operands: a rank uploads its share of B, the ranks all-gather it, the rank's rows come home
         import numpy as np
-        for (M, N, K) in [(4099, 520, 300), (8192, 1024, 512), (5, 64, 3)]:
+        # (several column blocks of B, the last one ragged; more rows than the first row block takes; fewer rows than ranks)
+        for (M, N, K) in [(4099, 520, 300), (300, 3001, 70), (24000, 2304, 64), (5, 64, 3)]:
             A = torch.empty((M, K), device=dev); Bm = torch.empty((K, N), device=dev)
             ctx.fill_uniform(A, M, K, K, 3); ctx.fill_uniform(Bm, K, N, N, 4)
             f, l = b.shard_range(M, world, rank)
