@@ -468,7 +468,7 @@ extern "C" int decxb_gemm_f32_rowshard_host(decxb_ctx* ctx, decxb_comm* c, int m
     if (rc) {                                      /* the pipeline drained its own streams; the transfer stream is this layer's */
         cudaStreamSynchronize(c->stream);
         cudaGetLastError();
-        if (c->last_error.empty()) c->last_error = decxb_last_error(ctx);
+        c->last_error = decxb_last_error(ctx);
         return rc;
     }
     return comm_drain(c);

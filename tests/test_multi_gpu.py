@@ -39,6 +39,40 @@ def test_single_rank_communicator_runs_the_panel_groups(ctx):
         comm.close()
 
 
+def test_single_rank_host_resident_product_with_b_in_shares(ctx):
+    """world = 1: the host-resident sharded entry uploads 'its share' (all) of each column block of B, gathers it
+    (nothing travels) and returns the bits of the device-resident product; a CUDA call that fails in the middle
+    (injected on the host) is reported, and the same call then succeeds."""
+    comm = b.Comm(ctx, 1, 0, b.Comm.unique_id(), timeout_ms=20000)
+    try:
+        for (M, N, K) in [(1500, 264, 200), (700, 3001, 70), (11000, 2304, 36)]:
+            A = o.fill_uniform(M * K, 1).reshape(M, K); B = o.fill_uniform(K * N, 2).reshape(K, N)
+            dA, dB = torch.from_numpy(A).to("cuda:0"), torch.from_numpy(B).to("cuda:0")
+            want = torch.empty((M, N), device="cuda:0")
+            ctx.gemm(M, N, K, dA, K, dB, N, want, N)
+            ctx.synchronize()
+            hD = np.full((M, N + 5), np.nan, dtype=np.float32)
+            comm.gemm_rowshard_host(M, N, K, A, K, B, N, hD, N + 5)
+            assert np.array_equal(hD[:, :N], want.cpu().numpy())
+            assert np.isnan(hD[:, N:]).all()
+        M, N, K = 1500, 264, 200
+        A = o.fill_uniform(M * K, 1).reshape(M, K); B = o.fill_uniform(K * N, 2).reshape(K, N)
+        hD = np.full((M, N), np.nan, dtype=np.float32)
+        good = hD.copy()
+        comm.gemm_rowshard_host(M, N, K, A, K, B, N, good, N)
+        L = b.load_library()
+        for nth in (0, 3, 6):
+            assert L.decxb_inject_pipeline_error(ctx.h, nth) == 0
+            with pytest.raises(b.DecxbError):
+                comm.gemm_rowshard_host(M, N, K, A, K, B, N, hD, N)
+            L.decxb_inject_pipeline_error(ctx.h, -1)
+            hD[:] = np.nan
+            comm.gemm_rowshard_host(M, N, K, A, K, B, N, hD, N)
+            assert np.array_equal(hD, good)
+    finally:
+        comm.close()
+
+
 def test_prepared_b_gives_the_bits_of_the_plain_entry(ctx):
     M, N, K = 700, 328, 260
     A = o.fill_uniform(M * K, 1).reshape(M, K); B = o.fill_uniform(K * N, 2).reshape(K, N)
