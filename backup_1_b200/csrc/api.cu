@@ -381,8 +381,13 @@ int decxb_gemm_host_pipeline(decxb_ctx* ctx, int mode, int tile, int64_t M, int6
      * at 250 TFLOP/s and 50 GB/s, whatever the sizes.  (With K = 32768 the first block was the whole of A: 80 ms of
      * upload with the GPU idle.) */
     int64_t cap0 = 10240;
-    /* shares of B arrive `world` times as fast, over a host link that the ranks of the box share (about half the rate each) */
-    if (share && share->world > 1) cap0 = decxb_ceil_to(20480 / share->world, 256);
+    /* shares of B arrive `world` times as fast, over a host link that the ranks of the box share (measured per rank:
+     * about 0.9 of the rate of a rank alone at 2 ranks, 0.5 at 4 and 8) */
+    if (share && share->world > 1) {
+        double slow = 0.6 + 0.25 * share->world;
+        if (slow > 2.0) slow = 2.0;
+        cap0 = decxb_ceil_to((int64_t)(10240.0 * slow / share->world), 256);
+    }
     if (cap0 < 1024) cap0 = 1024;
     if (rows0 > cap0) rows0 = cap0;
     if (rows0 < rows) rows0 = rows;
