@@ -397,23 +397,13 @@ int decxb_gemm_host_pipeline(decxb_ctx* ctx, int mode, int tile, int64_t M, int6
     if (N < 2048 || ncol > N) ncol = N;
 
     auto fail = [&](int code) { drain_all_streams(ctx); return code; };
-    cudaEvent_t e_a0 = evs.make();
-    if (!e_a0) return decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate");
-    if (rows0 > 0) PIPE_TRY(cudaMemcpy2DAsync(dA, Kp * 4, hA, lda * 4, K * 4, rows0, cudaMemcpyHostToDevice, up));
-    if (hC && rows0 > 0) PIPE_TRY(cudaMemcpy2DAsync(dC, Np * 4, hC, ldc * 4, N * 4, rows0, cudaMemcpyHostToDevice, up));
-    PIPE_TRY(cudaEventRecord(e_a0, up));
-    PIPE_TRY(cudaStreamWaitEvent(s, e_a0, 0));
-    const float *a0_hi = dA, *a0_lo = nullptr;
-    if (x3 && rows0 > 0) {
-        float *hi = nullptr, *lo = nullptr;
-        if ((rc = scratch.get((size_t)rows0 * Kp * 4, (void**)&hi)) || (rc = scratch.get((size_t)rows0 * Kp * 4, (void**)&lo))) return fail(rc);
-        if ((rc = decxb_launch_split_rows(ctx, dA, rows0, K, Kp, hi, lo, Kp, rows0, s))) return fail(rc);
-        a0_hi = hi; a0_lo = lo;
-    }
-    for (int64_t c0 = 0; c0 < N; c0 += ncol) {
-        const int64_t nc = N - c0 < ncol ? N - c0 : ncol;
-        cudaEvent_t e_up = evs.make(), e_done = evs.make();
-        if (!e_up || !e_done) return fail(decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"));
+    float *a0_hi = dA, *a0_lo = nullptr;
+    if (x3 && rows0 > 0 &&
+        ((rc = scratch.get((size_t)rows0 * Kp * 4, (void**)&a0_hi)) || (rc = scratch.get((size_t)rows0 * Kp * 4, (void**)&a0_lo)))) return rc;
+    /* a column block of B: up (whole, or this rank's rows of it, completed by the peers), split and transposed */
+    auto stage_b_block = [&](int64_t c0, int64_t nc) -> int {
+        cudaEvent_t e_up = evs.make();
+        if (!e_up) return fail(decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"));
         /* whole B: the column block in place in the K x Np array; shares: the block on its own, K rows of nc floats,
          * so that the rows the peers send are contiguous */
         float* blk = share ? dB + K * c0 : dB + c0;
@@ -424,25 +414,77 @@ int decxb_gemm_host_pipeline(decxb_ctx* ctx, int mode, int tile, int64_t M, int6
                                        share->k_last - share->k_first, cudaMemcpyHostToDevice, up));
         PIPE_TRY(cudaEventRecord(e_up, up));
         PIPE_TRY(cudaStreamWaitEvent(s, e_up, 0));
-        if (share && (rc = share->gather(share->user, blk, (size_t)blk_ld * 4, K, s))) return fail(rc);
-        if (M == 0) continue;
+        int r = DECXB_OK;
+        if (share && (r = share->gather(share->user, blk, (size_t)blk_ld * 4, K, s))) return fail(r);
+        if (M == 0) return DECXB_OK;
         /* columns c0.. of B are rows c0.. of the prepared (K-contiguous) operand */
-        if ((rc = decxb_launch_split_transpose(ctx, blk, K, nc, blk_ld, b_hi + c0 * Kp, x3 ? b_lo + c0 * Kp : nullptr, Kp,
-                                               x3 ? 0 : 1, s))) return fail(rc);
+        if ((r = decxb_launch_split_transpose(ctx, blk, K, nc, blk_ld, b_hi + c0 * Kp, x3 ? b_lo + c0 * Kp : nullptr, Kp,
+                                              x3 ? 0 : 1, s))) return fail(r);
+        return DECXB_OK;
+    };
+    /* rows [r0, r0 + nr) of the first row block times a column block, and that piece of the result on its way home */
+    auto first_block_product = [&](int64_t r0, int64_t nr, int64_t c0, int64_t nc) -> int {
+        cudaEvent_t e_done = evs.make();
+        if (!e_done) return fail(decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"));
         decxb_gemm_args g = {};
-        g.M = rows0; g.N = nc; g.K = K;
-        g.a_hi = a0_hi; g.a_lo = a0_lo; g.lda = Kp;
+        g.M = nr; g.N = nc; g.K = K;
+        g.a_hi = a0_hi + r0 * Kp; g.a_lo = x3 ? a0_lo + r0 * Kp : nullptr; g.lda = Kp;
         g.b_hi = b_hi + c0 * Kp; g.b_lo = x3 ? b_lo + c0 * Kp : nullptr; g.ldb = Kp; g.b_rows = nc;
-        g.C = dC ? dC + c0 : nullptr; g.ldc = Np; g.D = dD + c0; g.ldd = Np;
+        g.C = dC ? dC + r0 * Np + c0 : nullptr; g.ldc = Np; g.D = dD + r0 * Np + c0; g.ldd = Np;
         g.tile = tile; g.chunked = strict ? 1 : 0;
-        if ((rc = decxb_launch_gemm_tn(ctx, g, s))) return fail(rc);
+        int r = decxb_launch_gemm_tn(ctx, g, s);
+        if (r) return fail(r);
         PIPE_TRY(cudaEventRecord(e_done, s));
         PIPE_TRY(cudaStreamWaitEvent(down, e_done, 0));
-        PIPE_TRY(cudaMemcpy2DAsync(hD + c0, ldd * 4, dD + c0, Np * 4, nc * 4, rows0, cudaMemcpyDeviceToHost, down));
+        PIPE_TRY(cudaMemcpy2DAsync(hD + r0 * ldd + c0, ldd * 4, dD + r0 * Np + c0, Np * 4, nc * 4, nr, cudaMemcpyDeviceToHost, down));
+        return DECXB_OK;
+    };
+    /* The first column block of B goes up first, then the first row block of A in up to four pieces: each piece is
+     * split and multiplied with that column block as it lands, so the arithmetic starts a quarter of the way into
+     * the row block's upload instead of at its end. */
+    /* the first column blocks are narrower (a quarter, then half of the regular width): less to wait for before the
+     * first product; likewise the last row blocks of the second phase, whose results nothing hides on their way home */
+    std::vector<std::pair<int64_t, int64_t>> col_blocks, row_blocks;
+    {
+        int64_t w = ncol / 4 >= 1024 && ncol % 4 == 0 ? ncol / 4 : ncol;
+        for (int64_t c0 = 0; c0 < N;) {
+            const int64_t nc = N - c0 < w ? N - c0 : w;
+            col_blocks.push_back({c0, nc});
+            c0 += nc;
+            if (w < ncol) w *= 2;
+        }
+        int64_t r0 = rows0;
+        while (r0 < M) {
+            int64_t nr = M - r0;
+            if (nr > rows) nr = rows;                                    /* regular blocks ... */
+            else if (nr >= 2048 && nr % 512 == 0) nr /= 2;               /* ... then halves of what is left, down to 1024 rows */
+            row_blocks.push_back({r0, nr});
+            r0 += nr;
+        }
+    }
+    const int64_t nc0 = col_blocks[0].second;
+    if ((rc = stage_b_block(0, nc0))) return rc;
+    int64_t piece = decxb_ceil_to(decxb_ceil_div(rows0 > 0 ? rows0 : 1, 4), 256);
+    if (piece < 512) piece = 512;
+    for (int64_t r0 = 0; r0 < rows0; r0 += piece) {
+        const int64_t nr = rows0 - r0 < piece ? rows0 - r0 : piece;
+        cudaEvent_t e_up = evs.make();
+        if (!e_up) return fail(decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"));
+        PIPE_TRY(cudaMemcpy2DAsync(dA + r0 * Kp, Kp * 4, hA + r0 * lda, lda * 4, K * 4, nr, cudaMemcpyHostToDevice, up));
+        if (hC) PIPE_TRY(cudaMemcpy2DAsync(dC + r0 * Np, Np * 4, hC + r0 * ldc, ldc * 4, N * 4, nr, cudaMemcpyHostToDevice, up));
+        PIPE_TRY(cudaEventRecord(e_up, up));
+        PIPE_TRY(cudaStreamWaitEvent(s, e_up, 0));
+        if (x3 && (rc = decxb_launch_split_rows(ctx, dA + r0 * Kp, nr, K, Kp, a0_hi + r0 * Kp, a0_lo + r0 * Kp, Kp, nr, s))) return fail(rc);
+        if ((rc = first_block_product(r0, nr, 0, nc0))) return rc;
+    }
+    for (size_t bi = 1; bi < col_blocks.size(); ++bi) {
+        const int64_t c0 = col_blocks[bi].first, nc = col_blocks[bi].second;
+        if ((rc = stage_b_block(c0, nc))) return rc;
+        if (rows0 > 0 && (rc = first_block_product(0, rows0, c0, nc))) return rc;
     }
     PreparedB pb = {b_hi, b_lo, Kp};
-    for (int64_t r0 = rows0; r0 < M; r0 += rows) {
-        const int64_t nr = M - r0 < rows ? M - r0 : rows;
+    for (const auto& rbk : row_blocks) {
+        const int64_t r0 = rbk.first, nr = rbk.second;
         cudaEvent_t e_up = evs.make(), e_done = evs.make();
         if (!e_up || !e_done) return fail(decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"));
         PIPE_TRY(cudaMemcpy2DAsync(dA + r0 * Kp, Kp * 4, hA + r0 * lda, lda * 4, K * 4, nr, cudaMemcpyHostToDevice, up));
