@@ -11,8 +11,10 @@ with N GPUs the rows of A and C are sharded over the ranks and B is replicated (
 no data-path collective; the all-gather of C is timed separately and reported beside it).
 Prints ONE JSON line on rank 0.  `value` is device-timed (CUDA events on the launch stream, max
 over ranks) with operands resident in HBM; `e2e` runs the host-resident entry point (pinned host
-buffers, H2D and D2H inside the timed region); `also` carries the other BASELINE configurations
-measured in the same process.
+buffers, H2D and D2H inside the timed region; with N GPUs on the sharded GEMM a rank uploads its
+rows of A and its 1/N of B, and the ranks all-gather B on the device: `--no-host-gather` makes every
+rank upload all of B instead); `also` carries the other BASELINE configurations measured in the
+same process.
 """
 from __future__ import annotations
 
