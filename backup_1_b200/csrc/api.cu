@@ -349,10 +349,11 @@ int decxb_gemm_host_pipeline(decxb_ctx* ctx, int mode, int tile, int64_t M, int6
         return decxb_fail(ctx, DECXB_ERR_BAD_FLAG, "gemm mode");
     /* Three streams: uploads, compute, downloads.  (The reference does the three phases one
      * after the other on one stream, GEMM.h:106-123.)
-     * Phase 1: the first row-block of A (about K rows, so that its result takes as long to
-     * download as B takes to upload) goes up, then B in column blocks; every column block is
-     * prepared and multiplied with that row-block as soon as it has landed, and its piece of
-     * the result starts its way back while the next column block is still in flight.
+     * Phase 1: a first, narrow column block of B goes up, then the first row-block of A in
+     * pieces, each multiplied with that column block as it lands, then the rest of B in column
+     * blocks; every column block is prepared and multiplied with the row-block as soon as it
+     * has landed, and its piece of the result starts its way back while the next column block
+     * is still in flight.
      * Phase 2: the remaining row-blocks of A (and C) go up, each multiplied with the whole
      * prepared B as it lands while the previous result block downloads. */
     cudaStream_t s = ctx->stream, up = ctx->copy_stream[0], down = ctx->copy_stream[1];
