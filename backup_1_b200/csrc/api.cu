@@ -332,6 +332,81 @@ extern "C" int decxb_gemm_f32_host(decxb_ctx* ctx, int mode, int tile, int64_t M
     return decxb_gemm_host_pipeline(ctx, mode, tile, M, N, K, hA, lda, hB, ldb, hC, ldc, hD, ldd, nullptr);
 }
 
+/* How the host-resident product is cut (pure host arithmetic, no CUDA call): column blocks of B in upload order, the
+ * pieces of the first row-block of A, the later row-blocks. */
+struct HostPlan {
+    int64_t rows0 = 0;                                         /* rows of the first row-block */
+    std::vector<std::pair<int64_t, int64_t>> col_blocks, pieces, row_blocks;   /* (first, count) */
+};
+
+static HostPlan host_plan(int64_t M, int64_t N, int64_t K, int world)
+{
+    HostPlan pl;
+    /* later row-blocks: about 1/8 of M, multiples of 256 rows, at least 512 */
+    int64_t rows = decxb_ceil_to(decxb_ceil_div(M, 8), 256);
+    if (rows < 512) rows = 512;
+    if (rows > M) rows = M;
+    /* first row-block: about K rows; column blocks of B: about 1/8 of N, at least 1024 columns */
+    int64_t rows0 = decxb_ceil_to(K, 256);
+    /* ... but no more rows than the GPU needs to stay busy while B comes up: multiplying rows0 rows with a column
+     * block takes 2 rows0 ncol K / F, uploading the block 4 K ncol / BW, equal at rows0 = 2 F / BW, about 10 000 rows
+     * at 250 TFLOP/s and 50 GB/s, whatever the sizes.  (With K = 32768 the first block was the whole of A: 80 ms of
+     * upload with the GPU idle.) */
+    int64_t cap0 = 10240;
+    /* shares of B arrive `world` times as fast, over a host link that the ranks of the box share (measured per rank:
+     * about 0.9 of the rate of a rank alone at 2 ranks, 0.5 at 4 and 8) */
+    if (world > 1) {
+        double slow = 0.6 + 0.25 * world;
+        if (slow > 2.0) slow = 2.0;
+        cap0 = decxb_ceil_to((int64_t)(10240.0 * slow / world), 256);
+    }
+    if (cap0 < 1024) cap0 = 1024;
+    if (rows0 > cap0) rows0 = cap0;
+    if (rows0 < rows) rows0 = rows;
+    if (rows0 > M) rows0 = M;
+    int64_t ncol = decxb_ceil_to(decxb_ceil_div(N, 8), 256);
+    if (ncol < 1024) ncol = 1024;
+    if (N < 2048 || ncol > N) ncol = N;
+    pl.rows0 = rows0;
+    /* the first column blocks are narrower (a quarter, then half of the regular width): less to wait for before the
+     * first product; likewise the last row blocks of the second phase, whose results nothing hides on their way home */
+    int64_t w = ncol / 4 >= 1024 && ncol % 4 == 0 ? ncol / 4 : ncol;
+    for (int64_t c0 = 0; c0 < N;) {
+        const int64_t nc = N - c0 < w ? N - c0 : w;
+        pl.col_blocks.push_back({c0, nc});
+        c0 += nc;
+        if (w < ncol) w *= 2;
+    }
+    /* the first row-block goes up in up to four pieces, each multiplied with the first column block as it lands */
+    int64_t piece = decxb_ceil_to(decxb_ceil_div(rows0 > 0 ? rows0 : 1, 4), 256);
+    if (piece < 512) piece = 512;
+    for (int64_t r0 = 0; r0 < rows0; r0 += piece) pl.pieces.push_back({r0, rows0 - r0 < piece ? rows0 - r0 : piece});
+    int64_t r0 = rows0;
+    while (r0 < M) {
+        int64_t nr = M - r0;
+        if (nr > rows) nr = rows;                                    /* regular blocks ... */
+        else if (nr >= 2048 && nr % 512 == 0) nr /= 2;               /* ... then halves of what is left, down to 1024 rows */
+        pl.row_blocks.push_back({r0, nr});
+        r0 += nr;
+    }
+    return pl;
+}
+
+extern "C" int decxb_gemm_host_plan(int64_t M, int64_t N, int64_t K, int world, int64_t* kind_first_count, int capacity)
+{
+    if (M < 0 || N <= 0 || K <= 0 || world < 1 || capacity < 0 || (capacity > 0 && !kind_first_count)) return -1;
+    const HostPlan pl = host_plan(M, N, K, world);
+    int n = 0;
+    auto put = [&](int64_t kind, const std::pair<int64_t, int64_t>& b) {
+        if (n < capacity) { kind_first_count[3 * n] = kind; kind_first_count[3 * n + 1] = b.first; kind_first_count[3 * n + 2] = b.second; }
+        ++n;
+    };
+    for (const auto& b : pl.col_blocks) put(0, b);
+    for (const auto& b : pl.pieces) put(1, b);
+    for (const auto& b : pl.row_blocks) put(2, b);
+    return n;
+}
+
 /* The host-resident product.  With `share` (several ranks, every one of which can read the whole B in host memory)
  * a column block of B is kept contiguous on the device, this rank uploads only rows [k_first, k_last) of it and
  * share->gather completes it from the peers; M may then be 0 (a rank without rows still contributes its rows of B). */
@@ -371,31 +446,10 @@ int decxb_gemm_host_pipeline(decxb_ctx* ctx, int mode, int tile, int64_t M, int6
     if ((rc = scratch.get((size_t)N * Kp * 4, (void**)&b_hi))) return rc;
     if (x3 && (rc = scratch.get((size_t)N * Kp * 4, (void**)&b_lo))) return rc;
     if ((rc = fence_copy_streams(ctx, evs))) return rc;
-    /* later row-blocks: about 1/8 of M, multiples of 256 rows, at least 512 */
-    int64_t rows = decxb_ceil_to(decxb_ceil_div(M, 8), 256);
-    if (rows < 512) rows = 512;
-    if (rows > M) rows = M;
-    /* first row-block: about K rows; column blocks of B: about 1/8 of N, at least 1024 columns */
-    int64_t rows0 = decxb_ceil_to(K, 256);
-    /* ... but no more rows than the GPU needs to stay busy while B comes up: multiplying rows0 rows with a column
-     * block takes 2 rows0 ncol K / F, uploading the block 4 K ncol / BW, equal at rows0 = 2 F / BW, about 10 000 rows
-     * at 250 TFLOP/s and 50 GB/s, whatever the sizes.  (With K = 32768 the first block was the whole of A: 80 ms of
-     * upload with the GPU idle.) */
-    int64_t cap0 = 10240;
-    /* shares of B arrive `world` times as fast, over a host link that the ranks of the box share (measured per rank:
-     * about 0.9 of the rate of a rank alone at 2 ranks, 0.5 at 4 and 8) */
-    if (share && share->world > 1) {
-        double slow = 0.6 + 0.25 * share->world;
-        if (slow > 2.0) slow = 2.0;
-        cap0 = decxb_ceil_to((int64_t)(10240.0 * slow / share->world), 256);
-    }
-    if (cap0 < 1024) cap0 = 1024;
-    if (rows0 > cap0) rows0 = cap0;
-    if (rows0 < rows) rows0 = rows;
-    if (rows0 > M) rows0 = M;
-    int64_t ncol = decxb_ceil_to(decxb_ceil_div(N, 8), 256);
-    if (ncol < 1024) ncol = 1024;
-    if (N < 2048 || ncol > N) ncol = N;
+    const HostPlan plan = host_plan(M, N, K, share ? share->world : 1);
+    const int64_t rows0 = plan.rows0;
+    const auto& col_blocks = plan.col_blocks;
+    const auto& row_blocks = plan.row_blocks;
 
     auto fail = [&](int code) { drain_all_streams(ctx); return code; };
     float *a0_hi = dA, *a0_lo = nullptr;
@@ -443,32 +497,10 @@ int decxb_gemm_host_pipeline(decxb_ctx* ctx, int mode, int tile, int64_t M, int6
     /* The first column block of B goes up first, then the first row block of A in up to four pieces: each piece is
      * split and multiplied with that column block as it lands, so the arithmetic starts a quarter of the way into
      * the row block's upload instead of at its end. */
-    /* the first column blocks are narrower (a quarter, then half of the regular width): less to wait for before the
-     * first product; likewise the last row blocks of the second phase, whose results nothing hides on their way home */
-    std::vector<std::pair<int64_t, int64_t>> col_blocks, row_blocks;
-    {
-        int64_t w = ncol / 4 >= 1024 && ncol % 4 == 0 ? ncol / 4 : ncol;
-        for (int64_t c0 = 0; c0 < N;) {
-            const int64_t nc = N - c0 < w ? N - c0 : w;
-            col_blocks.push_back({c0, nc});
-            c0 += nc;
-            if (w < ncol) w *= 2;
-        }
-        int64_t r0 = rows0;
-        while (r0 < M) {
-            int64_t nr = M - r0;
-            if (nr > rows) nr = rows;                                    /* regular blocks ... */
-            else if (nr >= 2048 && nr % 512 == 0) nr /= 2;               /* ... then halves of what is left, down to 1024 rows */
-            row_blocks.push_back({r0, nr});
-            r0 += nr;
-        }
-    }
     const int64_t nc0 = col_blocks[0].second;
     if ((rc = stage_b_block(0, nc0))) return rc;
-    int64_t piece = decxb_ceil_to(decxb_ceil_div(rows0 > 0 ? rows0 : 1, 4), 256);
-    if (piece < 512) piece = 512;
-    for (int64_t r0 = 0; r0 < rows0; r0 += piece) {
-        const int64_t nr = rows0 - r0 < piece ? rows0 - r0 : piece;
+    for (const auto& pc : plan.pieces) {
+        const int64_t r0 = pc.first, nr = pc.second;
         cudaEvent_t e_up = evs.make();
         if (!e_up) return fail(decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"));
         PIPE_TRY(cudaMemcpy2DAsync(dA + r0 * Kp, Kp * 4, hA + r0 * lda, lda * 4, K * 4, nr, cudaMemcpyHostToDevice, up));

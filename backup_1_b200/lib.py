@@ -115,6 +115,7 @@ SIGNATURES = {
     "decxb_comm_allgather_blocks": (_i, [_vp, _vp, _sz, _i64, _vp]),
     "decxb_gemm_f32_rowshard_gather": (_i, [_vp, _vp, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i, _vp]),
     "decxb_gemm_f32_rowshard_host": (_i, [_vp, _vp, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64]),
+    "decxb_gemm_host_plan": (_i, [_i64, _i64, _i64, _i, _vp, _i]),
     "decxb_comm_selftest_handshake": (_i, [C.c_char_p, _i, _i, _vp, _i, C.c_char_p, _sz]),
     "decxb_probe_tensor_peak": (_i, [_vp, _i, C.c_double, C.POINTER(TensorProbe)]),
     "decxb_bounds_build": (_i, []),

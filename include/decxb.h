@@ -487,6 +487,13 @@ DECXB_API int decxb_gemm_f32_rowshard_host(decxb_ctx* ctx, decxb_comm* comm, int
                                            int64_t M, int64_t N, int64_t K,
                                            const float* hA_rows, int64_t lda, const float* hB, int64_t ldb,
                                            float* hD_rows, int64_t ldd);
+/* How decxb_gemm_f32_host (world = 1) and decxb_gemm_f32_rowshard_host (M = the rank's rows) cut a product: pure
+ * host arithmetic, no CUDA call.  Writes up to `capacity` triples (kind, first, count) in the order of use and
+ * returns how many there are (-1 for bad arguments): kind 0 = a column block of B (columns first .. first+count),
+ * kind 1 = a piece of the first row-block of A, kind 2 = a later row-block.  The column blocks cover [0, N) once,
+ * pieces and row-blocks together cover [0, M) once.  For tests and for callers that want to see the granularity of
+ * the copies; no counterpart in the reference, whose host path copies whole matrices (GEMM.h:106-123). */
+DECXB_API int decxb_gemm_host_plan(int64_t M, int64_t N, int64_t K, int world, int64_t* kind_first_count, int capacity);
 /* Failure-detection self-test on the host: the joining half of decxb_comm_init (load the library at
  * nccl_path, non-blocking init, bounded poll, abort on expiry) with no CUDA call, so that a rank
  * which never arrives can be played by a stand-in library on a machine without a GPU. */

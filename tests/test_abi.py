@@ -65,3 +65,52 @@ def test_config_sizes_of_baseline():
     assert (g3.M, g3.Kp) == (50176, 576) and g3.M * g3.Kp * 4 == 115605504
     g4 = b.conv_geometry(56, 56, 256, 3, 3, 256, 1)
     assert (g4.M, g4.Kp) == (3136, 2304) and g4.M * g4.Kp * 4 == 28901376
+
+
+def _host_plan(L, M, N, K, world):
+    n = L.decxb_gemm_host_plan(M, N, K, world, None, 0)
+    assert n >= 1
+    buf = (C.c_int64 * (3 * n))()
+    assert L.decxb_gemm_host_plan(M, N, K, world, buf, n) == n
+    t = [tuple(buf[3 * i:3 * i + 3]) for i in range(n)]
+    return [x[1:] for x in t if x[0] == 0], [x[1:] for x in t if x[0] == 1], [x[1:] for x in t if x[0] == 2]
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("dims", [(32768, 32768, 32768), (8192, 4096, 2048), (1, 1, 1), (5, 64, 3), (24000, 2304, 64),
+                                  (700, 3001, 70), (4099, 520, 300), (10241, 2047, 9000), (0, 128, 128)])
+def test_host_pipeline_plan_covers_every_row_and_column_once(world, dims):
+    """The cut of the host-resident product (pure host arithmetic): the column blocks of B tile [0, N), the pieces
+    of the first row-block followed by the later row-blocks tile [0, M), nothing is empty, and the blocks that
+    the peers complete start on a 16-byte boundary of the row."""
+    L = b.load_library()
+    M, N, K = dims
+    if M == 0 and world == 1:
+        M = 1
+    cols, pieces, rows = _host_plan(L, M, N, K, world)
+    at = 0
+    for first, count in cols:
+        assert first == at and count > 0
+        assert first % 4 == 0
+        at += count
+    assert at == N
+    at = 0
+    for first, count in pieces + rows:
+        assert first == at and count > 0
+        at += count
+    assert at == M
+    if M > 0:
+        assert len(pieces) >= 1 and len(pieces) <= 4
+    # the first row-block shrinks with the number of ranks that share the host link, never below a quarter of a tile wave
+    first_rows = sum(c for _, c in pieces)
+    assert first_rows <= max(10240, -(-M // 8 // 256) * 256, 512)
+    if world > 1 and M >= 10240 and K >= 10240:
+        assert first_rows < 10240
+
+
+def test_host_pipeline_plan_rejects_bad_arguments():
+    L = b.load_library()
+    assert L.decxb_gemm_host_plan(-1, 8, 8, 1, None, 0) == -1
+    assert L.decxb_gemm_host_plan(8, 0, 8, 1, None, 0) == -1
+    assert L.decxb_gemm_host_plan(8, 8, 8, 0, None, 0) == -1
+    assert L.decxb_gemm_host_plan(8, 8, 8, 1, None, 4) == -1
