@@ -697,13 +697,26 @@ def main():
     err = bench.max_over_ranks(err) if err is not None else None
 
     # ---- the NCCL layer (N > 1): B's shares in the host-resident leg, the result blocks after it ---------
-    comm = None
+    comm, comm_error = None, None
     if world > 1 and wl["scaling"] == "strong" and not (args.no_gather and args.no_host_gather):
         if args.comm_ctas > 0:
             os.environ["DECXB_COMM_MAX_CTAS"] = str(args.comm_ctas)
-        uid = [bench.b.Comm.unique_id() if rank == 0 else None]
+        # the layer loads NCCL at run time: if it cannot on this box, every rank goes on without it (said in the line)
+        try:
+            uid = [bench.b.Comm.unique_id() if rank == 0 else None]
+        except Exception as ex:
+            uid, comm_error = [None], str(ex)[:200]
         dist.broadcast_object_list(uid, src=0)
-        comm = bench.b.Comm(ctx, world, rank, uid[0], timeout_ms=120000)
+        if uid[0] is not None:
+            try:
+                comm = bench.b.Comm(ctx, world, rank, uid[0], timeout_ms=120000)
+            except Exception as ex:
+                comm_error = str(ex)[:200]
+        if bench.max_over_ranks(0.0 if comm is not None else 1.0) > 0.0:
+            if comm is not None:
+                comm.close()
+            comm = None
+            comm_error = comm_error or "the communicator could not be created on another rank"
 
     # ---- host-resident leg (e2e) ---------------------------------------------------------------------
     e2e_how = "decxb_gemm_f32_host / decxb_conv2_im2col_f32_host per rank on its shard: every rank uploads all of the shared operand"
@@ -897,6 +910,8 @@ def main():
                                       "the same clocks; `value` uses the plain entry, which prepares them on every call"),
             "gpu_launches": res["launches"], "clocks": clocks, "per_rank_ms_per_step": per_rank_ms, "also": also,
         }
+        if comm_error:
+            line["comm_unavailable"] = comm_error
         if gather:
             line["allgather"] = gather
             line["value_with_gather"] = res["total_flops"] / ((res["ms_per_step"] + gather["ms"]) * 1e-3) / 1e12
