@@ -53,7 +53,9 @@ ALSO = [("gemm16k", 5), ("cfg2", 40), ("cfg4", 8), ("cfg3", 60), ("cfg1", 60)]  
 NCU_TRAFFIC_BYTES = {("cfg2", "3xtf32", "gemm"): 727.8e6, ("cfg2", "strict", "gemm"): 737.8e6,
                      ("cfg3", "3xtf32", "pack"): 70.7e6, ("cfg3", "strict", "pack"): 70.7e6,
                      ("cfg4", "strict", "gemm"): 2530e6, ("cfg4", "3xtf32", "gemm"): 2515e6,
-                     ("cfg2", "tf32bf16", "gemm"): 738.0e6}
+                     ("cfg2", "tf32bf16", "gemm"): 738.0e6,
+                     # one launch of the whole 32768^3 product on one GPU (275.23 GB read + 4.44 GB written)
+                     ("cfg5", "strict", "gemm"): 279.67e9}
 # DRAM bytes per algorithmic flop of the 256 x 256-tile GEMM with the block pairs aligned, from the single-pass capture at
 # 16384^3 in profiles/gemm_tf32_kernel_16384.md (35.44 GB read + 1.10 GB written per 2 * 16384^3 flop).  A wave of 74
 # tiles reads 17.25 operand panels whatever K and N are, so the traffic of a larger product grows with its flops.
@@ -527,6 +529,8 @@ class Bench:
             bf16 = peaks["bf16_sustained"] if long_step else peaks["bf16_tflops"]
             peak = bf16 / div
             traffic = NCU_TRAFFIC_BYTES.get((w["name"], mode, "gemm")) if args.tile == 0 else None
+            if traffic is not None and wl["kind"] == "gemm" and (w["M_rank"] != wl["M"] or args.wave_align == 0):
+                traffic = None                      # the capture is of the unsharded, aligned launch
             if traffic is not None and wl["kind"] == "conv":
                 traffic = traffic * w["nb"] / wl["batch"] if (args.algo == "implicit" and not args.batch) else None
             traffic_note = None
