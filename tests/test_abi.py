@@ -114,3 +114,23 @@ def test_host_pipeline_plan_rejects_bad_arguments():
     assert L.decxb_gemm_host_plan(8, 0, 8, 1, None, 0) == -1
     assert L.decxb_gemm_host_plan(8, 8, 8, 0, None, 0) == -1
     assert L.decxb_gemm_host_plan(8, 8, 8, 1, None, 4) == -1
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_host_pipeline_plan_gives_every_rank_the_same_column_blocks(world):
+    """Ranks of a sharded host-resident product complete each column block of B together (one collective per block),
+    so the blocks must not depend on how many rows a rank owns: unequal shards, and ranks without rows, included."""
+    L = b.load_library()
+    for (M, N, K) in [(32768, 32768, 32768), (4099, 3001, 300), (5, 64, 3), (24001, 2304, 64)]:
+        plans = []
+        for rank in range(world):
+            f, l = b.shard_range(M, world, rank)
+            plans.append(_host_plan(L, l - f, N, K, world)[0])
+        assert all(p == plans[0] for p in plans)
+        # and the shares of B's rows that the ranks upload tile [0, K)
+        at = 0
+        for rank in range(world):
+            f, l = b.shard_range(K, world, rank)
+            assert f == at
+            at = l
+        assert at == K
