@@ -583,22 +583,53 @@ extern "C" int decxb_gemm_f16_host(decxb_ctx* ctx, int64_t M, int64_t N, int64_t
     if (!hA || !hB || !hD) return decxb_fail(ctx, DECXB_ERR_BAD_PARAM, "null operand");
     if (lda < K || ldb < N || ldd < N || (hC && ldc < N))
         return decxb_fail(ctx, DECXB_ERR_DIM_MISMATCH, "leading dimension smaller than the row length");
-    cudaStream_t s = ctx->stream;
+    /* Three streams, as in the fp32 entry: B goes up first and is transposed once, then A (and C) in row blocks
+     * of about an eighth of M: upload, product and the result's way home overlap.  (The reference stages the three
+     * phases one after the other, GEMM.h:106-123.) */
+    cudaStream_t s = ctx->stream, up = ctx->copy_stream[0], down = ctx->copy_stream[1];
     Scratch scratch(ctx, s);
+    ChunkEvents evs;
     const int64_t Kp = decxb_ceil_to(K, 8), Np = decxb_ceil_to(N, 8);
-    void *dA, *dB, *dC = nullptr, *dD;
-    if ((rc = scratch.get((size_t)M * Kp * 2, &dA))) return rc;
-    if ((rc = scratch.get((size_t)K * Np * 2, &dB))) return rc;
-    if ((rc = scratch.get((size_t)M * Np * 2, &dD))) return rc;
-    if (hC && (rc = scratch.get((size_t)M * Np * 2, &dC))) return rc;
-    auto fail = [&](int code) { cudaStreamSynchronize(s); cudaGetLastError(); return code; };
-    PIPE_TRY(cudaMemcpy2DAsync(dA, Kp * 2, hA, lda * 2, K * 2, M, cudaMemcpyHostToDevice, s));
-    PIPE_TRY(cudaMemcpy2DAsync(dB, Np * 2, hB, ldb * 2, N * 2, K, cudaMemcpyHostToDevice, s));
-    if (hC) PIPE_TRY(cudaMemcpy2DAsync(dC, Np * 2, hC, ldc * 2, N * 2, M, cudaMemcpyHostToDevice, s));
-    rc = gemm_f16_device(ctx, M, N, K, dA, Kp, dB, Np, dC, Np, dD, Np, s);
-    if (rc) return fail(rc);
-    PIPE_TRY(cudaMemcpy2DAsync(hD, ldd * 2, dD, Np * 2, N * 2, M, cudaMemcpyDeviceToHost, s));
-    PIPE_TRY(cudaStreamSynchronize(s));
+    char *dA, *dB, *dC = nullptr, *dD, *bt;
+    if ((rc = scratch.get((size_t)M * Kp * 2, (void**)&dA))) return rc;
+    if ((rc = scratch.get((size_t)K * Np * 2, (void**)&dB))) return rc;
+    if ((rc = scratch.get((size_t)M * Np * 2, (void**)&dD))) return rc;
+    if (hC && (rc = scratch.get((size_t)M * Np * 2, (void**)&dC))) return rc;
+    if ((rc = scratch.get((size_t)N * Kp * 2, (void**)&bt))) return rc;
+    if ((rc = fence_copy_streams(ctx, evs))) return rc;
+    auto fail = [&](int code) { drain_all_streams(ctx); return code; };
+    cudaEvent_t e_b = evs.make();
+    if (!e_b) return decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate");
+    PIPE_TRY(cudaMemcpy2DAsync(dB, Np * 2, hB, ldb * 2, N * 2, K, cudaMemcpyHostToDevice, up));
+    PIPE_TRY(cudaEventRecord(e_b, up));
+    PIPE_TRY(cudaStreamWaitEvent(s, e_b, 0));
+    if ((rc = decxb_launch_transpose_f16(ctx, dB, K, N, Np, bt, Kp, s))) return fail(rc);
+    int64_t rows = decxb_ceil_to(decxb_ceil_div(M, 8), 256);
+    if (rows < 1024) rows = 1024;
+    if (rows > M) rows = M;
+    const char *hA8 = (const char*)hA, *hC8 = (const char*)hC;
+    char* hD8 = (char*)hD;
+    for (int64_t r0 = 0; r0 < M; r0 += rows) {
+        const int64_t nr = M - r0 < rows ? M - r0 : rows;
+        cudaEvent_t e_up = evs.make(), e_done = evs.make();
+        if (!e_up || !e_done) return fail(decxb_fail(ctx, DECXB_ERR_CUDA, "cudaEventCreate"));
+        PIPE_TRY(cudaMemcpy2DAsync(dA + r0 * Kp * 2, Kp * 2, hA8 + r0 * lda * 2, lda * 2, K * 2, nr, cudaMemcpyHostToDevice, up));
+        if (hC) PIPE_TRY(cudaMemcpy2DAsync(dC + r0 * Np * 2, Np * 2, hC8 + r0 * ldc * 2, ldc * 2, N * 2, nr, cudaMemcpyHostToDevice, up));
+        PIPE_TRY(cudaEventRecord(e_up, up));
+        PIPE_TRY(cudaStreamWaitEvent(s, e_up, 0));
+        decxb_gemm_f16_args g = {};
+        g.M = nr; g.N = N; g.K = K;
+        g.A = dA + r0 * Kp * 2; g.lda = Kp;               /* pitch ceil8(K): every row block starts on a 16-byte boundary */
+        g.Bt = bt; g.ldbt = Kp;
+        g.C = dC ? dC + r0 * Np * 2 : nullptr; g.ldc = Np;
+        g.D = dD + r0 * Np * 2; g.ldd = Np;
+        g.act = DECXB_ACT_NONE;
+        if ((rc = decxb_launch_gemm_f16_tn(ctx, g, s))) return fail(rc);
+        PIPE_TRY(cudaEventRecord(e_done, s));
+        PIPE_TRY(cudaStreamWaitEvent(down, e_done, 0));
+        PIPE_TRY(cudaMemcpy2DAsync(hD8 + r0 * ldd * 2, ldd * 2, dD + r0 * Np * 2, Np * 2, N * 2, nr, cudaMemcpyDeviceToHost, down));
+    }
+    if ((rc = sync_all_streams(ctx))) return rc;
     scratch.release();
     return decxb_check_dev_status(ctx);
 }

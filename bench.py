@@ -723,7 +723,7 @@ def main():
             comm_error = comm_error or "the communicator could not be created on another rank"
 
     # ---- host-resident leg (e2e) ---------------------------------------------------------------------
-    e2e_how = ("decxb_gemm_f32_host / decxb_conv2_im2col_f32_host" if world == 1 else
+    e2e_how = ("decxb_gemm_f16_host" if args.mode == "f16" else "decxb_gemm_f32_host / decxb_conv2_im2col_f32_host" if world == 1 else
                "decxb_gemm_f32_host / decxb_conv2_im2col_f32_host per rank on its shard: every rank uploads all of the shared operand")
     if comm is not None and wl["kind"] == "gemm" and args.mode != "f16" and not args.no_host_gather:
         hA, hB, hD = w["host"]
